@@ -1,0 +1,176 @@
+/*
+ * pccnn_b200.h -- C ABI of libpccnn_b200.so, the sm_100a implementation of the
+ * point-convolution hot path of phermosilla/pccnn_lib.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its name ends in `_host`.
+ *   - Arrays are contiguous row-major.  Points are [n, D] float32, batch ids
+ *     int32, grid keys int64, neighbor lists [T, 2] int32 rows
+ *     (point index, sample index) grouped by ascending sample index, and
+ *     `start_ids[m]` is the INCLUSIVE END offset of sample m in that list
+ *     (the reference's naming; see compute_pdf/compute_pdf.cu:51-52 there).
+ *   - D is the point dimension, 2 <= D <= 6 (shared/defines.cuh:41-58 of the
+ *     reference dispatches the same range).
+ *   - `grid_size` [D] int32, `cell_size` / `radii` / `bandwidth` [D] float32 live
+ *     on the device, as the reference's tensors do.
+ *   - `stream` is a cudaStream_t passed as void*.  Calls enqueue on it and
+ *     return without synchronising, except where a host result is documented.
+ *   - Scratch memory is supplied by the caller: ask the matching
+ *     *_workspace_bytes() function, allocate at least that much (256-byte
+ *     aligned), and pass it in.  The library itself never allocates device
+ *     memory.
+ *   - Every function returns PCCNN_OK (0) or an error code; the text of the last
+ *     error of the calling thread is available from pccnn_last_error().
+ *   - There is no CPU fallback: without a CUDA device every compute entry point
+ *     returns PCCNN_ERR_CUDA.
+ *
+ * File:line citations name the reference interface each entry point replaces,
+ * relative to the root of phermosilla/pccnn_lib.
+ */
+#ifndef PCCNN_B200_H_
+#define PCCNN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PCCNN_OK 0
+#define PCCNN_ERR_INVALID 1   /* bad argument (dimension, size, null pointer, alignment) */
+#define PCCNN_ERR_CUDA 2      /* CUDA runtime error; message holds cudaGetErrorString */
+#define PCCNN_ERR_WORKSPACE 3 /* workspace too small */
+#define PCCNN_ERR_OVERFLOW 4  /* neighbor count does not fit the int32 CSR of the reference */
+#define PCCNN_ERR_DEVICE 5    /* a kernel reported a failed internal check (bounded wait ran out, bad index) */
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* pccnn_last_error(void);
+/* Library version string. */
+const char* pccnn_version(void);
+
+/* ------------------------------------------------------------------------- */
+/* Bounding box and grid sizing (caller-side code of the reference)           */
+/* ------------------------------------------------------------------------- */
+
+/* Per-cloud axis-aligned bounding box, exact float min/max then -/+ 1e-6f.
+ * Replaces pccnn_lib/pc/BoundingBox.py:17-18 (torch_scatter scatter_min/max).
+ * out_min, out_max: [num_batches, D] float32.  Clouds without points get
+ * +inf / -inf before the epsilon is applied. */
+int pccnn_bounding_box(int D, int64_t n, const float* pts, const int32_t* batch_ids,
+                       int64_t num_batches, float* out_min, float* out_max, void* stream);
+
+/* num_cells[d] = max_b( (int32)((max[b,d] - min[b,d]) / cell_size[d]) + 1 ).
+ * Replaces pccnn_lib/pc/Grid.py:27-28.  out_grid_size: [D] int32 on device. */
+int pccnn_grid_num_cells(int D, int64_t num_batches, const float* aabb_min, const float* aabb_max,
+                         const float* cell_size, int32_t* out_grid_size, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Keys, sort, cell-range table                                               */
+/* ------------------------------------------------------------------------- */
+
+/* Grid key of every point:  cell = clamp((int)floorf((p - min_b) * (1/cell)), 0, nc-1),
+ * key = row-major index over (batch, cell_0, ..., cell_{D-1}), last dimension fastest.
+ * Replaces compute_keys()  pccnn_lib_ops/compute_keys/compute_keys.cu:78-128
+ * (kernel :35-74, cell/key math shared/grid_utils.cuh:57-94).  Bit-exact. */
+int pccnn_compute_keys(int D, int64_t n, const float* pts, const int32_t* batch_ids,
+                       const float* aabb_min, const int32_t* grid_size, const float* cell_size,
+                       int64_t* out_keys, void* stream);
+
+/* Stable ascending sort of the keys; out_sorted_ids is the permutation (ties keep
+ * ascending original index).  Replaces torch.argsort in pccnn_lib/pc/Grid.py:52
+ * and the gather of the keys in Grid.py:68-70.  `key_bits` = number of low key bits
+ * that can be non-zero (1..64; 64 is always safe).  out_sorted_pts may be NULL;
+ * otherwise the points are gathered into sorted order too (D and pts required),
+ * replacing the index_select of pccnn_lib/pc/Neighborhood.py:27-29. */
+size_t pccnn_sort_keys_workspace_bytes(int64_t n);
+int pccnn_sort_keys(int64_t n, const int64_t* keys, int key_bits, int64_t* out_sorted_keys,
+                    int64_t* out_sorted_ids, int D, const float* pts, float* out_sorted_pts,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* Cell-range table over SORTED keys: entry (b, c0, c1) = [first, last+1) positions of
+ * the points whose cell starts with (c0, c1); untouched entries stay (0, 0).
+ * out_grid_ds: [num_entries, 2] int32, num_entries = B*nc0*nc1; zero-filled here.
+ * Replaces build_grid_ds()  pccnn_lib_ops/build_grid/build_grid_ds.cu:72-114
+ * (kernel :32-68, index math shared/grid_utils.cuh:127-137).  Bit-exact. */
+int pccnn_build_grid_ds(int D, int64_t n, const int64_t* sorted_keys, const int32_t* grid_size,
+                        int64_t num_entries, int32_t* out_grid_ds, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Radius neighbor search                                                     */
+/* ------------------------------------------------------------------------- */
+
+/* Two calls replace find_neighbors()  pccnn_lib_ops/find_neighbors/find_neighbors.cu:27-66
+ * (find_ranges_grid_ds.cu:41-167,306-338; count_neighbors.cu:37-104;
+ * store_neighbors.cu:45-282): the first counts and scans, the second writes the list
+ * once the caller has allocated it.
+ *
+ * A point p of the sorted array `pts` is a neighbor of sample s iff both are in the
+ * same cloud and sqrtf(sum_d ((s_d - p_d) * (1/radii_d))^2) < 1.0f, evaluated with the
+ * reference's float operation order.  The radius must equal the grid cell size.
+ * Within a sample the rows are in ascending order of the point index (the
+ * reference's order is the nondeterministic order of its atomic tickets).
+ *
+ * max_neighbors > 0: a sample with more than max_neighbors hits keeps exactly
+ * max_neighbors of them, chosen at even strides through the ascending list (the
+ * reference keeps a random subset of that size, store_neighbors.cu:45-113).
+ *
+ * pccnn_find_neighbors_count writes out_start_ids[num_samples] (inclusive ends) and,
+ * after synchronising the stream, *out_total_host = T.  The workspace keeps the raw
+ * per-sample counts for the store call and must be passed to it unchanged.
+ * Returns PCCNN_ERR_OVERFLOW if T >= 2^31. */
+size_t pccnn_find_neighbors_workspace_bytes(int D, int64_t num_samples);
+int pccnn_find_neighbors_count(int D, int64_t num_pts, const float* pts, const int64_t* pt_keys,
+                               int64_t num_samples, const float* samples, const int64_t* sample_keys,
+                               const int32_t* grid_ds, const int32_t* grid_size, const float* radii,
+                               int32_t max_neighbors, int32_t* out_start_ids, int64_t* out_total_host,
+                               void* workspace, size_t workspace_bytes, void* stream);
+/* pt_index_map may be NULL; otherwise row.x = (int32)pt_index_map[point index], which
+ * replaces the mapping through sorted_ids in pccnn_lib/pc/Neighborhood.py:47-53. */
+int pccnn_find_neighbors_store(int D, int64_t num_pts, const float* pts, const int64_t* pt_keys,
+                               int64_t num_samples, const float* samples, const int64_t* sample_keys,
+                               const int32_t* grid_ds, const int32_t* grid_size, const float* radii,
+                               int32_t max_neighbors, const int32_t* start_ids,
+                               const int64_t* pt_index_map, int32_t* out_neighbors,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Kernel density estimation                                                  */
+/* ------------------------------------------------------------------------- */
+
+/* pdf_i = sum_{j in seg(i)} prod_d(1/bw_d) * (2*3.1415)^(-manifold_dims/2)
+ *                           * expf(-0.5 * |(p_j - p_i) * (1/bw)|^2).
+ * Replaces compute_pdf()  pccnn_lib_ops/compute_pdf/compute_pdf.cu:153-203 (kernel :24-77).
+ * float32, summation order differs from the reference: tolerance-matched. */
+int pccnn_compute_pdf(int D, int manifold_dims, const float* bandwidth, int64_t n, const float* pts,
+                      const int32_t* neighbors, const int32_t* start_ids, float* out_pdf, void* stream);
+
+/* Gradient of sum_i in_grads[i] * pdf_i with respect to the points.
+ * Replaces compute_pdf_grads()  compute_pdf.cu:206-257 (kernel :80-149).
+ * out_pt_grads: [n, D] float32, zero-filled here. */
+int pccnn_compute_pdf_grads(int D, int manifold_dims, const float* bandwidth, int64_t n, const float* pts,
+                            const int32_t* neighbors, const int32_t* start_ids, const float* in_grads,
+                            float* out_pt_grads, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Poisson-disk sampling                                                      */
+/* ------------------------------------------------------------------------- */
+
+/* Cell-parallel greedy Poisson-disk selection over points in SORTED order with a
+ * self-neighborhood in sorted index space: 2^D passes by cell parity, cells of one
+ * pass in parallel, points of a cell in ascending position, a point is selected iff
+ * none of its neighbors is selected yet.
+ * Replaces poisson_disk_sampling()
+ * pccnn_lib_ops/poisson_disk_sampling/poisson_disk_sampling.cu:110-196 (kernel :36-106).
+ * out_selected: capacity n int64, ascending positions; *out_count_host = how many
+ * (written after synchronising the stream). */
+size_t pccnn_poisson_disk_sampling_workspace_bytes(int64_t n);
+int pccnn_poisson_disk_sampling(int D, int64_t n, const int64_t* sorted_keys, const int32_t* neighbors,
+                                const int32_t* start_ids, const int32_t* grid_size, int64_t* out_selected,
+                                int64_t* out_count_host, void* workspace, size_t workspace_bytes,
+                                void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PCCNN_B200_H_ */

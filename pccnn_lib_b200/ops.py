@@ -1,0 +1,236 @@
+"""Operator module with the call signatures of the reference's ``pccnn_lib_ops`` extension.
+
+Each function mirrors one ``m.def`` of pccnn_lib_ops/ops_list.cpp:27-43 of phermosilla/pccnn_lib
+(same argument order, meaning, dtypes and output shapes) and forwards to the C ABI of
+libpccnn_b200.so with raw device pointers on the current CUDA stream.  Outputs are allocated
+with torch so they live in the caller's caching allocator.  Tensors must be CUDA tensors:
+there is no CPU path.
+"""
+import ctypes
+
+import torch
+
+from . import _capi
+
+_lib = _capi.lib
+
+
+# ---- argument plumbing -----------------------------------------------------------------------
+def _need(t, name, dtype, ndim=None):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError("%s must be a torch.Tensor" % name)
+    if not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor (pccnn_lib_b200 has no CPU path)" % name)
+    if t.dtype != dtype:
+        raise RuntimeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+    if ndim is not None and t.dim() != ndim:
+        raise RuntimeError("%s must have %d dimensions, got %d" % (name, ndim, t.dim()))
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _p(t):
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _dims(pts, name="pts"):
+    d = pts.shape[1]
+    if d < 2 or d > 6:
+        raise RuntimeError("%s has %d dimensions; supported range is [2, 6]" % (name, d))
+    return d
+
+
+# ---- grid front end --------------------------------------------------------------------------
+def bounding_box(pts, batch_ids, num_batches):
+    """Per-cloud (min - 1e-6, max + 1e-6); pccnn_lib/pc/BoundingBox.py:17-18 of the reference."""
+    pts = _need(pts, "pts", torch.float32, 2)
+    batch_ids = _need(batch_ids, "batch_ids", torch.int32, 1)
+    d = _dims(pts)
+    b = int(num_batches)
+    mn = torch.empty((b, d), dtype=torch.float32, device=pts.device)
+    mx = torch.empty((b, d), dtype=torch.float32, device=pts.device)
+    with torch.cuda.device(pts.device):
+        _capi.check(_lib.pccnn_bounding_box(d, pts.shape[0], _p(pts), _p(batch_ids), b, _p(mn), _p(mx),
+                                            _stream()), "bounding_box")
+    return mn, mx
+
+
+def grid_num_cells(aabb_min, aabb_max, cell_size):
+    """Cells per dimension shared by all clouds; pccnn_lib/pc/Grid.py:27-28 of the reference."""
+    aabb_min = _need(aabb_min, "aabb_min", torch.float32, 2)
+    aabb_max = _need(aabb_max, "aabb_max", torch.float32, 2)
+    cell_size = _need(cell_size, "cell_size", torch.float32, 1)
+    d = aabb_min.shape[1]
+    out = torch.empty((d,), dtype=torch.int32, device=aabb_min.device)
+    with torch.cuda.device(aabb_min.device):
+        _capi.check(_lib.pccnn_grid_num_cells(d, aabb_min.shape[0], _p(aabb_min), _p(aabb_max), _p(cell_size),
+                                              _p(out), _stream()), "grid_num_cells")
+    return out
+
+
+def compute_keys(pts, batch_ids, aabb_min, grid_size, cell_size):
+    """int64 grid key per point; compute_keys() of compute_keys/compute_keys.cu:78-128."""
+    pts = _need(pts, "pts", torch.float32, 2)
+    batch_ids = _need(batch_ids, "batch_ids", torch.int32, 1)
+    aabb_min = _need(aabb_min, "aabb_min", torch.float32, 2)
+    grid_size = _need(grid_size, "grid_size", torch.int32, 1)
+    cell_size = _need(cell_size, "cell_size", torch.float32, 1)
+    d = _dims(pts)
+    if grid_size.numel() != d or cell_size.numel() != d or aabb_min.shape[1] != d:
+        raise RuntimeError("grid_size, cell_size and aabb_min must match the point dimension %d" % d)
+    if batch_ids.shape[0] != pts.shape[0]:
+        raise RuntimeError("batch_ids and pts disagree on the number of points")
+    out = torch.empty((pts.shape[0],), dtype=torch.int64, device=pts.device)
+    with torch.cuda.device(pts.device):
+        _capi.check(_lib.pccnn_compute_keys(d, pts.shape[0], _p(pts), _p(batch_ids), _p(aabb_min),
+                                            _p(grid_size), _p(cell_size), _p(out), _stream()), "compute_keys")
+    return out
+
+
+def sort_keys(keys, key_bits=64, pts=None):
+    """Stable sort of the keys -> (sorted_keys, sorted_ids[, sorted_pts]).
+
+    Replaces torch.argsort of pccnn_lib/pc/Grid.py:52 and the index_select gathers that follow
+    it (Grid.py:68-70, Neighborhood.py:27-32).  Ties keep ascending original index.
+    """
+    keys = _need(keys, "keys", torch.int64, 1)
+    n = keys.shape[0]
+    sorted_keys = torch.empty_like(keys)
+    sorted_ids = torch.empty_like(keys)
+    d, sorted_pts = 0, None
+    if pts is not None:
+        pts = _need(pts, "pts", torch.float32, 2)
+        d = _dims(pts)
+        sorted_pts = torch.empty_like(pts)
+    with torch.cuda.device(keys.device):
+        nbytes = _lib.pccnn_sort_keys_workspace_bytes(n)
+        ws = _workspace(nbytes, keys.device)
+        _capi.check(_lib.pccnn_sort_keys(n, _p(keys), int(key_bits), _p(sorted_keys), _p(sorted_ids), d, _p(pts),
+                                         _p(sorted_pts), ws.data_ptr(), ws.numel(), _stream()), "sort_keys")
+    if pts is None:
+        return sorted_keys, sorted_ids
+    return sorted_keys, sorted_ids, sorted_pts
+
+
+def build_grid_ds(keys, grid_size, out_shape):
+    """[B, nc0, nc1, 2] int32 cell-range table; build_grid_ds() of build_grid/build_grid_ds.cu:72-114."""
+    keys = _need(keys, "keys", torch.int64, 1)
+    grid_size = _need(grid_size, "grid_size", torch.int32, 1)
+    shape = [int(v) for v in out_shape]
+    if len(shape) != 4 or shape[3] != 2:
+        raise RuntimeError("out_shape must be [batch, cells0, cells1, 2], got %s" % (shape,))
+    d = grid_size.numel()
+    out = torch.empty(shape, dtype=torch.int32, device=keys.device)
+    entries = shape[0] * shape[1] * shape[2]
+    with torch.cuda.device(keys.device):
+        _capi.check(_lib.pccnn_build_grid_ds(d, keys.shape[0], _p(keys), _p(grid_size), entries, _p(out),
+                                             _stream()), "build_grid_ds")
+    return out
+
+
+# ---- neighbor search -------------------------------------------------------------------------
+def find_neighbors(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii, max_neighbors,
+                   pt_index_map=None):
+    """Radius search -> [neighbors [T, 2] int32, start_ids [M] int32 (inclusive ends)].
+
+    find_neighbors() of find_neighbors/find_neighbors.cu:27-66 of the reference.  `pts` and
+    `pt_keys` are in sorted order; row.x indexes that array unless `pt_index_map` (an
+    extension: the sorted_ids permutation) is given, in which case row.x is mapped through it
+    as pccnn_lib/pc/Neighborhood.py:47-53 does afterwards.
+    """
+    pts = _need(pts, "pts", torch.float32, 2)
+    pt_keys = _need(pt_keys, "pt_keys", torch.int64, 1)
+    samples = _need(samples, "samples", torch.float32, 2)
+    sample_keys = _need(sample_keys, "sample_keys", torch.int64, 1)
+    grid_ds = _need(grid_ds, "grid_ds", torch.int32)
+    grid_size = _need(grid_size, "grid_size", torch.int32, 1)
+    radii = _need(radii, "radii", torch.float32, 1)
+    if pt_index_map is not None:
+        pt_index_map = _need(pt_index_map, "pt_index_map", torch.int64, 1)
+    d = _dims(pts)
+    if samples.shape[1] != d or grid_size.numel() != d or radii.numel() != d:
+        raise RuntimeError("samples, grid_size and radii must match the point dimension %d" % d)
+    n, m = pts.shape[0], samples.shape[0]
+    if pt_keys.shape[0] != n or sample_keys.shape[0] != m:
+        raise RuntimeError("keys and coordinates disagree on the number of rows")
+    max_neighbors = int(max_neighbors)
+    start_ids = torch.empty((m,), dtype=torch.int32, device=pts.device)
+    total = ctypes.c_int64(0)
+    with torch.cuda.device(pts.device):
+        nbytes = _lib.pccnn_find_neighbors_workspace_bytes(d, m)
+        ws = _workspace(nbytes, pts.device)
+        common = (d, n, _p(pts), _p(pt_keys), m, _p(samples), _p(sample_keys), _p(grid_ds), _p(grid_size),
+                  _p(radii), max_neighbors)
+        _capi.check(_lib.pccnn_find_neighbors_count(*common, _p(start_ids), ctypes.byref(total), ws.data_ptr(),
+                                                    ws.numel(), _stream()), "find_neighbors (count)")
+        neighbors = torch.empty((total.value, 2), dtype=torch.int32, device=pts.device)
+        _capi.check(_lib.pccnn_find_neighbors_store(*common, _p(start_ids), _p(pt_index_map), _p(neighbors),
+                                                    ws.data_ptr(), ws.numel(), _stream()),
+                    "find_neighbors (store)")
+    return [neighbors, start_ids]
+
+
+# ---- kernel density estimation ---------------------------------------------------------------
+def _pdf_args(bandwidth, pts, neighbors, start_ids):
+    bandwidth = _need(bandwidth, "bandwidth", torch.float32, 1)
+    pts = _need(pts, "pts", torch.float32, 2)
+    neighbors = _need(neighbors, "neighbors", torch.int32, 2)
+    start_ids = _need(start_ids, "start_ids", torch.int32, 1)
+    d = _dims(pts)
+    if bandwidth.numel() != d:
+        raise RuntimeError("bandwidth must have %d entries" % d)
+    if start_ids.shape[0] != pts.shape[0]:
+        raise RuntimeError("start_ids must have one entry per point")
+    if neighbors.shape[1] != 2:
+        raise RuntimeError("neighbors must be [T, 2]")
+    return bandwidth, pts, neighbors, start_ids, d
+
+
+def compute_pdf(manifold_dims, bandwidth, pts, neighbors, start_ids):
+    """Unnormalised KDE per point; compute_pdf() of compute_pdf/compute_pdf.cu:153-203."""
+    bandwidth, pts, neighbors, start_ids, d = _pdf_args(bandwidth, pts, neighbors, start_ids)
+    out = torch.empty((pts.shape[0],), dtype=torch.float32, device=pts.device)
+    with torch.cuda.device(pts.device):
+        _capi.check(_lib.pccnn_compute_pdf(d, int(manifold_dims), _p(bandwidth), pts.shape[0], _p(pts),
+                                           _p(neighbors), _p(start_ids), _p(out), _stream()), "compute_pdf")
+    return out
+
+
+def compute_pdf_grads(manifold_dims, bandwidth, pts, neighbors, start_ids, in_grads):
+    """Point gradients of the KDE; compute_pdf_grads() of compute_pdf/compute_pdf.cu:206-257."""
+    bandwidth, pts, neighbors, start_ids, d = _pdf_args(bandwidth, pts, neighbors, start_ids)
+    in_grads = _need(in_grads, "in_grads", torch.float32, 1)
+    out = torch.empty_like(pts)
+    with torch.cuda.device(pts.device):
+        _capi.check(_lib.pccnn_compute_pdf_grads(d, int(manifold_dims), _p(bandwidth), pts.shape[0], _p(pts),
+                                                 _p(neighbors), _p(start_ids), _p(in_grads), _p(out), _stream()),
+                    "compute_pdf_grads")
+    return out
+
+
+# ---- Poisson-disk sampling -------------------------------------------------------------------
+def poisson_disk_sampling(sorted_keys, neighbors, start_ids, grid_size):
+    """Selected positions [k, 1] int64 (ascending); poisson_disk_sampling() of
+    poisson_disk_sampling/poisson_disk_sampling.cu:110-196 of the reference."""
+    sorted_keys = _need(sorted_keys, "sorted_keys", torch.int64, 1)
+    neighbors = _need(neighbors, "neighbors", torch.int32, 2)
+    start_ids = _need(start_ids, "start_ids", torch.int32, 1)
+    grid_size = _need(grid_size, "grid_size", torch.int32, 1)
+    n = sorted_keys.shape[0]
+    d = grid_size.numel()
+    selected = torch.empty((n,), dtype=torch.int64, device=sorted_keys.device)
+    count = ctypes.c_int64(0)
+    with torch.cuda.device(sorted_keys.device):
+        ws = _workspace(_lib.pccnn_poisson_disk_sampling_workspace_bytes(n), sorted_keys.device)
+        _capi.check(_lib.pccnn_poisson_disk_sampling(d, n, _p(sorted_keys), _p(neighbors), _p(start_ids),
+                                                     _p(grid_size), _p(selected), ctypes.byref(count),
+                                                     ws.data_ptr(), ws.numel(), _stream()),
+                    "poisson_disk_sampling")
+    return selected[:count.value].reshape(-1, 1)

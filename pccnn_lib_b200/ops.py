@@ -136,15 +136,15 @@ def build_grid_ds(keys, grid_size, out_shape):
 
 
 # ---- neighbor search -------------------------------------------------------------------------
-def find_neighbors(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii, max_neighbors,
-                   pt_index_map=None):
-    """Radius search -> [neighbors [T, 2] int32, start_ids [M] int32 (inclusive ends)].
+class _NeighborSearch(object):
+    """State carried from the count call to the store call of one neighbor search."""
+    __slots__ = ("common", "start_ids", "total", "workspace", "device", "pt_index_map", "keep")
 
-    find_neighbors() of find_neighbors/find_neighbors.cu:27-66 of the reference.  `pts` and
-    `pt_keys` are in sorted order; row.x indexes that array unless `pt_index_map` (an
-    extension: the sorted_ids permutation) is given, in which case row.x is mapped through it
-    as pccnn_lib/pc/Neighborhood.py:47-53 does afterwards.
-    """
+
+def find_neighbors_count(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii, max_neighbors,
+                         pt_index_map=None):
+    """First half of find_neighbors: counts, scans and learns T (one host synchronisation).
+    Returns the state object to hand to find_neighbors_store."""
     pts = _need(pts, "pts", torch.float32, 2)
     pt_keys = _need(pt_keys, "pt_keys", torch.int64, 1)
     samples = _need(samples, "samples", torch.float32, 2)
@@ -160,21 +160,44 @@ def find_neighbors(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii
     n, m = pts.shape[0], samples.shape[0]
     if pt_keys.shape[0] != n or sample_keys.shape[0] != m:
         raise RuntimeError("keys and coordinates disagree on the number of rows")
-    max_neighbors = int(max_neighbors)
-    start_ids = torch.empty((m,), dtype=torch.int32, device=pts.device)
+    st = _NeighborSearch()
+    st.device = pts.device
+    st.pt_index_map = pt_index_map
+    st.keep = (pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii)  # keep the inputs alive
+    st.start_ids = torch.empty((m,), dtype=torch.int32, device=pts.device)
     total = ctypes.c_int64(0)
     with torch.cuda.device(pts.device):
-        nbytes = _lib.pccnn_find_neighbors_workspace_bytes(d, m)
-        ws = _workspace(nbytes, pts.device)
-        common = (d, n, _p(pts), _p(pt_keys), m, _p(samples), _p(sample_keys), _p(grid_ds), _p(grid_size),
-                  _p(radii), max_neighbors)
-        _capi.check(_lib.pccnn_find_neighbors_count(*common, _p(start_ids), ctypes.byref(total), ws.data_ptr(),
-                                                    ws.numel(), _stream()), "find_neighbors (count)")
-        neighbors = torch.empty((total.value, 2), dtype=torch.int32, device=pts.device)
-        _capi.check(_lib.pccnn_find_neighbors_store(*common, _p(start_ids), _p(pt_index_map), _p(neighbors),
-                                                    ws.data_ptr(), ws.numel(), _stream()),
+        st.workspace = _workspace(_lib.pccnn_find_neighbors_workspace_bytes(d, m), pts.device)
+        st.common = (d, n, _p(pts), _p(pt_keys), m, _p(samples), _p(sample_keys), _p(grid_ds), _p(grid_size),
+                     _p(radii), int(max_neighbors))
+        _capi.check(_lib.pccnn_find_neighbors_count(*st.common, _p(st.start_ids), ctypes.byref(total),
+                                                    st.workspace.data_ptr(), st.workspace.numel(), _stream()),
+                    "find_neighbors (count)")
+    st.total = total.value
+    return st
+
+
+def find_neighbors_store(st):
+    """Second half of find_neighbors: allocates the [T, 2] list and fills it."""
+    neighbors = torch.empty((st.total, 2), dtype=torch.int32, device=st.device)
+    with torch.cuda.device(st.device):
+        _capi.check(_lib.pccnn_find_neighbors_store(*st.common, _p(st.start_ids), _p(st.pt_index_map), _p(neighbors),
+                                                    st.workspace.data_ptr(), st.workspace.numel(), _stream()),
                     "find_neighbors (store)")
-    return [neighbors, start_ids]
+    return [neighbors, st.start_ids]
+
+
+def find_neighbors(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii, max_neighbors,
+                   pt_index_map=None):
+    """Radius search -> [neighbors [T, 2] int32, start_ids [M] int32 (inclusive ends)].
+
+    find_neighbors() of find_neighbors/find_neighbors.cu:27-66 of the reference.  `pts` and
+    `pt_keys` are in sorted order; row.x indexes that array unless `pt_index_map` (an
+    extension: the sorted_ids permutation) is given, in which case row.x is mapped through it
+    as pccnn_lib/pc/Neighborhood.py:47-53 does afterwards.
+    """
+    return find_neighbors_store(find_neighbors_count(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii,
+                                                     max_neighbors, pt_index_map))
 
 
 # ---- kernel density estimation ---------------------------------------------------------------

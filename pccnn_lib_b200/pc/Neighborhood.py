@@ -1,0 +1,32 @@
+import torch
+
+from .. import ops
+from ..op_wrappers import ComputeKeys
+
+
+class Neighborhood(object):
+    """Radius neighborhood of every sample in the points of a grid
+    (pccnn_lib/pc/Neighborhood.py:10-53 of the reference).
+
+    ``neighbors_`` [T, 2] int32 rows (ORIGINAL point index, sample index), grouped by sample,
+    ascending sorted position inside a sample; ``start_ids_`` [M] int32 inclusive end offsets.
+    The search radius is the grid's cell size.  The mapping from sorted positions back to
+    original indices happens inside the search kernel.
+    """
+
+    def __init__(self, p_grid, p_samples, p_max_neighbors=0):
+        self.grid_ = p_grid
+        self.samples_ = p_samples
+        with torch.no_grad():
+            grid = self.grid_
+            if grid.grid_ds_ is None:
+                grid.compute_cell_ids()
+                grid.build_ds()
+            sample_cell_ids = ComputeKeys.apply(self.samples_.pts_.detach(), self.samples_.batch_ids_,
+                                                grid.bounding_box_.min_, grid.num_cells_, grid.cell_size_)
+            self.neighbors_, self.start_ids_ = ops.find_neighbors(
+                grid.sorted_pts_, grid.sorted_cell_ids_, self.samples_.pts_.detach(), sample_cell_ids,
+                grid.grid_ds_, grid.num_cells_, grid.cell_size_, p_max_neighbors, pt_index_map=grid.sorted_ids_)
+
+    def __repr__(self):
+        return "### Neighbors:\n{}\n### Start indices:\n{}".format(self.neighbors_, self.start_ids_)

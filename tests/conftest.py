@@ -52,7 +52,7 @@ def synthetic_case(seed, batch_size, num_pts, num_dims, ragged=True):
     rs = np.random.RandomState(seed)
     pts, ids = [], []
     for b in range(batch_size):
-        n = int(num_pts * rs.uniform(0.5, 1.0)) if ragged else num_pts
+        n = max(1, int(num_pts * rs.uniform(0.5, 1.0))) if ragged else num_pts
         scale = rs.uniform(0.5, 1.5, size=(1, num_dims))
         pts.append((rs.rand(n, num_dims) * scale + rs.uniform(-1, 1, size=(1, num_dims))).astype(np.float32))
         ids.append(np.full((n,), b, np.int32))

@@ -82,7 +82,7 @@ class ClockSampler(threading.Thread):
     BAD = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20}
     NOTED = {"sw_power_cap": 0x4}
 
-    def __init__(self, device_index, period=0.1):
+    def __init__(self, device_index, period=0.02):
         super().__init__(daemon=True)
         self.period, self.samples, self.reasons, self.max_mhz = period, [], set(), None
         self._stop_evt = threading.Event()
@@ -325,7 +325,7 @@ def run_b200(args):
                 "ms_per_launch_set": round(dom_ms, 4),
                 "stage_ms": {k: round(v * n_sub, 4) for k, v in stage_ms.items()}}
 
-    cpu = cpu_baseline_sample()
+    cpu = None if args.no_cpu else cpu_baseline_sample()
 
     h2d = sum(s["h_pts"].numel() * 4 + s["h_ids"].numel() * 4 for s in subs)
     d2h = sum(s["out_pdf"].numel() * 4 + s["out_ends"].numel() * 4 + s["out_perm"].numel() * 8 for s in subs)
@@ -334,8 +334,8 @@ def run_b200(args):
         "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32+i32/i64",
         "data": "synthetic",
-        "config": {"workload": "neighbor search + KDE: 16 clouds x 100k surface points per GPU, radius 0.05, "
-                               "int32 CSR, fp32 KDE bandwidth 0.01",
+        "config": {"workload": "neighbor search + KDE: %d clouds x 100k surface points per GPU, radius 0.05, "
+                               "int32 CSR, fp32 KDE bandwidth 0.01" % CLOUDS_PER_RANK,
                    "clouds_per_gpu": CLOUDS_PER_RANK, "points_per_cloud": POINTS_PER_CLOUD,
                    "pairs_per_step_per_gpu": t_rank, "neighbors_per_point": t_rank / n_pts,
                    "sub_batches_for_int32_offsets": n_sub, "l2": "inputs larger than L2 (neighbor list)",
@@ -365,14 +365,15 @@ def cpu_step(pts, batch_ids, num_clouds):
     return neigh.shape[0]
 
 
-def cpu_baseline_sample(num_clouds=2):
+def cpu_baseline_sample(num_clouds=None):
+    num_clouds = num_clouds or CLOUDS_PER_RANK
     cores = len(os.sched_getaffinity(0))
     pts, ids = make_batch(0, num_clouds)
     t0 = time.perf_counter()
     pairs = cpu_step(pts, ids, num_clouds)
     dt = time.perf_counter() - t0
     return {"value": pairs / dt, "unit": "pairs/s", "cores": cores, "kind": "port",
-            "sample": "%d of the 16 clouds (%d points, %d pairs) in %.2f s, C + OpenMP restatement"
+            "sample": "one step over %d of the 16 clouds (%d points, %d pairs) in %.2f s, C + OpenMP restatement"
                       % (num_clouds, pts.shape[0], pairs, dt)}
 
 
@@ -382,7 +383,7 @@ def run_reference(args):
     if rank != 0:
         return
     cores = len(os.sched_getaffinity(0))
-    num_clouds = 2
+    num_clouds = 8  # half of the batch per step keeps the default run within a couple of minutes
     pts, ids = make_batch(0, num_clouds)
     for _ in range(max(args.warmup, 1)):
         cpu_step(pts, ids, num_clouds)
@@ -410,10 +411,14 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--clouds", type=int, default=CLOUDS_PER_RANK,
+                    help="clouds per GPU (default: the full workload; smaller values are for profiler captures)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
     args = ap.parse_args()
+    globals()["CLOUDS_PER_RANK"] = args.clouds
     if args.impl == "reference":
         run_reference(args)
     else:

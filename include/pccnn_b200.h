@@ -118,8 +118,14 @@ int pccnn_build_grid_ds(int D, int64_t n, const int64_t* sorted_keys, const int3
  * pccnn_find_neighbors_count writes out_start_ids[num_samples] (inclusive ends) and,
  * after synchronising the stream, *out_total_host = T.  The workspace keeps the raw
  * per-sample counts for the store call and must be passed to it unchanged.
- * Returns PCCNN_ERR_OVERFLOW if T >= 2^31. */
+ * Returns PCCNN_ERR_OVERFLOW if T >= 2^31.
+ *
+ * Workspace: pccnn_find_neighbors_workspace_bytes is the recommended size.  Beyond the fixed
+ * part (pccnn_find_neighbors_min_workspace_bytes) it holds a pool in which the count pass keeps
+ * one bit per tested candidate so that the store pass need not test again; samples whose bits
+ * no longer fit are simply tested twice.  Any size >= the minimum gives the same result. */
 size_t pccnn_find_neighbors_workspace_bytes(int D, int64_t num_samples);
+size_t pccnn_find_neighbors_min_workspace_bytes(int D, int64_t num_samples);
 int pccnn_find_neighbors_count(int D, int64_t num_pts, const float* pts, const int64_t* pt_keys,
                                int64_t num_samples, const float* samples, const int64_t* sample_keys,
                                const int32_t* grid_ds, const int32_t* grid_size, const float* radii,

@@ -57,52 +57,65 @@ __global__ void bbox_init_kernel(int64_t count, int* mn, int* mx) {
     }
 }
 
+constexpr int kBboxItems = 16;  // points per thread
+
 template <int D>
-__global__ void bbox_accum_kernel(int64_t n, const float* __restrict__ pts,
-                                  const int32_t* __restrict__ batch_ids, int64_t num_batches, int* mn,
-                                  int* mx) {
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    // Every warp walks whole rounds so that the shuffles below stay convergent.
-    const int64_t rounds = (n + stride - 1) / stride;
-    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    for (int64_t r = 0; r < rounds; ++r, i += stride) {
-        const bool valid = i < n;
-        int b = valid ? batch_ids[i] : -1;
-        if (b < 0 || b >= num_batches) b = -1;
-        float lo[D], hi[D];
+__device__ __forceinline__ void bbox_flush(int b, const float (&lo)[D], const float (&hi)[D], int* mn, int* mx) {
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+        atomicMin(mn + (int64_t)b * D + d, float_to_ordered(lo[d]));
+        atomicMax(mx + (int64_t)b * D + d, float_to_ordered(hi[d]));
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(256)
+bbox_accum_kernel(int64_t n, const float* __restrict__ pts, const int32_t* __restrict__ batch_ids,
+                  int64_t num_batches, int* mn, int* mx) {
+    // A block owns 256 * kBboxItems consecutive points; a thread strides through them by 256 so
+    // loads stay coalesced.  Clouds are stored contiguously, so a thread almost always sees one
+    // cloud: it keeps a running min/max in registers and only touches memory when the cloud
+    // changes.  Warps that hold a single cloud then reduce with shuffles: one atomic pair per
+    // dimension and warp instead of one per point.
+    const float inf = __int_as_float(0x7f800000);
+    const int64_t base = (int64_t)blockIdx.x * (256 * kBboxItems);
+    int cur = -1;
+    float lo[D], hi[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) { lo[d] = inf; hi[d] = -inf; }
+#pragma unroll 4
+    for (int it = 0; it < kBboxItems; ++it) {
+        const int64_t i = base + it * 256 + threadIdx.x;
+        if (i >= n) break;
+        const int b = batch_ids[i];
+        if (b < 0 || b >= num_batches) continue;
+        if (b != cur) {
+            if (cur >= 0) bbox_flush<D>(cur, lo, hi, mn, mx);
+            cur = b;
+#pragma unroll
+            for (int d = 0; d < D; ++d) { lo[d] = inf; hi[d] = -inf; }
+        }
 #pragma unroll
         for (int d = 0; d < D; ++d) {
-            float v = (b >= 0) ? pts[i * D + d] : 0.f;
-            lo[d] = (b >= 0) ? v : __int_as_float(0x7f800000);
-            hi[d] = (b >= 0) ? v : __int_as_float(0xff800000);
+            const float v = pts[i * D + d];
+            lo[d] = fminf(lo[d], v);
+            hi[d] = fmaxf(hi[d], v);
         }
-        // Clouds are stored contiguously, so almost every warp holds a single cloud: reduce in
-        // the warp and issue one atomic pair per dimension.  Lanes past the end carry +/-inf.
-        const int b0 = __shfl_sync(kFullMask, b, 0);
-        const bool uniform = __all_sync(kFullMask, b == b0 || b < 0) && b0 >= 0;
-        if (uniform) {
+    }
+    const int c0 = __shfl_sync(kFullMask, cur, 0);
+    const bool uniform = __all_sync(kFullMask, cur == c0 || cur < 0) && c0 >= 0;
+    if (uniform) {
 #pragma unroll
-            for (int d = 0; d < D; ++d) {
+        for (int d = 0; d < D; ++d) {
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    lo[d] = fminf(lo[d], __shfl_xor_sync(kFullMask, lo[d], o));
-                    hi[d] = fmaxf(hi[d], __shfl_xor_sync(kFullMask, hi[d], o));
-                }
-            }
-            if (lane_id() == 0) {
-#pragma unroll
-                for (int d = 0; d < D; ++d) {
-                    atomicMin(mn + (int64_t)b0 * D + d, float_to_ordered(lo[d]));
-                    atomicMax(mx + (int64_t)b0 * D + d, float_to_ordered(hi[d]));
-                }
-            }
-        } else if (b >= 0) {
-#pragma unroll
-            for (int d = 0; d < D; ++d) {
-                atomicMin(mn + (int64_t)b * D + d, float_to_ordered(lo[d]));
-                atomicMax(mx + (int64_t)b * D + d, float_to_ordered(hi[d]));
+            for (int o = 16; o > 0; o >>= 1) {
+                lo[d] = fminf(lo[d], __shfl_xor_sync(kFullMask, lo[d], o));
+                hi[d] = fmaxf(hi[d], __shfl_xor_sync(kFullMask, hi[d], o));
             }
         }
+        if (lane_id() == 0) bbox_flush<D>(c0, lo, hi, mn, mx);
+    } else if (cur >= 0) {
+        bbox_flush<D>(cur, lo, hi, mn, mx);
     }
 }
 
@@ -237,7 +250,7 @@ int pccnn_bounding_box(int D, int64_t n, const float* pts, const int32_t* batch_
     bbox_init_kernel<<<cb, 256, 0, s>>>(count, (int*)out_min, (int*)out_max);
     PCCNN_LAUNCH_CHECK();
     if (n > 0) {
-        PCCNN_DISPATCH_DIM(D, (bbox_accum_kernel<DIM><<<grid_for(n, 256, 8), 256, 0, s>>>(
+        PCCNN_DISPATCH_DIM(D, (bbox_accum_kernel<DIM><<<(unsigned)((n + 256 * kBboxItems - 1) / (256 * kBboxItems)), 256, 0, s>>>(
                                   n, pts, batch_ids, num_batches, (int*)out_min, (int*)out_max)));
         PCCNN_LAUNCH_CHECK();
     }

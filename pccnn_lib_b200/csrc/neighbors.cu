@@ -8,13 +8,20 @@
 // correctly rounded, and the largest float below 1 has a square root that still rounds below
 // 1, so the predicate equals `sum < 1.0f`; the kernels test that and skip the square root.
 //
-// Design: one warp per sample.  The lanes first resolve the 3^(D-1) candidate ranges in
-// parallel (cell-range table lookup + binary search for the three consecutive last-dimension
-// cells, which are contiguous in the sorted array), park them in shared memory, then sweep
-// each range 32 candidates at a time with coalesced loads.  __ballot_sync + popc give every
-// hit its rank, so rows come out in ascending point index without atomics and the result is
-// deterministic.  A count pass, a device-wide scan and a store pass replace the reference's
-// three kernels + cumsum; the candidate ranges never travel through HBM.
+// Design.  The reference re-reads every candidate from global memory for every sample, twice
+// (count and store), through three kernels and a [M, 9, 2] range tensor.  Here the samples are
+// visited in cell order (their own order when they are the sorted points themselves, a sorted
+// permutation otherwise), and one warp owns 32 consecutive samples.  Samples of the same cell
+// share their candidate ranges, so the warp resolves the 3^(D-1) ranges once per cell (table
+// lookup + binary search for the three consecutive last-dimension cells, which are contiguous
+// in the sorted array), copies the candidates (coordinates + position) once into its private
+// shared-memory buffer with coalesced loads, and then sweeps that buffer for each of its
+// samples: one conflict-free 16-byte shared load per test instead of three L2 loads.
+// __ballot_sync + popc rank the hits, so rows come out in ascending point index without
+// atomics and the result is deterministic.  A count pass, a device-wide scan and a store pass
+// replace the reference's three kernels + cumsum.  Everything is warp-synchronous: no block
+// barrier, no wait on another warp.
+#include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 
 #include "common.cuh"
@@ -28,9 +35,13 @@ struct Stencil {
     static constexpr int kOffsetDims = (D == 2) ? 2 : D - 1;
     static constexpr int pow3(int e) { return e == 0 ? 1 : 3 * pow3(e - 1); }
     static constexpr int kRanges = pow3(kOffsetDims);
+    // A staged candidate is D coordinates + its position, padded to whole float4s; the float4s
+    // of one candidate live in separate planes so that every shared load has a 16-byte lane stride.
+    static constexpr int kPlanes = (D + 1 + 3) / 4;
+    static constexpr int kSlots = (kPlanes == 1) ? 256 : 96;  // candidates staged per round and warp (multiple of 32)
 };
 
-constexpr int kWarpsPerBlock = 4;
+constexpr int kWarpsPerBlock = 8;
 
 __device__ __forceinline__ int lower_bound_key(const int64_t* __restrict__ keys, int lo, int hi, long long v) {
     while (lo < hi) {
@@ -47,119 +58,318 @@ __device__ __forceinline__ int upper_bound_key(const int64_t* __restrict__ keys,
     return lo;
 }
 
-// Candidate ranges of one sample, ascending in sorted position; computed by the whole warp.
+// Candidate ranges of the cell with key `key`, ascending in sorted position, computed by the
+// whole warp: range starts go to lo[], the exclusive prefix of their lengths to pref[].
+// Returns the number of candidates.
 template <int D>
-__device__ __forceinline__ void resolve_ranges(long long key, const GridDesc<D>& g,
-                                               const int2* __restrict__ grid_ds,
-                                               const int64_t* __restrict__ pt_keys, int num_pts,
-                                               int2* __restrict__ ranges) {
+__device__ __forceinline__ int resolve_ranges(long long key, const GridDesc<D>& g,
+                                              const int2* __restrict__ grid_ds,
+                                              const int64_t* __restrict__ pt_keys, int num_pts,
+                                              int* __restrict__ lo, int* __restrict__ pref) {
     using S = Stencil<D>;
+    const int lane = lane_id();
     int c[D];
     const int b = key_to_cell<D>(key, g, c);
-    for (int o = lane_id(); o < S::kRanges; o += 32) {
+    int carry = 0;
+    for (int o0 = 0; o0 < S::kRanges; o0 += 32) {
+        const int o = o0 + lane;
         int2 r = make_int2(0, 0);
-        int cc[D];
+        if (o < S::kRanges) {
+            int cc[D];
 #pragma unroll
-        for (int d = 0; d < D; ++d) cc[d] = c[d];
-        int rem = o;
-        bool inside = true;
+            for (int d = 0; d < D; ++d) cc[d] = c[d];
+            int rem = o;
+            bool inside = true;
 #pragma unroll
-        for (int d = S::kOffsetDims - 1; d >= 0; --d) {
-            const int q = rem / 3;
-            cc[d] += rem - q * 3 - 1;
-            rem = q;
-            inside = inside && cc[d] >= 0 && cc[d] < g.nc[d];
-        }
-        if (inside) {
-            const long long ds = ((long long)b * g.nc[0] + cc[0]) * g.nc[1] + cc[1];
-            int2 tube = __ldg(grid_ds + ds);
-            tube.x = max(tube.x, 0);
-            tube.y = min(tube.y, num_pts);
-            if (D == 2) {
-                r = tube;
-            } else if (tube.y > tube.x) {
-                const long long k = cell_key<D>(cc, g, b);
-                const long long klo = k - (c[D - 1] > 0 ? 1 : 0);
-                const long long khi = k + (c[D - 1] < g.nc[D - 1] - 1 ? 1 : 0);
-                r.x = lower_bound_key(pt_keys, tube.x, tube.y, klo);
-                r.y = upper_bound_key(pt_keys, r.x, tube.y, khi);
+            for (int d = S::kOffsetDims - 1; d >= 0; --d) {
+                const int q = rem / 3;
+                cc[d] += rem - q * 3 - 1;
+                rem = q;
+                inside = inside && cc[d] >= 0 && cc[d] < g.nc[d];
+            }
+            if (inside) {
+                const long long ds = ((long long)b * g.nc[0] + cc[0]) * g.nc[1] + cc[1];
+                int2 tube = __ldg(grid_ds + ds);
+                tube.x = max(tube.x, 0);
+                tube.y = min(tube.y, num_pts);
+                if (D == 2) {
+                    r = tube;
+                } else if (tube.y > tube.x) {
+                    const long long k = cell_key<D>(cc, g, b);
+                    const long long klo = k - (c[D - 1] > 0 ? 1 : 0);
+                    const long long khi = k + (c[D - 1] < g.nc[D - 1] - 1 ? 1 : 0);
+                    r.x = lower_bound_key(pt_keys, tube.x, tube.y, klo);
+                    r.y = upper_bound_key(pt_keys, r.x, tube.y, khi);
+                }
             }
         }
-        if (r.y < r.x) r.y = r.x;
-        ranges[o] = r;
-    }
-    __syncwarp();
-}
-
-template <int D>
-__device__ __forceinline__ bool in_radius(const float (&s)[D], const float* __restrict__ p,
-                                          const float (&inv)[D]) {
-    float acc = 0.f;
+        int len = max(r.y - r.x, 0);
+        int incl = len;
 #pragma unroll
-    for (int d = 0; d < D; ++d) {
-        const float v = __fmul_rn(__fsub_rn(s[d], __ldg(p + d)), inv[d]);
-        acc = (d == 0) ? __fmul_rn(v, v) : __fmaf_rn(v, v, acc);
+        for (int s = 1; s < 32; s <<= 1) {
+            const int v = __shfl_up_sync(kFullMask, incl, s);
+            if (lane >= s) incl += v;
+        }
+        if (o < S::kRanges) {
+            lo[o] = r.x;
+            pref[o + 1] = carry + incl;
+        }
+        carry += __shfl_sync(kFullMask, incl, 31);
     }
-    return acc < 1.0f;
+    if (lane == 0) pref[0] = 0;
+    __syncwarp();
+    return carry;
 }
 
 enum : int { kCount = 0, kStore = 1, kStoreLimited = 2 };
+
+constexpr unsigned kNoMask = 0xffffffffu;
+
+// Hit-mask cache.  The count pass keeps the ballot of every 32-candidate group it tests
+// (1 bit per test) in a pool inside the workspace; the store pass then only replays the bits
+// instead of reloading coordinates and repeating the arithmetic.  Space is reserved per run of
+// same-cell samples with one atomic add; a run that no longer fits is marked kNoMask and the
+// store pass recomputes it, so any pool size is correct and a larger one is merely faster.
+struct MaskCache {
+    unsigned* sample_off;             // [M] first mask word of the sample, or kNoMask
+    unsigned* pool;                   // mask words
+    unsigned long long* cursor;       // words handed out so far (count pass)
+    unsigned long long pool_words;
+};
+
+template <int D>
+__device__ __forceinline__ int chunks_per_sample(int num_cand) {
+    using S = Stencil<D>;
+    return (num_cand / S::kSlots) * (S::kSlots / 32) + ((num_cand % S::kSlots) + 31) / 32;
+}
+
+template <int MODE>
+__device__ __forceinline__ void emit_row(int2* __restrict__ out, int base, int rank, int id, int m, int total,
+                                         int max_neighbors) {
+    if (MODE == kStore || total <= max_neighbors) {
+        out[base + rank] = make_int2(id, m);
+    } else {
+        // Even-stride thinning: hit `rank` of `total` is kept iff it starts a new one of the
+        // max_neighbors equal slices of the list.
+        const long long a = (long long)rank * max_neighbors / total;
+        const long long bnext = (long long)(rank + 1) * max_neighbors / total;
+        if (bnext > a) out[base + (int)a] = make_int2(id, m);
+    }
+}
 
 template <int D, int MODE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 neighbors_kernel(int num_pts, const float* __restrict__ pts, const int64_t* __restrict__ pt_keys,
                  int num_samples, const float* __restrict__ samples, const int64_t* __restrict__ sample_keys,
+                 const int32_t* __restrict__ sample_order,  // samples in cell order, or null = identity
                  const int2* __restrict__ grid_ds, const int32_t* __restrict__ grid_size,
                  const float* __restrict__ radii, int max_neighbors,
                  int32_t* __restrict__ counts,             // kCount: out; kStoreLimited: raw counts in
                  const int32_t* __restrict__ start_ids,    // stores: inclusive ends
-                 const int64_t* __restrict__ pt_index_map, int2* __restrict__ out) {
+                 const int64_t* __restrict__ pt_index_map, int2* __restrict__ out, MaskCache cache) {
     using S = Stencil<D>;
-    __shared__ int2 s_ranges[kWarpsPerBlock][S::kRanges];
+    constexpr int kChunks = S::kSlots / 32;
+    __shared__ float4 s_slots[kWarpsPerBlock][S::kPlanes * S::kSlots];
+    __shared__ int s_lo[kWarpsPerBlock][S::kRanges];
+    __shared__ int s_pref[kWarpsPerBlock][S::kRanges + 1];
     const int warp = threadIdx.x >> 5, lane = lane_id();
     const unsigned lt_mask = (1u << lane) - 1u;
+    float4* slots = s_slots[warp];
+    int* slot_ids = reinterpret_cast<int*>(s_slots[warp]);  // masked store pass: positions only
+    int* lo = s_lo[warp];
+    int* pref = s_pref[warp];
+
+    const int i0 = (blockIdx.x * kWarpsPerBlock + warp) * 32;
+    if (i0 >= num_samples) return;
+    const int n_here = min(32, num_samples - i0);
     const GridDesc<D> g = load_grid<D>(grid_size);
     float inv[D];
 #pragma unroll
     for (int d = 0; d < D; ++d) inv[d] = __frcp_rn(__ldg(radii + d));
 
-    const int warps_total = gridDim.x * kWarpsPerBlock;
-    for (int m = blockIdx.x * kWarpsPerBlock + warp; m < num_samples; m += warps_total) {
-        resolve_ranges<D>(__ldg(sample_keys + m), g, grid_ds, pt_keys, num_pts, s_ranges[warp]);
-        float s[D];
+    // Lane k owns the k-th sample of this warp's tile.
+    int my_sample = -1, my_found = 0, my_base = 0, my_total = 0;
+    unsigned my_mask = kNoMask;
+    long long my_key = -1;
+    float my_s[D];
 #pragma unroll
-        for (int d = 0; d < D; ++d) s[d] = __ldg(samples + (int64_t)m * D + d);
+    for (int d = 0; d < D; ++d) my_s[d] = 0.f;
+    if (lane < n_here) {
+        my_sample = sample_order ? __ldg(sample_order + i0 + lane) : i0 + lane;
+        my_key = __ldg(sample_keys + my_sample);
+#pragma unroll
+        for (int d = 0; d < D; ++d) my_s[d] = __ldg(samples + (int64_t)my_sample * D + d);
+        if (MODE != kCount) {
+            my_base = (my_sample > 0) ? __ldg(start_ids + my_sample - 1) : 0;
+            my_mask = cache.sample_off[my_sample];
+        }
+        if (MODE == kStoreLimited) my_total = __ldg(counts + my_sample);
+    }
 
-        int found = 0;
-        int base = 0, total = 0;
-        if (MODE != kCount) base = (m > 0) ? __ldg(start_ids + m - 1) : 0;
-        if (MODE == kStoreLimited) total = __ldg(counts + m);
-        const bool thin = (MODE == kStoreLimited) && total > max_neighbors;
+    int k0 = 0;
+    while (k0 < n_here) {
+        // Run of samples [k0, k1) that share the cell of sample k0.
+        const long long key0 = __shfl_sync(kFullMask, my_key, k0);
+        const unsigned same = __ballot_sync(kFullMask, lane < n_here && my_key == key0) >> k0;
+        const int k1 = k0 + (same == 0xffffffffu ? 32 : __ffs(~same) - 1);
+        const int num_cand = resolve_ranges<D>(key0, g, grid_ds, pt_keys, num_pts, lo, pref);
+        const int cps = chunks_per_sample<D>(num_cand);
 
-        for (int r = 0; r < S::kRanges; ++r) {
-            const int2 rg = s_ranges[warp][r];
-            for (int j0 = rg.x; j0 < rg.y; j0 += 32) {
-                const int j = j0 + lane;
-                const bool hit = (j < rg.y) && in_radius<D>(s, pts + (int64_t)j * D, inv);
-                const unsigned bal = __ballot_sync(kFullMask, hit);
-                if (MODE != kCount && hit) {
-                    const int rank = found + __popc(bal & lt_mask);
-                    const int id = pt_index_map ? (int)__ldg(pt_index_map + j) : j;
-                    if (!thin) {
-                        out[base + rank] = make_int2(id, m);
-                    } else {
-                        // Even-stride thinning: hit `rank` of `total` is kept iff it starts a new
-                        // one of the max_neighbors equal slices of the list.
-                        const long long a = (long long)rank * max_neighbors / total;
-                        const long long bnext = (long long)(rank + 1) * max_neighbors / total;
-                        if (bnext > a) out[base + (int)a] = make_int2(id, m);
+        // Mask space of this run.
+        unsigned run_mask = kNoMask;
+        if (MODE == kCount) {
+            unsigned long long got = 0;
+            const unsigned long long need = (unsigned long long)(k1 - k0) * cps;
+            if (lane == 0) got = atomicAdd(cache.cursor, need);
+            got = __shfl_sync(kFullMask, got, 0);
+            if (got + need <= cache.pool_words) run_mask = (unsigned)got;
+            if (lane >= k0 && lane < k1 && run_mask != kNoMask) my_mask = run_mask + (unsigned)(lane - k0) * cps;
+        } else {
+            run_mask = __shfl_sync(kFullMask, my_mask, k0);
+        }
+        const bool replay = (MODE != kCount) && run_mask != kNoMask;
+
+        int r = 0;  // range that holds this lane's next candidate; only ever moves forward
+        for (int round0 = 0; round0 < num_cand; round0 += S::kSlots) {
+            const int n_slots = min(S::kSlots, num_cand - round0);
+            const int n_padded = (n_slots + 31) & ~31;
+            const int n_chunks = n_padded >> 5;
+            const int chunk_base = (round0 / S::kSlots) * kChunks;
+            // Stage: consecutive lanes take consecutive candidates (contiguous in memory inside a
+            // range).  The last 32-group is padded with candidates at +inf, which never pass the
+            // test, so the sweep below needs no bounds check.  A replaying store pass only needs
+            // the positions.
+            for (int sl = lane; sl < n_padded; sl += 32) {
+                float w[4 * S::kPlanes];
+#pragma unroll
+                for (int d = 0; d < 4 * S::kPlanes; ++d) w[d] = __int_as_float(0x7f800000);
+                int j = 0;
+                if (sl < n_slots) {
+                    const int gidx = round0 + sl;
+                    while (gidx >= pref[r + 1]) ++r;
+                    j = lo[r] + gidx - pref[r];
+                    if (!replay) {
+#pragma unroll
+                        for (int d = 0; d < D; ++d) w[d] = __ldg(pts + (int64_t)j * D + d);
+                        w[D] = __int_as_float(j);
                     }
                 }
-                found += __popc(bal);
+                if (replay) {
+                    slot_ids[sl] = j;
+                } else {
+#pragma unroll
+                    for (int q = 0; q < S::kPlanes; ++q)
+                        slots[q * S::kSlots + sl] = make_float4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                }
             }
+            __syncwarp();
+
+            if (replay) {
+                // Store pass, bits known.  One load fetches the mask words of kReplay samples
+                // (lane = sample-in-group * kChunks + group-of-32 index), and the load for the next
+                // samples is issued before the current ones are replayed, so the memory latency
+                // is paid once per run instead of once per sample.
+                constexpr int kReplay = (32 / kChunks) < 8 ? (32 / kChunks) : 8;
+                const int sub = lane / kChunks, cidx = lane - sub * kChunks;
+                auto load_words = [&](int k) -> unsigned {
+                    const int kk = k + sub;
+                    const unsigned off = __shfl_sync(kFullMask, my_mask, min(kk, 31));
+                    const bool want = sub < kReplay && kk < k1 && cidx < n_chunks;
+                    return want ? __ldcs(cache.pool + off + chunk_base + cidx) : 0u;
+                };
+                unsigned words = load_words(k0);
+                for (int k = k0; k < k1; k += kReplay) {
+                    const unsigned cur = words;
+                    if (k + kReplay < k1) words = load_words(k + kReplay);
+                    const int n_sub = min(kReplay, k1 - k);
+                    for (int gi = 0; gi < n_sub; ++gi) {
+                        const int kk = k + gi;
+                        int found = __shfl_sync(kFullMask, my_found, kk);
+                        const int m = __shfl_sync(kFullMask, my_sample, kk);
+                        const int base = __shfl_sync(kFullMask, my_base, kk);
+                        const int total = (MODE == kStoreLimited) ? __shfl_sync(kFullMask, my_total, kk) : 0;
+                        for (int ci = 0; ci < n_chunks; ++ci) {
+                            const unsigned bal = __shfl_sync(kFullMask, cur, gi * kChunks + ci);
+                            if (bal == 0u) continue;
+                            if ((bal >> lane) & 1u) {
+                                const int j = slot_ids[ci * 32 + lane];
+                                const int id = pt_index_map ? (int)__ldg(pt_index_map + j) : j;
+                                emit_row<MODE>(out, base, found + __popc(bal & lt_mask), id, m, total, max_neighbors);
+                            }
+                            found += __popc(bal);
+                        }
+                        if (lane == kk) my_found = found;
+                    }
+                }
+            } else {
+                // Sweep with arithmetic: kGroup samples share every candidate load.
+                constexpr int kGroup = (MODE == kCount) ? 4 : 2;
+                for (int k = k0; k < k1; k += kGroup) {
+                    float s[kGroup][D];
+                    int found[kGroup], m[kGroup], base[kGroup], total[kGroup];
+                    unsigned word[kGroup];
+#pragma unroll
+                    for (int gi = 0; gi < kGroup; ++gi) {
+                        const int kk = min(k + gi, k1 - 1);  // the tail of a run repeats its last sample
+#pragma unroll
+                        for (int d = 0; d < D; ++d) s[gi][d] = __shfl_sync(kFullMask, my_s[d], kk);
+                        found[gi] = (MODE == kCount) ? 0 : __shfl_sync(kFullMask, my_found, kk);
+                        m[gi] = (MODE == kCount) ? 0 : __shfl_sync(kFullMask, my_sample, kk);
+                        base[gi] = (MODE == kCount) ? 0 : __shfl_sync(kFullMask, my_base, kk);
+                        total[gi] = (MODE == kStoreLimited) ? __shfl_sync(kFullMask, my_total, kk) : 0;
+                        word[gi] = 0u;
+                    }
+                    for (int ci = 0; ci < n_chunks; ++ci) {
+                        float w[4 * S::kPlanes];
+#pragma unroll
+                        for (int q = 0; q < S::kPlanes; ++q) {
+                            const float4 v = slots[q * S::kSlots + ci * 32 + lane];
+                            w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
+                        }
+#pragma unroll
+                        for (int gi = 0; gi < kGroup; ++gi) {
+                            float acc = 0.f;
+#pragma unroll
+                            for (int d = 0; d < D; ++d) {
+                                const float v = __fmul_rn(__fsub_rn(s[gi][d], w[d]), inv[d]);
+                                acc = (d == 0) ? __fmul_rn(v, v) : __fmaf_rn(v, v, acc);
+                            }
+                            const bool hit = acc < 1.0f;
+                            const unsigned bal = __ballot_sync(kFullMask, hit);
+                            if (MODE == kCount) {
+                                if (lane == ci) word[gi] = bal;  // lane ci keeps the bits of group ci
+                            } else {
+                                if (hit && (gi == 0 || k + gi < k1)) {
+                                    const int j = __float_as_int(w[D]);
+                                    const int id = pt_index_map ? (int)__ldg(pt_index_map + j) : j;
+                                    emit_row<MODE>(out, base[gi], found[gi] + __popc(bal & lt_mask), id, m[gi],
+                                                   total[gi], max_neighbors);
+                                }
+                                found[gi] += __popc(bal);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int gi = 0; gi < kGroup; ++gi) {
+                        const bool live = k + gi < k1;
+                        if (MODE == kCount) {
+                            const int sum = __reduce_add_sync(kFullMask, __popc(word[gi]));
+                            if (lane == k + gi && live) my_found += sum;
+                            if (run_mask != kNoMask && live && lane < n_chunks)
+                                cache.pool[run_mask + (unsigned)(k + gi - k0) * cps + chunk_base + lane] = word[gi];
+                        } else if (lane == k + gi && live) {
+                            my_found = found[gi];
+                        }
+                    }
+                }
+            }
+            __syncwarp();  // everyone is done with the buffer before the next round overwrites it
         }
-        if (MODE == kCount && lane == 0) counts[m] = found;
-        __syncwarp();
+        k0 = k1;
+    }
+    if (MODE == kCount && lane < n_here) {
+        counts[my_sample] = my_found;
+        cache.sample_off[my_sample] = my_mask;
     }
 }
 
@@ -178,20 +388,38 @@ __global__ void clamp_counts_kernel(int n, const int32_t* __restrict__ counts, i
     if (lane_id() == 0 && local) atomicAdd(total, local);
 }
 
+__global__ void iota32_kernel(int n, int32_t* out) {
+    const int stride = gridDim.x * blockDim.x;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = i;
+}
+
 struct NeighborLayout {
-    size_t counts_off, total_off, cub_off, cub_bytes, total;
+    size_t counts_off, total_off, order_off, iota_off, keys_off, cub_off, cub_bytes, mask_off_off, pool_off, total;
 };
+
+// Hit-mask pool requested by default: 256 bytes (2048 tested candidates) per sample.
+constexpr size_t kMaskBytesPerSample = 256;
 
 static NeighborLayout neighbor_layout(int64_t m) {
     NeighborLayout L;
-    size_t cub_bytes = 0;
-    cub::DeviceScan::InclusiveSum(nullptr, cub_bytes, (const int32_t*)nullptr, (int32_t*)nullptr,
-                                  (int)(m > 0 ? m : 1));
+    const int mm = (int)(m > 0 ? m : 1);
+    size_t scan_bytes = 0, sort_bytes = 0;
+    cub::DeviceScan::InclusiveSum(nullptr, scan_bytes, (const int32_t*)nullptr, (int32_t*)nullptr, mm);
+    cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, (const int64_t*)nullptr, (int64_t*)nullptr,
+                                    (const int32_t*)nullptr, (int32_t*)nullptr, mm, 0, 64);
+    L.cub_bytes = scan_bytes > sort_bytes ? scan_bytes : sort_bytes;
     L.counts_off = 0;
     L.total_off = align_up((size_t)m * 4);
-    L.cub_off = L.total_off + 256;
-    L.cub_bytes = cub_bytes;
-    L.total = L.cub_off + align_up(cub_bytes) + 256;
+    L.order_off = L.total_off + 256;
+    L.iota_off = L.order_off + align_up((size_t)m * 4);
+    L.keys_off = L.iota_off + align_up((size_t)m * 4);
+    L.cub_off = L.keys_off + align_up((size_t)m * 8);
+    L.mask_off_off = L.cub_off + align_up(L.cub_bytes) + 256;
+    L.pool_off = L.mask_off_off + align_up((size_t)m * 4);
+    size_t pool = (size_t)m * kMaskBytesPerSample;
+    if (pool < (1u << 20)) pool = 1u << 20;
+    if (pool > ((size_t)8 << 30)) pool = (size_t)8 << 30;
+    L.total = L.pool_off + pool;
     return L;
 }
 
@@ -204,6 +432,28 @@ static int check_common(const char* who, int D, int64_t num_pts, int64_t num_sam
     return PCCNN_OK;
 }
 
+// Samples that ARE the sorted points (same arrays) are already in cell order.
+static bool samples_are_sorted_points(const float* pts, const int64_t* pt_keys, const float* samples,
+                                      const int64_t* sample_keys) {
+    return samples == pts && sample_keys == pt_keys;
+}
+
+// The pool is whatever the caller's workspace holds beyond the fixed part.
+static MaskCache mask_cache(char* ws, const NeighborLayout& L, size_t workspace_bytes) {
+    MaskCache c;
+    c.sample_off = (unsigned*)(ws + L.mask_off_off);
+    c.pool = (unsigned*)(ws + L.pool_off);
+    c.cursor = (unsigned long long*)(ws + L.total_off + 8);
+    size_t words = workspace_bytes > L.pool_off ? (workspace_bytes - L.pool_off) / 4 : 0;
+    if (words > 0xfffffff0ull) words = 0xfffffff0ull;
+    c.pool_words = words;
+    return c;
+}
+
+static unsigned neighbor_grid(int64_t num_samples) {
+    return (unsigned)((num_samples + kWarpsPerBlock * 32 - 1) / (kWarpsPerBlock * 32));
+}
+
 }  // namespace pccnn
 
 using namespace pccnn;
@@ -213,6 +463,11 @@ extern "C" {
 size_t pccnn_find_neighbors_workspace_bytes(int D, int64_t num_samples) {
     (void)D;
     return neighbor_layout(num_samples < 0 ? 0 : num_samples).total;
+}
+
+size_t pccnn_find_neighbors_min_workspace_bytes(int D, int64_t num_samples) {
+    (void)D;
+    return neighbor_layout(num_samples < 0 ? 0 : num_samples).pool_off;
 }
 
 int pccnn_find_neighbors_count(int D, int64_t num_pts, const float* pts, const int64_t* pt_keys,
@@ -229,27 +484,37 @@ int pccnn_find_neighbors_count(int D, int64_t num_pts, const float* pts, const i
                     "find_neighbors_count: null pointer");
     PCCNN_CHECK_ARG(num_pts == 0 || (pts && pt_keys), "find_neighbors_count: null points");
     const NeighborLayout L = neighbor_layout(num_samples);
-    if (!workspace || workspace_bytes < L.total) {
-        set_error("find_neighbors_count: workspace of %zu bytes, need %zu", workspace_bytes, L.total);
+    if (!workspace || workspace_bytes < L.pool_off) {
+        set_error("find_neighbors_count: workspace of %zu bytes, need at least %zu", workspace_bytes, L.pool_off);
         return PCCNN_ERR_WORKSPACE;
     }
     cudaStream_t s = (cudaStream_t)stream;
     char* ws = (char*)workspace;
     int32_t* counts = (int32_t*)(ws + L.counts_off);
     unsigned long long* total_dev = (unsigned long long*)(ws + L.total_off);
-    PCCNN_CUDA(cudaMemsetAsync(total_dev, 0, 8, s));
-    const unsigned grid = grid_for(num_samples * 32, kWarpsPerBlock * 32, 16);
-    PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kCount><<<grid, kWarpsPerBlock * 32, 0, s>>>(
-                              (int)num_pts, pts, pt_keys, (int)num_samples, samples, sample_keys,
-                              (const int2*)grid_ds, grid_size, radii, max_neighbors, counts, nullptr, nullptr,
-                              nullptr)));
+    const int m = (int)num_samples;
+    PCCNN_CUDA(cudaMemsetAsync(total_dev, 0, 16, s));  // pair total + mask cursor
+    const MaskCache cache = mask_cache(ws, L, workspace_bytes);
+
+    const int32_t* order = nullptr;
+    if (!samples_are_sorted_points(pts, pt_keys, samples, sample_keys)) {
+        // Visit the samples in cell order: stable sort of (key, index).
+        int32_t* iota = (int32_t*)(ws + L.iota_off);
+        iota32_kernel<<<grid_for(m, 256, 8), 256, 0, s>>>(m, iota);
+        PCCNN_LAUNCH_CHECK();
+        size_t cub_bytes = L.cub_bytes;
+        PCCNN_CUDA(cub::DeviceRadixSort::SortPairs(ws + L.cub_off, cub_bytes, sample_keys, (int64_t*)(ws + L.keys_off),
+                                                   (const int32_t*)iota, (int32_t*)(ws + L.order_off), m, 0, 64, s));
+        order = (const int32_t*)(ws + L.order_off);
+    }
+    PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kCount><<<neighbor_grid(m), kWarpsPerBlock * 32, 0, s>>>(
+                              (int)num_pts, pts, pt_keys, m, samples, sample_keys, order, (const int2*)grid_ds,
+                              grid_size, radii, max_neighbors, counts, nullptr, nullptr, nullptr, cache)));
     PCCNN_LAUNCH_CHECK();
-    clamp_counts_kernel<<<grid_for(num_samples, 256, 8), 256, 0, s>>>((int)num_samples, counts, max_neighbors,
-                                                                     out_start_ids, total_dev);
+    clamp_counts_kernel<<<grid_for(m, 256, 8), 256, 0, s>>>(m, counts, max_neighbors, out_start_ids, total_dev);
     PCCNN_LAUNCH_CHECK();
     size_t cub_bytes = L.cub_bytes;
-    PCCNN_CUDA(cub::DeviceScan::InclusiveSum(ws + L.cub_off, cub_bytes, out_start_ids, out_start_ids,
-                                             (int)num_samples, s));
+    PCCNN_CUDA(cub::DeviceScan::InclusiveSum(ws + L.cub_off, cub_bytes, out_start_ids, out_start_ids, m, s));
     unsigned long long total = 0;
     PCCNN_CUDA(cudaMemcpyAsync(&total, total_dev, 8, cudaMemcpyDeviceToHost, s));
     PCCNN_CUDA(cudaStreamSynchronize(s));
@@ -273,23 +538,27 @@ int pccnn_find_neighbors_store(int D, int64_t num_pts, const float* pts, const i
     PCCNN_CHECK_ARG(pts && pt_keys && samples && sample_keys && grid_ds && grid_size && radii && start_ids,
                     "find_neighbors_store: null pointer");
     const NeighborLayout L = neighbor_layout(num_samples);
-    if (!workspace || workspace_bytes < L.total) {
-        set_error("find_neighbors_store: workspace of %zu bytes, need %zu", workspace_bytes, L.total);
+    if (!workspace || workspace_bytes < L.pool_off) {
+        set_error("find_neighbors_store: workspace of %zu bytes, need at least %zu", workspace_bytes, L.pool_off);
         return PCCNN_ERR_WORKSPACE;
     }
     cudaStream_t s = (cudaStream_t)stream;
-    int32_t* counts = (int32_t*)((char*)workspace + L.counts_off);
-    const unsigned grid = grid_for(num_samples * 32, kWarpsPerBlock * 32, 16);
+    char* ws = (char*)workspace;
+    int32_t* counts = (int32_t*)(ws + L.counts_off);
+    const int32_t* order =
+        samples_are_sorted_points(pts, pt_keys, samples, sample_keys) ? nullptr : (const int32_t*)(ws + L.order_off);
+    const int m = (int)num_samples;
+    const MaskCache cache = mask_cache(ws, L, workspace_bytes);
     if (max_neighbors > 0) {
-        PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kStoreLimited><<<grid, kWarpsPerBlock * 32, 0, s>>>(
-                                  (int)num_pts, pts, pt_keys, (int)num_samples, samples, sample_keys,
-                                  (const int2*)grid_ds, grid_size, radii, max_neighbors, counts, start_ids,
-                                  pt_index_map, (int2*)out_neighbors)));
+        PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kStoreLimited><<<neighbor_grid(m), kWarpsPerBlock * 32, 0, s>>>(
+                                  (int)num_pts, pts, pt_keys, m, samples, sample_keys, order, (const int2*)grid_ds,
+                                  grid_size, radii, max_neighbors, counts, start_ids, pt_index_map,
+                                  (int2*)out_neighbors, cache)));
     } else {
-        PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kStore><<<grid, kWarpsPerBlock * 32, 0, s>>>(
-                                  (int)num_pts, pts, pt_keys, (int)num_samples, samples, sample_keys,
-                                  (const int2*)grid_ds, grid_size, radii, max_neighbors, counts, start_ids,
-                                  pt_index_map, (int2*)out_neighbors)));
+        PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kStore><<<neighbor_grid(m), kWarpsPerBlock * 32, 0, s>>>(
+                                  (int)num_pts, pts, pt_keys, m, samples, sample_keys, order, (const int2*)grid_ds,
+                                  grid_size, radii, max_neighbors, counts, start_ids, pt_index_map,
+                                  (int2*)out_neighbors, cache)));
     }
     PCCNN_LAUNCH_CHECK();
     return PCCNN_OK;

@@ -142,9 +142,11 @@ class _NeighborSearch(object):
 
 
 def find_neighbors_count(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii, max_neighbors,
-                         pt_index_map=None):
+                         pt_index_map=None, workspace_bytes=None):
     """First half of find_neighbors: counts, scans and learns T (one host synchronisation).
-    Returns the state object to hand to find_neighbors_store."""
+    Returns the state object to hand to find_neighbors_store.  `workspace_bytes` overrides the
+    recommended scratch size (never below the library's minimum); a smaller scratch only makes
+    the store pass repeat more distance tests."""
     pts = _need(pts, "pts", torch.float32, 2)
     pt_keys = _need(pt_keys, "pt_keys", torch.int64, 1)
     samples = _need(samples, "samples", torch.float32, 2)
@@ -167,7 +169,10 @@ def find_neighbors_count(pts, pt_keys, samples, sample_keys, grid_ds, grid_size,
     st.start_ids = torch.empty((m,), dtype=torch.int32, device=pts.device)
     total = ctypes.c_int64(0)
     with torch.cuda.device(pts.device):
-        st.workspace = _workspace(_lib.pccnn_find_neighbors_workspace_bytes(d, m), pts.device)
+        nbytes = _lib.pccnn_find_neighbors_workspace_bytes(d, m)
+        if workspace_bytes is not None:
+            nbytes = max(int(workspace_bytes), _lib.pccnn_find_neighbors_min_workspace_bytes(d, m))
+        st.workspace = _workspace(nbytes, pts.device)
         st.common = (d, n, _p(pts), _p(pt_keys), m, _p(samples), _p(sample_keys), _p(grid_ds), _p(grid_size),
                      _p(radii), int(max_neighbors))
         _capi.check(_lib.pccnn_find_neighbors_count(*st.common, _p(st.start_ids), ctypes.byref(total),
@@ -188,7 +193,7 @@ def find_neighbors_store(st):
 
 
 def find_neighbors(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii, max_neighbors,
-                   pt_index_map=None):
+                   pt_index_map=None, workspace_bytes=None):
     """Radius search -> [neighbors [T, 2] int32, start_ids [M] int32 (inclusive ends)].
 
     find_neighbors() of find_neighbors/find_neighbors.cu:27-66 of the reference.  `pts` and
@@ -197,7 +202,7 @@ def find_neighbors(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii
     as pccnn_lib/pc/Neighborhood.py:47-53 does afterwards.
     """
     return find_neighbors_store(find_neighbors_count(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii,
-                                                     max_neighbors, pt_index_map))
+                                                     max_neighbors, pt_index_map, workspace_bytes))
 
 
 # ---- kernel density estimation ---------------------------------------------------------------

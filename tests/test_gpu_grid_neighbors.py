@@ -151,3 +151,21 @@ def test_poisson_disk_selection_is_identical(ref_clouds, batch_size, num_pts, nu
     expect = oracle.poisson_disk_sampling(o["sorted_keys"], on, os_, o["num_cells"])
     assert got.dtype == torch.int64 and got.dim() == 2 and got.shape[1] == 1
     assert np.array_equal(got.cpu().numpy(), expect)
+
+
+@pytest.mark.parametrize("scratch", ["minimum", "partial"])
+@pytest.mark.parametrize("max_neighs", [0, 16])
+def test_neighbor_lists_do_not_depend_on_the_scratch_size(ref_clouds, scratch, max_neighs):
+    # With little scratch the store pass repeats the distance tests instead of replaying the
+    # bits kept by the count pass; with some scratch both paths run in one call.
+    from pccnn_lib_b200 import _capi, ops
+    pts, batch_ids = ref_case(ref_clouds, 16, 1000, 3)
+    cell = np.full((3,), 0.15, np.float32)
+    g = gpu_grid(pts, batch_ids, 16, cell)
+    args = (g["sorted_pts"], g["sorted_keys"], g["sorted_pts"], g["sorted_keys"], g["grid_ds"], g["num_cells"],
+            g["cell"], max_neighs)
+    full_n, full_s = ops.find_neighbors(*args)
+    lo = _capi.lib.pccnn_find_neighbors_min_workspace_bytes(3, pts.shape[0])
+    nbytes = lo if scratch == "minimum" else lo + 40000
+    n, s = ops.find_neighbors(*args, workspace_bytes=nbytes)
+    assert torch.equal(s, full_s) and torch.equal(n, full_n)

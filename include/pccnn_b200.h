@@ -176,6 +176,19 @@ int pccnn_poisson_disk_sampling(int D, int64_t n, const int64_t* sorted_keys, co
                                 int64_t* out_count_host, void* workspace, size_t workspace_bytes,
                                 void* stream);
 
+/* ------------------------------------------------------------------------- */
+/* Dense contraction on the tensor cores                                      */
+/* ------------------------------------------------------------------------- */
+
+/* C[M, N] = A[M, K] * B[N, K]^T, fp32 in and out, row strides lda / ldb / ldc in elements.
+ * Replaces the torch::matmul (cuBLAS SGEMM) calls of pccnn_lib_ops/pcconvs/kpconv.cu:56-57,95-96
+ * and mcconv.cu:64-68,111-120.  split != 0: operands are split into bf16 hi + lo parts and three
+ * tcgen05 passes give fp32-level accuracy (relative error of a product below 2^-16);
+ * split == 0: one bf16 pass.  Synchronises the stream to read the kernel's status word. */
+size_t pccnn_gemm_workspace_bytes(int64_t M, int N, int K);
+int pccnn_gemm_f32(int64_t M, int N, int K, const float* A, int64_t lda, const float* B, int64_t ldb,
+                   float* C, int64_t ldc, int split, void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,396 @@
+// Dense contraction on the 5th-generation tensor cores:  C[M, N] (fp32) = A[M, K] * B[N, K]^T.
+//
+// This is the contraction of the convolutions (out = P * W, pccnn_lib_ops/pcconvs/kpconv.cu:55-59
+// and mcconv.cu:63-70 of phermosilla/pccnn_lib, and dP = g * W^T of kpconv.cu:95-96), which the
+// reference hands to cuBLAS SGEMM.
+//
+// Operands are bf16, K-contiguous ("K-major"), with rows padded to a multiple of 64 elements.
+// fp32 accuracy comes from a split: x = hi + lo with hi = bf16(x), lo = bf16(x - hi), and three
+// tensor-core passes hi*hi + lo*hi + hi*lo accumulated in the same fp32 accumulator; the
+// dropped lo*lo term is below 2^-16 relative.  One pass serves bf16 inputs.
+//
+// Kernel: one CTA per 128 x BN output tile, 128 threads.
+//   warp 0, one lane : TMA producer  -- cp.async.bulk.tensor 2-D loads of 128 x 64 (A) and BN x 64 (B)
+//                      bf16 boxes, 128-byte swizzle, into a 3-stage ring, completion on mbarriers
+//   warp 1, one lane : MMA issuer    -- tcgen05.mma.cta_group::1.kind::f16, four K=16 steps per stage,
+//                      accumulator [128 lanes x BN columns] fp32 in tensor memory; tcgen05.commit
+//                      releases the stage and finally signals the epilogue
+//   all four warps   : epilogue      -- tcgen05.ld 32 lanes x 32 columns per warp and step, plain
+//                      global stores of whole 128-byte row segments
+// Three stages of (16 + BN/8) KB let two CTAs share an SM, so one CTA's epilogue overlaps the
+// other's main loop.  Every wait is bounded: on expiry the kernel records a status word,
+// leaves its loops, releases tensor memory and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "gemm.cuh"
+
+namespace pccnn {
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: false when the barrier did not flip within the iteration limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < (1u << 21); ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes, stored with the
+// 128-byte swizzle TMA produces: 8-row groups are 1024 bytes apart (stride byte offset), the
+// leading byte offset is unused for swizzled K-major tiles, descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);       // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                            // leading byte offset (ignored)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+    d |= (uint64_t)1 << 46;                            // version
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+
+constexpr int kGemmStages = 3;
+constexpr int kGemmBM = 128;
+constexpr int kGemmBK = 64;  // bf16 elements: one 128-byte swizzle row
+
+template <int BN>
+struct GemmSmem {
+    static constexpr int kA = kGemmBM * kGemmBK * 2;
+    static constexpr int kB = BN * kGemmBK * 2;
+    static constexpr int kStage = kA + kB;
+    static constexpr int kBytes = kGemmStages * kStage + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(128)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                 const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                 float* __restrict__ C, int M, int N, int ldc, int k_blocks, int passes, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + kGemmStages * GemmSmem<BN>::kStage);
+    uint64_t* full = bars;                       // [stages] TMA -> MMA
+    uint64_t* empty = bars + kGemmStages;        // [stages] MMA -> TMA
+    uint64_t* acc_ready = bars + 2 * kGemmStages;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kGemmStages + 1);
+    constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;  // power of two >= 32
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * kGemmBM, n0 = blockIdx.y * BN;
+    const int total = k_blocks * passes;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGemmStages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        mbar_init(acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool ok = true;
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer
+        for (int it = 0; it < total && ok; ++it) {
+            const int s = it % kGemmStages, round = it / kGemmStages;
+            if (round > 0) ok = mbar_wait(empty + s, (round - 1) & 1);
+            if (!ok) break;
+            const int pass = it / k_blocks, kb = it - pass * k_blocks;
+            const CUtensorMap* ma = (pass == 1) ? &map_a_lo : &map_a_hi;
+            const CUtensorMap* mb = (pass == 2) ? &map_b_lo : &map_b_hi;
+            uint8_t* sa = smem + s * GemmSmem<BN>::kStage;
+            mbar_expect_tx(full + s, GemmSmem<BN>::kStage);
+            tma_load_2d(sa, ma, full + s, kb * kGemmBK, m0);
+            tma_load_2d(sa + GemmSmem<BN>::kA, mb, full + s, kb * kGemmBK, n0);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer.  Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major.
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                   ((uint32_t)(kGemmBM >> 4) << 24);
+        for (int it = 0; it < total && ok; ++it) {
+            const int s = it % kGemmStages, round = it / kGemmStages;
+            ok = mbar_wait(full + s, round & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * GemmSmem<BN>::kStage);
+            const uint64_t da = umma_desc_k_sw128(sa), db = umma_desc_k_sw128(sa + GemmSmem<BN>::kA);
+#pragma unroll
+            for (int k = 0; k < kGemmBK / 16; ++k) {
+                // 16 bf16 = 32 bytes further along K inside the swizzle row: +2 in 16-byte units.
+                tc_mma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit(empty + s);  // arrives once the MMAs above have finished reading the stage
+        }
+        if (ok) tc_commit(acc_ready);
+    }
+    if (!ok) atomicExch(status, 1);
+
+    // ---- epilogue: all four warps; warp w owns accumulator lanes [32w, 32w + 32).
+    __syncwarp();
+    bool ready = mbar_wait(acc_ready, 0);
+    if (!ready && lane == 0) atomicExch(status, 2);
+    tc_fence_after();
+    if (ready) {
+        const int row = m0 + warp * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+            if (row < M) {
+                float* dst = C + (size_t)row * ldc + n0 + c0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    const int col = n0 + c0 + j;
+                    if (col + 3 < N && ((((uintptr_t)dst) & 15) == 0)) {
+                        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                          __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (col + e < N) dst[j + e] = __uint_as_float(r[j + e]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- fp32 -> (hi, lo) bf16 split with zero padding ------------------------------------------
+__global__ void __launch_bounds__(256)
+split_bf16_kernel(int64_t rows, int cols, const float* __restrict__ src, int64_t ld_src, int ld_dst,
+                  __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
+    const int64_t total = rows * ld_dst;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t r = i / ld_dst;
+        const int c = (int)(i - r * ld_dst);
+        const float v = (c < cols) ? src[r * ld_src + c] : 0.f;
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        hi[i] = h;
+        if (lo) lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+    }
+}
+
+// Transposing variant: dst[c, r] = src[r, c]; dst rows (one per source column) padded to ld_dst.
+__global__ void __launch_bounds__(256)
+split_bf16_transpose_kernel(int rows, int cols, const float* __restrict__ src, int64_t ld_src, int ld_dst,
+                            __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
+    const int64_t total = (int64_t)cols * ld_dst;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t c = i / ld_dst;
+        const int r = (int)(i - c * ld_dst);
+        const float v = (r < rows) ? src[(int64_t)r * ld_src + c] : 0.f;
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        hi[i] = h;
+        if (lo) lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// 2-D bf16 tensor [rows, ld] (ld elements per row, K contiguous), box = box_rows x 64, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return PCCNN_ERR_CUDA;
+    }
+    if (((uintptr_t)base & 15) || (ld % 64)) {
+        set_error("gemm operand must be 16-byte aligned with rows padded to 64 elements (ld = %lld)", (long long)ld);
+        return PCCNN_ERR_INVALID;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)ld, (cuuint64_t)(rows > 0 ? rows : 1)};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with code %d (rows %lld, ld %lld, box %d)", (int)r, (long long)rows,
+                  (long long)ld, box_rows);
+        return PCCNN_ERR_CUDA;
+    }
+    return PCCNN_OK;
+}
+
+template <int BN>
+static int launch_gemm(const GemmOperand& a, const GemmOperand& b, float* C, int64_t M, int N, int K_padded, int ldc,
+                       int* status, cudaStream_t s) {
+    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    const int passes = (a.lo && b.lo) ? 3 : 1;
+    if (int rc = make_map(&ma_hi, a.hi, M, a.ld, kGemmBM)) return rc;
+    if (int rc = make_map(&ma_lo, passes == 3 ? a.lo : a.hi, M, a.ld, kGemmBM)) return rc;
+    if (int rc = make_map(&mb_hi, b.hi, N, b.ld, BN)) return rc;
+    if (int rc = make_map(&mb_lo, passes == 3 ? b.lo : b.hi, N, b.ld, BN)) return rc;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        GemmSmem<BN>::kBytes);
+    });
+    PCCNN_CUDA(attr_err);
+    dim3 grid((unsigned)((M + kGemmBM - 1) / kGemmBM), (unsigned)((N + BN - 1) / BN));
+    gemm_bf16_kernel<BN><<<grid, 128, GemmSmem<BN>::kBytes, s>>>(ma_hi, ma_lo, mb_hi, mb_lo, C, (int)M, N, ldc,
+                                                               K_padded / kGemmBK, passes, status);
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
+int gemm_bf16_nt(const GemmOperand& a, const GemmOperand& b, float* C, int64_t M, int N, int K_padded, int ldc,
+                 int* status, cudaStream_t s) {
+    PCCNN_CHECK_ARG(M >= 0 && M < 0x7fffffffLL && N > 0 && K_padded > 0 && K_padded % kGemmBK == 0,
+                    "gemm: bad shape M=%lld N=%d K=%d", (long long)M, N, K_padded);
+    PCCNN_CHECK_ARG(a.ld >= K_padded && b.ld >= K_padded, "gemm: leading dimensions smaller than K");
+    if (M == 0) return PCCNN_OK;
+    if (N <= 16) return launch_gemm<16>(a, b, C, M, N, K_padded, ldc, status, s);
+    if (N <= 32) return launch_gemm<32>(a, b, C, M, N, K_padded, ldc, status, s);
+    if (N <= 64) return launch_gemm<64>(a, b, C, M, N, K_padded, ldc, status, s);
+    if (N <= 128) return launch_gemm<128>(a, b, C, M, N, K_padded, ldc, status, s);
+    return launch_gemm<256>(a, b, C, M, N, K_padded, ldc, status, s);
+}
+
+int split_bf16(int64_t rows, int cols, const float* src, int64_t ld_src, int ld_dst, void* hi, void* lo,
+               cudaStream_t s) {
+    if (rows == 0) return PCCNN_OK;
+    split_bf16_kernel<<<grid_for(rows * ld_dst, 256, 8), 256, 0, s>>>(rows, cols, src, ld_src, ld_dst,
+                                                                    (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
+int split_bf16_transpose(int rows, int cols, const float* src, int64_t ld_src, int ld_dst, void* hi, void* lo,
+                         cudaStream_t s) {
+    if (rows == 0 || cols == 0) return PCCNN_OK;
+    split_bf16_transpose_kernel<<<grid_for((int64_t)cols * ld_dst, 256, 8), 256, 0, s>>>(
+        rows, cols, src, ld_src, ld_dst, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo);
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
+}  // namespace pccnn
+
+using namespace pccnn;
+
+extern "C" {
+
+size_t pccnn_gemm_workspace_bytes(int64_t M, int N, int K) {
+    const int64_t kp = (K + 63) / 64 * 64;
+    return (size_t)(align_up((size_t)M * kp * 2) * 2 + align_up((size_t)N * kp * 2) * 2 + 256);
+}
+
+int pccnn_gemm_f32(int64_t M, int N, int K, const float* A, int64_t lda, const float* B, int64_t ldb, float* C,
+                   int64_t ldc, int split, void* workspace, size_t workspace_bytes, void* stream) {
+    PCCNN_CHECK_ARG(M >= 0 && N > 0 && K > 0, "gemm_f32: bad shape");
+    if (M == 0) return PCCNN_OK;
+    PCCNN_CHECK_ARG(A && B && C, "gemm_f32: null pointer");
+    if (!workspace || workspace_bytes < pccnn_gemm_workspace_bytes(M, N, K)) {
+        set_error("gemm_f32: workspace of %zu bytes, need %zu", workspace_bytes, pccnn_gemm_workspace_bytes(M, N, K));
+        return PCCNN_ERR_WORKSPACE;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const int kp = (K + 63) / 64 * 64;
+    char* ws = (char*)workspace;
+    const size_t a_bytes = align_up((size_t)M * kp * 2), b_bytes = align_up((size_t)N * kp * 2);
+    GemmOperand a{ws, split ? ws + a_bytes : nullptr, kp};
+    GemmOperand b{ws + 2 * a_bytes, split ? ws + 2 * a_bytes + b_bytes : nullptr, kp};
+    int* status = (int*)(ws + 2 * a_bytes + 2 * b_bytes);
+    PCCNN_CUDA(cudaMemsetAsync(status, 0, 4, s));
+    if (int rc = split_bf16(M, K, A, lda, kp, a.hi, a.lo, s)) return rc;
+    if (int rc = split_bf16(N, K, B, ldb, kp, b.hi, b.lo, s)) return rc;
+    if (int rc = gemm_bf16_nt(a, b, C, M, N, kp, (int)ldc, status, s)) return rc;
+    int host_status = 0;
+    PCCNN_CUDA(cudaMemcpyAsync(&host_status, status, 4, cudaMemcpyDeviceToHost, s));
+    PCCNN_CUDA(cudaStreamSynchronize(s));
+    if (host_status != 0) {
+        set_error("gemm_f32: a bounded wait inside the tensor-core kernel ran out (status %d)", host_status);
+        return PCCNN_ERR_DEVICE;
+    }
+    return PCCNN_OK;
+}
+
+}  // extern "C"

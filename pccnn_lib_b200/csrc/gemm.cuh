@@ -1,0 +1,30 @@
+// Internal interface of the tensor-core contraction (gemm.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pccnn {
+
+// A bf16 matrix with K contiguous, rows padded with zeros to `ld` elements (a multiple of 64),
+// optionally split into hi + lo parts for fp32 accuracy.
+struct GemmOperand {
+    void* hi;
+    void* lo;  // null: single bf16 pass
+    int64_t ld;
+};
+
+// C[M, N] (fp32, row stride ldc) = A[M, K] * B[N, K]^T.  Three passes when both operands carry a
+// lo part, one otherwise.  `status` is a device int the kernel sets non-zero if a bounded wait
+// ran out.
+int gemm_bf16_nt(const GemmOperand& a, const GemmOperand& b, float* C, int64_t M, int N, int K_padded, int ldc,
+                 int* status, cudaStream_t s);
+
+// hi = bf16(src), lo = bf16(src - hi); destination rows padded with zeros to ld_dst.  lo may be null.
+int split_bf16(int64_t rows, int cols, const float* src, int64_t ld_src, int ld_dst, void* hi, void* lo,
+               cudaStream_t s);
+// Same, but writes the transpose: destination row c holds source column c.
+int split_bf16_transpose(int rows, int cols, const float* src, int64_t ld_src, int ld_dst, void* hi, void* lo,
+                         cudaStream_t s);
+
+}  // namespace pccnn

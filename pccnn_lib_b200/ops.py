@@ -262,3 +262,24 @@ def poisson_disk_sampling(sorted_keys, neighbors, start_ids, grid_size):
                                                      ws.data_ptr(), ws.numel(), _stream()),
                     "poisson_disk_sampling")
     return selected[:count.value].reshape(-1, 1)
+
+
+# ---- dense contraction -----------------------------------------------------------------------
+def gemm_f32(a, b, split=True):
+    """a [M, K] @ b[N, K]^T -> [M, N] float32 on the tcgen05 tensor cores (bf16 hi/lo split when
+    `split`, one bf16 pass otherwise).  Stand-in for the torch::matmul calls of the reference's
+    pcconvs/kpconv.cu:56-57 and mcconv.cu:64-68."""
+    a = _need(a, "a", torch.float32, 2)
+    b = _need(b, "b", torch.float32, 2)
+    if a.shape[1] != b.shape[1]:
+        raise RuntimeError("gemm_f32: inner dimensions differ")
+    m, k = a.shape
+    n = b.shape[0]
+    out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    if n == 0 or k == 0:
+        return out.zero_()
+    with torch.cuda.device(a.device):
+        ws = _workspace(_lib.pccnn_gemm_workspace_bytes(m, n, k), a.device)
+        _capi.check(_lib.pccnn_gemm_f32(m, n, k, _p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0),
+                                        1 if split else 0, ws.data_ptr(), ws.numel(), _stream()), "gemm_f32")
+    return out

@@ -177,6 +177,38 @@ int pccnn_poisson_disk_sampling(int D, int64_t n, const int64_t* sorted_keys, co
                                 void* stream);
 
 /* ------------------------------------------------------------------------- */
+/* Point convolutions                                                         */
+/* ------------------------------------------------------------------------- */
+
+/* Shared conventions: feats [num_pts, cin] float32; neighbors / start_ids as produced by the
+ * neighbor search (row.x indexes pts and feats, row.y indexes samples); radii [D] on the device;
+ * out [num_samples, cout] float32.  The contraction runs on the tensor cores with a bf16 hi/lo
+ * split (three passes), which keeps the result within 1e-4 relative of an fp32 evaluation.
+ * Scratch: pccnn_conv_workspace_bytes(num_samples, cin, basis_size, cout). */
+size_t pccnn_conv_workspace_bytes(int64_t num_samples, int cin, int basis_size, int cout);
+
+/* KPConv forward: basis b[t,k] = clamp(1 - |kernel_pts[k] - d_t| / sigma, 0, 1), weights
+ * [num_kernel_pts * cin, cout] with row index c * num_kernel_pts + k.
+ * Replaces kpconv()  pccnn_lib_ops/pcconvs/kpconv.cu:32-60 (stages shared/pt_diff.cu:27-49,
+ * shared/kernel_pts_basis.cu:23-39, shared/feat_basis_proj.cu:133-191).  Any 1 <= num_kernel_pts
+ * <= 64 is accepted (the reference only instantiates 8, 16, 32 and 64). */
+int pccnn_kp_conv(int D, int64_t num_pts, const float* pts, const float* feats, int cin,
+                  int64_t num_samples, const float* samples, const int32_t* neighbors,
+                  const int32_t* start_ids, const float* radii, const float* kernel_pts,
+                  int num_kernel_pts, float sigma, const float* weights, int cout, float* out,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* MCConv forward: basis b[t,:] = leaky_relu_{0.2}(d_t . axis + bias) / pdf[n0(t)], axis [D, hidden],
+ * bias [hidden], weights [num_mlps, hidden / num_mlps * cin, cout / num_mlps] (hidden counts the
+ * units of all MLPs together, as the reference's proj_axis_ does).
+ * Replaces mcconv()  pccnn_lib_ops/pcconvs/mcconv.cu:32-71 (stages shared/mlp_basis.cu:27-48). */
+int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, const float* feats, int cin,
+                  int64_t num_samples, const float* samples, const int32_t* neighbors,
+                  const int32_t* start_ids, const float* radii, const float* axis, const float* bias,
+                  int hidden, int num_mlps, const float* weights, int cout, float* out,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- */
 /* Dense contraction on the tensor cores                                      */
 /* ------------------------------------------------------------------------- */
 

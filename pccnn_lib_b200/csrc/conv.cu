@@ -1,0 +1,312 @@
+// KPConv / MCConv forward: neighbor gather x basis projection, then the tensor-core contraction.
+//
+// Restates pccnn_lib_ops/pcconvs/kpconv.cu:32-60 and mcconv.cu:32-71 of phermosilla/pccnn_lib with
+// their stages pt_diff (shared/pt_diff.cu:27-49), kernel_pts_basis (shared/kernel_pts_basis.cu:23-39),
+// mlp_basis (shared/mlp_basis.cu:27-48) and feat_basis_proj (shared/feat_basis_proj.cu:30-129):
+//     d_t      = (pts[n0(t)] - samples[n1(t)]) * (1 / radii)
+//     b[t, k]  = clamp(1 - |kp_k - d_t| / sigma, 0, 1)                  (KPConv)
+//              = leaky_relu_{0.2}(d_t . A[:, k] + bias[k]) / pdf[n0(t)]  (MCConv)
+//     P[m,c,k] = sum_{t in seg(m)} F[n0(t), c] * b[t, k]
+//     out      = P.reshape(M, Cin*K) @ W
+//
+// Design.  The reference runs ~10 elementwise launches that materialise [T, D], [T, K, D] and
+// [T, K] tensors, then a 64-thread block per (sample, 8 channels) that re-reads the basis row
+// Cin/8 times.  Here one kernel does everything up to P: a warp owns a sample, its lanes first
+// act as 32 neighbors (offset + all K basis values per lane, parked in shared memory), then as
+// 32 channels x CPL, streaming the neighbors' feature rows with coalesced 128-byte loads and
+// broadcasting the basis row from shared memory; CPL * K = 64 fp32 accumulators per lane, so the
+// basis is evaluated once per pair for up to 32 * CPL channels.  P leaves the kernel as bf16
+// hi + lo parts in the layout the contraction's TMA loads expect, and out = P @ W runs on
+// tcgen05 (gemm.cu), in sample chunks so the scratch stays bounded.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "gemm.cuh"
+
+namespace pccnn {
+
+constexpr int kConvWarps = 4;
+
+struct KPBasisArgs {
+    const float* kernel_pts;  // [K, D]
+    float inv_sigma;
+};
+struct MLPBasisArgs {
+    const float* axis;  // [D, H]
+    const float* bias;  // [H]
+    const float* pdf;   // [N]
+};
+
+// Basis functors: eval() fills b[0..K) for one pair given its normalised offset.
+template <int D, int KP>
+struct KPBasis {
+    static constexpr int kParamFloats = KP * D;
+    __device__ static void load_params(float* sp, const KPBasisArgs& a, int K) {
+        for (int i = threadIdx.x; i < KP * D; i += blockDim.x) sp[i] = (i < K * D) ? __ldg(a.kernel_pts + i) : 0.f;
+    }
+    __device__ static void eval(const float* sp, const KPBasisArgs& a, int K, const float (&d)[D], int /*n0*/,
+                                float (&b)[KP]) {
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+            float acc = 0.f;
+#pragma unroll
+            for (int x = 0; x < D; ++x) {
+                const float v = sp[k * D + x] - d[x];
+                acc = fmaf(v, v, acc);
+            }
+            const float val = 1.0f - sqrtf(fmaxf(acc, 0.f)) * a.inv_sigma;
+            b[k] = (k < K) ? fminf(fmaxf(val, 0.f), 1.f) : 0.f;
+        }
+    }
+};
+
+template <int D, int KP>
+struct MLPBasis {
+    static constexpr int kParamFloats = (D + 1) * KP;
+    __device__ static void load_params(float* sp, const MLPBasisArgs& a, int K) {
+        for (int i = threadIdx.x; i < (D + 1) * KP; i += blockDim.x) {
+            const int row = i / KP, k = i - row * KP;
+            float v = 0.f;
+            if (k < K) v = (row < D) ? __ldg(a.axis + row * K + k) : __ldg(a.bias + k);
+            sp[i] = v;
+        }
+    }
+    __device__ static void eval(const float* sp, const MLPBasisArgs& a, int K, const float (&d)[D], int n0,
+                                float (&b)[KP]) {
+        const float inv_pdf = 1.0f / __ldg(a.pdf + n0);
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+            float acc = 0.f;
+#pragma unroll
+            for (int x = 0; x < D; ++x) acc = fmaf(d[x], sp[x * KP + k], acc);
+            acc += sp[D * KP + k];
+            acc = acc > 0.f ? acc : 0.2f * acc;
+            b[k] = (k < K) ? acc * inv_pdf : 0.f;
+        }
+    }
+};
+
+// P[m, c*K + k] for the samples [m_begin, m_end), written as bf16 hi (+ lo) rows of ld_p elements.
+template <int D, int KP, class BASIS, class ARGS>
+__global__ void __launch_bounds__(kConvWarps * 32)
+project_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __restrict__ feats, int cin,
+               const float* __restrict__ samples, const int2* __restrict__ neighbors,
+               const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
+               __nv_bfloat16* __restrict__ p_hi, __nv_bfloat16* __restrict__ p_lo, int ld_p) {
+    constexpr int CPL = 64 / KP;  // channels per lane
+    __shared__ float s_params[BASIS::kParamFloats];
+    __shared__ float s_basis[kConvWarps][32][KP + 1];
+    __shared__ int s_n0[kConvWarps][32];
+    BASIS::load_params(s_params, args, K);
+    __syncthreads();
+
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    float inv[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) inv[d] = __frcp_rn(__ldg(radii + d));
+    const int inner = cin * K;
+
+    for (int m = m_begin + blockIdx.x * kConvWarps + warp; m < m_end; m += gridDim.x * kConvWarps) {
+        const int lo = (m > 0) ? __ldg(start_ids + m - 1) : 0;
+        const int hi = __ldg(start_ids + m);
+        float s[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) s[d] = __ldg(samples + (int64_t)m * D + d);
+        const size_t row = (size_t)(m - m_begin) * ld_p;
+
+        for (int cb = 0; cb < cin; cb += 32 * CPL) {
+            float acc[CPL][KP];
+#pragma unroll
+            for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                for (int k = 0; k < KP; ++k) acc[i][k] = 0.f;
+
+            for (int t0 = lo; t0 < hi; t0 += 32) {
+                // Lanes as neighbors: offset and basis row of pair t0 + lane.
+                const int t = t0 + lane;
+                if (t < hi) {
+                    const int n0 = __ldg(&neighbors[t]).x;
+                    float d[D], b[KP];
+#pragma unroll
+                    for (int x = 0; x < D; ++x) d[x] = (__ldg(pts + (int64_t)n0 * D + x) - s[x]) * inv[x];
+                    BASIS::eval(s_params, args, K, d, n0, b);
+#pragma unroll
+                    for (int k = 0; k < KP; ++k) s_basis[warp][lane][k] = b[k];
+                    s_n0[warp][lane] = n0;
+                }
+                __syncwarp();
+                // Lanes as channels: stream the feature rows of the staged neighbors.
+                const int cnt = min(32, hi - t0);
+                for (int j = 0; j < cnt; ++j) {
+                    const float* frow = feats + (int64_t)s_n0[warp][j] * cin + cb + lane;
+                    float f[CPL];
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) f[i] = (cb + i * 32 + lane < cin) ? __ldg(frow + i * 32) : 0.f;
+#pragma unroll
+                    for (int k = 0; k < KP; ++k) {
+                        const float bk = s_basis[warp][j][k];
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i) acc[i][k] = fmaf(f[i], bk, acc[i][k]);
+                    }
+                }
+                __syncwarp();
+            }
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+                const int c = cb + i * 32 + lane;
+                if (c < cin) {
+#pragma unroll
+                    for (int k = 0; k < KP; ++k) {
+                        if (k < K) {
+                            const float v = acc[i][k];
+                            const __nv_bfloat16 h = __float2bfloat16_rn(v);
+                            p_hi[row + (size_t)c * K + k] = h;
+                            if (p_lo) p_lo[row + (size_t)c * K + k] = __float2bfloat16_rn(v - __bfloat162float(h));
+                        }
+                    }
+                }
+            }
+        }
+        // Padding columns feed the tensor cores too: keep them zero.
+        for (int c = inner + lane; c < ld_p; c += 32) {
+            p_hi[row + c] = __float2bfloat16_rn(0.f);
+            if (p_lo) p_lo[row + c] = __float2bfloat16_rn(0.f);
+        }
+    }
+}
+
+template <int D, class ARGS, template <int, int> class BASIS>
+static int launch_project(int K, const ARGS& args, const float* pts, const float* feats, int cin, const float* samples,
+                          const int32_t* neighbors, const int32_t* start_ids, const float* radii, int m_begin,
+                          int m_end, void* p_hi, void* p_lo, int ld_p, cudaStream_t s) {
+    const int count = m_end - m_begin;
+    if (count <= 0) return PCCNN_OK;
+    const unsigned grid = grid_for((int64_t)count * 32, kConvWarps * 32, 8);
+#define PCCNN_PROJECT(KP)                                                                                        \
+    project_kernel<D, KP, BASIS<D, KP>, ARGS><<<grid, kConvWarps * 32, 0, s>>>(                                   \
+        args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids, radii, m_begin, m_end,             \
+        (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo, ld_p)
+    if (K <= 8) PCCNN_PROJECT(8);
+    else if (K <= 16) PCCNN_PROJECT(16);
+    else if (K <= 32) PCCNN_PROJECT(32);
+    else PCCNN_PROJECT(64);
+#undef PCCNN_PROJECT
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
+// Samples are processed in chunks so that the P scratch stays bounded.
+constexpr int64_t kConvChunk = 1 << 17;
+
+struct ConvLayout {
+    int ld_p;      // padded Cin * K
+    int64_t chunk;
+    size_t p_hi_off, p_lo_off, w_hi_off, w_lo_off, status_off, total;
+};
+
+static ConvLayout conv_layout(int64_t num_samples, int cin, int K, int cout) {
+    ConvLayout L;
+    L.ld_p = (cin * K + 63) / 64 * 64;
+    L.chunk = num_samples < kConvChunk ? (num_samples > 0 ? num_samples : 1) : kConvChunk;
+    const size_t p_bytes = align_up((size_t)L.chunk * L.ld_p * 2);
+    const size_t w_bytes = align_up((size_t)cout * L.ld_p * 2);
+    L.p_hi_off = 0;
+    L.p_lo_off = p_bytes;
+    L.w_hi_off = 2 * p_bytes;
+    L.w_lo_off = L.w_hi_off + w_bytes;
+    L.status_off = L.w_lo_off + w_bytes;
+    L.total = L.status_off + 256;
+    return L;
+}
+
+template <class ARGS, template <int, int> class BASIS>
+static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t num_pts, const float* pts,
+                        const float* feats, int cin, int64_t num_samples, const float* samples,
+                        const int32_t* neighbors, const int32_t* start_ids, const float* radii, int num_mlps,
+                        const float* weights, int cout, float* out, void* workspace, size_t workspace_bytes,
+                        cudaStream_t s) {
+    PCCNN_CHECK_ARG(D >= kMinDims && D <= kMaxDims, "%s: point dimension %d outside [2, 6]", who, D);
+    PCCNN_CHECK_ARG(K >= 1 && K <= 64, "%s: basis size %d outside [1, 64]", who, K);
+    PCCNN_CHECK_ARG(cin >= 1 && cout >= 1 && num_mlps >= 1 && cout % num_mlps == 0 && (cin * K) % num_mlps == 0,
+                    "%s: bad channel counts (cin %d, cout %d, mlps %d)", who, cin, cout, num_mlps);
+    PCCNN_CHECK_ARG(num_samples >= 0 && num_samples < 0x7fffffffLL && num_pts >= 0, "%s: bad sizes", who);
+    if (num_samples == 0) return PCCNN_OK;
+    PCCNN_CHECK_ARG(pts && feats && samples && start_ids && radii && weights && out, "%s: null pointer", who);
+    const ConvLayout L = conv_layout(num_samples, cin, K, cout);
+    if (!workspace || workspace_bytes < L.total) {
+        set_error("%s: workspace of %zu bytes, need %zu", who, workspace_bytes, L.total);
+        return PCCNN_ERR_WORKSPACE;
+    }
+    char* ws = (char*)workspace;
+    int* status = (int*)(ws + L.status_off);
+    PCCNN_CUDA(cudaMemsetAsync(status, 0, 4, s));
+
+    // W^T as bf16 hi/lo, K-contiguous.  With several MLPs the weight tensor is [mlps, inner/mlps... ]:
+    // MLP j maps the j-th slice of the flattened (c, k) index to the j-th slice of the outputs
+    // (mcconv.cu:59-68 of the reference reshapes exactly so).
+    const int inner = cin * K, inner_j = inner / num_mlps, cout_j = cout / num_mlps;
+    PCCNN_CUDA(cudaMemsetAsync(ws + L.w_hi_off, 0, L.status_off - L.w_hi_off, s));
+    for (int j = 0; j < num_mlps; ++j) {
+        const size_t off = (size_t)j * cout_j * L.ld_p * 2;
+        if (int rc = split_bf16_transpose(inner_j, cout_j, weights + (size_t)j * inner_j * cout_j, cout_j, L.ld_p,
+                                          ws + L.w_hi_off + off, ws + L.w_lo_off + off, s))
+            return rc;
+    }
+    for (int64_t m0 = 0; m0 < num_samples; m0 += L.chunk) {
+        const int64_t m1 = (m0 + L.chunk < num_samples) ? m0 + L.chunk : num_samples;
+        int rc = PCCNN_OK;
+        PCCNN_DISPATCH_DIM(D, (rc = launch_project<DIM, ARGS, BASIS>(K, args, pts, feats, cin, samples, neighbors,
+                                                                     start_ids, radii, (int)m0, (int)m1,
+                                                                     ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, s)));
+        if (rc) return rc;
+        for (int j = 0; j < num_mlps; ++j) {
+            // Slice j of the P rows (offset j * inner_j, 16-byte aligned because inner_j % 8 == 0 is checked
+            // below) times W_j^T.  Columns read past the slice meet zero weights.
+            const size_t a_off = (size_t)j * inner_j * 2;
+            const size_t b_off = (size_t)j * cout_j * L.ld_p * 2;
+            PCCNN_CHECK_ARG(num_mlps == 1 || inner_j % 64 == 0, "%s: Cin*K per MLP must be a multiple of 64", who);
+            const int kp = num_mlps == 1 ? L.ld_p : inner_j;
+            GemmOperand a{ws + L.p_hi_off + a_off, ws + L.p_lo_off + a_off, L.ld_p};
+            GemmOperand b{ws + L.w_hi_off + b_off, ws + L.w_lo_off + b_off, L.ld_p};
+            if (int rc2 = gemm_bf16_nt(a, b, out + (size_t)m0 * cout + (size_t)j * cout_j, m1 - m0, cout_j, kp, cout,
+                                       status, s))
+                return rc2;
+        }
+    }
+    return PCCNN_OK;
+}
+
+}  // namespace pccnn
+
+using namespace pccnn;
+
+extern "C" {
+
+size_t pccnn_conv_workspace_bytes(int64_t num_samples, int cin, int basis_size, int cout) {
+    return conv_layout(num_samples < 0 ? 0 : num_samples, cin, basis_size, cout).total;
+}
+
+int pccnn_kp_conv(int D, int64_t num_pts, const float* pts, const float* feats, int cin, int64_t num_samples,
+                  const float* samples, const int32_t* neighbors, const int32_t* start_ids, const float* radii,
+                  const float* kernel_pts, int num_kernel_pts, float sigma, const float* weights, int cout,
+                  float* out, void* workspace, size_t workspace_bytes, void* stream) {
+    PCCNN_CHECK_ARG(kernel_pts && sigma > 0.f, "kp_conv: kernel points missing or sigma <= 0");
+    KPBasisArgs args{kernel_pts, 1.0f / sigma};
+    return conv_forward<KPBasisArgs, KPBasis>("kp_conv", D, num_kernel_pts, args, num_pts, pts, feats, cin, num_samples,
+                                              samples, neighbors, start_ids, radii, 1, weights, cout, out, workspace,
+                                              workspace_bytes, (cudaStream_t)stream);
+}
+
+int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, const float* feats, int cin,
+                  int64_t num_samples, const float* samples, const int32_t* neighbors, const int32_t* start_ids,
+                  const float* radii, const float* axis, const float* bias, int hidden, int num_mlps,
+                  const float* weights, int cout, float* out, void* workspace, size_t workspace_bytes,
+                  void* stream) {
+    PCCNN_CHECK_ARG(pdf && axis && bias, "mc_conv: null pointer");
+    MLPBasisArgs args{axis, bias, pdf};
+    return conv_forward<MLPBasisArgs, MLPBasis>("mc_conv", D, hidden, args, num_pts, pts, feats, cin, num_samples,
+                                                samples, neighbors, start_ids, radii, num_mlps, weights, cout, out,
+                                                workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+}  // extern "C"

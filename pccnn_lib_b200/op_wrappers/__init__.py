@@ -5,3 +5,5 @@ from .compute_keys import ComputeKeys
 from .find_neighbors import FindNeighbors
 from .compute_pdf import ComputePDF
 from .poisson_disk_sampling import PoissonDiskSamlping
+from .compute_kpconv import ComputeKPConv
+from .compute_mcconv import ComputeMCConv

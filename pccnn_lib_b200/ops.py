@@ -283,3 +283,61 @@ def gemm_f32(a, b, split=True):
         _capi.check(_lib.pccnn_gemm_f32(m, n, k, _p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0),
                                         1 if split else 0, ws.data_ptr(), ws.numel(), _stream()), "gemm_f32")
     return out
+
+
+# ---- point convolutions ----------------------------------------------------------------------
+def _conv_common(pts, feats, samples, neighbors, start_ids, radii):
+    pts = _need(pts, "pts", torch.float32, 2)
+    feats = _need(feats, "features", torch.float32, 2)
+    samples = _need(samples, "samples", torch.float32, 2)
+    neighbors = _need(neighbors, "neighbors", torch.int32, 2)
+    start_ids = _need(start_ids, "start_ids", torch.int32, 1)
+    radii = _need(radii, "radii", torch.float32, 1)
+    d = _dims(pts)
+    if samples.shape[1] != d or radii.numel() != d:
+        raise RuntimeError("samples and radii must match the point dimension %d" % d)
+    if feats.shape[0] != pts.shape[0]:
+        raise RuntimeError("features need one row per point")
+    if start_ids.shape[0] != samples.shape[0]:
+        raise RuntimeError("start_ids needs one entry per sample")
+    return pts, feats, samples, neighbors, start_ids, radii, d
+
+
+def kp_conv(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights):
+    """KPConv forward -> [M, Cout]; kpconv() of pccnn_lib_ops/pcconvs/kpconv.cu:32-60 of the reference."""
+    pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii)
+    kernel_pts = _need(kernel_pts, "kernel_pts", torch.float32, 2)
+    weights = _need(weights, "weights", torch.float32, 2)
+    k, cin, cout = kernel_pts.shape[0], feats.shape[1], weights.shape[1]
+    if kernel_pts.shape[1] != d or weights.shape[0] != k * cin:
+        raise RuntimeError("kernel_pts must be [K, %d] and weights [K * Cin, Cout]" % d)
+    m = samples.shape[0]
+    out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
+    with torch.cuda.device(pts.device):
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
+        _capi.check(_lib.pccnn_kp_conv(d, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
+                                       _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
+                                       _p(out), ws.data_ptr(), ws.numel(), _stream()), "kp_conv")
+    return out
+
+
+def mc_conv(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_proj, axis_bias, weights):
+    """MCConv forward -> [M, Cout]; mcconv() of pccnn_lib_ops/pcconvs/mcconv.cu:32-71 of the reference."""
+    pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii)
+    pdf = _need(pdf, "pdf", torch.float32, 1)
+    axis_proj = _need(axis_proj, "axis_proj", torch.float32, 2)
+    axis_bias = _need(axis_bias, "axis_bias", torch.float32)
+    weights = _need(weights, "weights", torch.float32, 3)
+    hidden, cin = axis_proj.shape[1], feats.shape[1]
+    n_mlps = weights.shape[0]
+    cout = weights.shape[2] * n_mlps
+    if axis_proj.shape[0] != d or axis_bias.numel() != hidden or weights.shape[1] * n_mlps != hidden * cin:
+        raise RuntimeError("axis_proj must be [%d, H], axis_bias [1, H] and weights [mlps, H * Cin / mlps, Cout / mlps]" % d)
+    m = samples.shape[0]
+    out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
+    with torch.cuda.device(pts.device):
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, hidden, cout), pts.device)
+        _capi.check(_lib.pccnn_mc_conv(d, pts.shape[0], _p(pts), _p(pdf), _p(feats), cin, m, _p(samples), _p(neighbors),
+                                       _p(start_ids), _p(radii), _p(axis_proj), _p(axis_bias), hidden, n_mlps,
+                                       _p(weights), cout, _p(out), ws.data_ptr(), ws.numel(), _stream()), "mc_conv")
+    return out

@@ -1,0 +1,121 @@
+"""Pins the convolution oracle (oracle/conv_oracle.py) to the NumPy expectations of the reference's
+own tests and checks its hand-written backward formulas against finite differences."""
+import numpy as np
+import pytest
+import torch
+
+from conv_helpers import KP_CASES, MC_CASES, kp_case, mc_case
+from oracle import conv_oracle
+
+
+def numpy_projection(case, basis, k):
+    """unit_test/test_kpconv.py:72-79 of the reference: per-pair outer products into [N, Cin, K]."""
+    proj = np.zeros((case["samples"].shape[0], case["feats"].shape[1], k))
+    for t in range(case["neighbors"].shape[0]):
+        n0, n1 = case["neighbors"][t]
+        proj[n1] += case["feats"][n0].reshape(-1, 1) * basis[t].reshape(1, -1)
+    return proj.reshape(case["samples"].shape[0], -1)
+
+
+@pytest.mark.parametrize("c", KP_CASES, ids=lambda c: "d%d_n%d_k%d" % (c["dims"], c["n"], c["k"]))
+def test_kpconv_oracle_matches_reference_numpy(ref_clouds, c):
+    case = kp_case(ref_clouds, c)
+    nb = case["neighbors"]
+    # unit_test/test_kpconv.py:60-82
+    diff = (case["pts"][nb[:, 0]] - case["samples"][nb[:, 1]]) / case["radii"].reshape(1, -1)
+    kd = diff.reshape(-1, 1, c["dims"]) - case["kernel_pts"].reshape(1, -1, c["dims"])
+    basis = np.clip(1.0 - np.linalg.norm(kd, axis=-1) / case["sigma"], 0.0, 1.0)
+    expect = np.dot(numpy_projection(case, basis, c["k"]), case["weights"])
+    got = conv_oracle.kp_conv(case["pts"], case["feats"], case["samples"], nb, case["start_ids"], case["radii"],
+                              case["kernel_pts"], case["sigma"], case["weights"]).numpy()
+    assert np.isclose(expect, got, rtol=1e-4, atol=1e-4).all()
+
+
+@pytest.mark.parametrize("c", MC_CASES, ids=lambda c: "d%d_n%d" % (c["dims"], c["n"]))
+def test_mcconv_oracle_matches_reference_numpy(ref_clouds, c):
+    case = mc_case(ref_clouds, c)
+    nb = case["neighbors"]
+    # unit_test/test_mcconv.py:65-91
+    diff = (case["pts"][nb[:, 0]] - case["samples"][nb[:, 1]]) / case["radii"].reshape(1, -1)
+    proj = np.dot(diff, case["axis"]) + case["bias"]
+    proj = np.where(proj < 0.0, proj * 0.2, proj) / case["pdf"][nb[:, 0]].reshape(-1, 1)
+    expect = np.dot(numpy_projection(case, proj, c["k"]), case["weights"].reshape(c["cin"] * c["k"], -1))
+    got = conv_oracle.mc_conv(case["pts"], case["pdf"], case["feats"], case["samples"], nb, case["start_ids"],
+                              case["radii"], case["axis"], case["bias"], case["weights"]).numpy()
+    assert np.isclose(expect, got, rtol=1e-4, atol=1e-4).all()
+
+
+def _autograd_check(fn, args, names, in_grads, analytic, tie=None):
+    """Gradients of sum(out * in_grads) from torch autograd of the float64 forward against the
+    hand-written backward.  Entries where autograd is NaN are skipped: d|x|/dx at x = 0 (a sample
+    that is its own neighbor sits exactly on the centre kernel point), where the reference's
+    formula returns 0 thanks to its 1e-6 guard."""
+    leaves = {n: torch.tensor(np.asarray(args[n], dtype=np.float64), requires_grad=True) for n in names}
+    call = dict(args)
+    call.update(leaves)
+    if tie:  # e.g. samples are the same tensor as pts
+        call[tie[0]] = leaves[tie[1]]
+    (fn(**call) * torch.as_tensor(in_grads)).sum().backward()
+    for n in names:
+        auto, ana = leaves[n].grad.numpy(), analytic[n]
+        ok = np.isfinite(auto)
+        assert ok.mean() > 0.5
+        scale = np.abs(auto[ok]).max() + 1e-30
+        assert np.abs(auto[ok] - ana[ok]).max() <= 2e-5 * scale, n
+
+
+def _fd_points_check(fn, args, in_grads, analytic, probes=8, h=1e-6):
+    """Central differences with respect to the points when samples are the same array (the
+    analytic value is dPts + dSamples).  autograd cannot serve here: every point is its own
+    neighbor at distance 0 from the centre kernel point, where sqrt has no derivative."""
+    rs = np.random.RandomState(11)
+    base = args["pts"].astype(np.float64)
+    rest = {k: v for k, v in args.items() if k not in ("pts", "samples")}
+    for _ in range(probes):
+        idx = (rs.randint(base.shape[0]), rs.randint(base.shape[1]))
+        plus, minus = base.copy(), base.copy()
+        plus[idx] += h
+        minus[idx] -= h
+        lp = float((fn(pts=plus, samples=plus, **rest).numpy() * in_grads).sum())
+        lm = float((fn(pts=minus, samples=minus, **rest).numpy() * in_grads).sum())
+        num = (lp - lm) / (2 * h)
+        assert abs(num - analytic[idx]) <= 2e-3 * max(1.0, abs(num)), (idx, num, analytic[idx])  # 1e-6 guard of the reference formula
+
+
+@pytest.mark.parametrize("c", KP_CASES, ids=lambda c: "d%d_n%d" % (c["dims"], c["n"]))
+def test_kpconv_backward_formulas(ref_clouds, c):
+    # the reference gradchecks weights, features and kernel points (unit_test/test_kpconv_grads.py:111-121)
+    # and points (test_kpconv_pt_grads.py:98-100) numerically in float32; here the hand-written
+    # backward is compared with autograd of the float64 forward.
+    case = kp_case(ref_clouds, c, normal_feats=True)
+    g = np.random.RandomState(3).normal(size=(case["samples"].shape[0], c["cout"]))
+    args = dict(pts=case["pts"], feats=case["feats"], samples=case["samples"], neighbors=case["neighbors"],
+                start_ids=case["start_ids"], radii=case["radii"], kernel_pts=case["kernel_pts"],
+                sigma=case["sigma"], weights=case["weights"])
+    dw, df, dk, dp, ds = [t.numpy() for t in conv_oracle.kp_conv_grads(**args, in_grads=g)]
+    _autograd_check(conv_oracle.kp_conv, args, ["weights", "feats", "kernel_pts"], g,
+                    dict(weights=dw, feats=df, kernel_pts=dk))
+    if c["dims"] != 2:  # the 2-D table puts every shell point at distance sigma from the centre: a kink at every self pair
+        _fd_points_check(conv_oracle.kp_conv, args, g, dp + ds)
+
+
+@pytest.mark.parametrize("c", MC_CASES, ids=lambda c: "d%d_n%d" % (c["dims"], c["n"]))
+def test_mcconv_backward_formulas(ref_clouds, c):
+    # unit_test/test_mcconv_grads.py:127-141 and test_mcconv_pt_grads.py:118-124 of the reference
+    case = mc_case(ref_clouds, c, normal_feats=True)
+    g = np.random.RandomState(4).normal(size=(case["samples"].shape[0], c["cout"]))
+    args = dict(pts=case["pts"], pdf=case["pdf"], feats=case["feats"], samples=case["samples"],
+                neighbors=case["neighbors"], start_ids=case["start_ids"], radii=case["radii"], axis=case["axis"],
+                bias=case["bias"], weights=case["weights"])
+    dw, df, da, db, dpdf, dp, ds = [t.numpy() for t in conv_oracle.mc_conv_grads(**args, in_grads=g)]
+    _autograd_check(conv_oracle.mc_conv, args, ["weights", "feats", "axis", "bias", "pdf"], g,
+                    dict(weights=dw, feats=df, axis=da, bias=db, pdf=dpdf))
+    _autograd_check(conv_oracle.mc_conv, args, ["pts"], g, dict(pts=dp + ds), tie=("samples", "pts"))
+
+
+def test_mcconv_oracle_with_two_mlps_is_block_diagonal(ref_clouds):
+    c = dict(MC_CASES[0], cout=64)
+    case = mc_case(ref_clouds, c, num_mlps=2)
+    got = conv_oracle.mc_conv(case["pts"], case["pdf"], case["feats"], case["samples"], case["neighbors"],
+                              case["start_ids"], case["radii"], case["axis"], case["bias"], case["weights"])
+    assert tuple(got.shape) == (case["samples"].shape[0], 64) and torch.isfinite(got).all()

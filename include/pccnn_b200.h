@@ -221,6 +221,13 @@ size_t pccnn_gemm_workspace_bytes(int64_t M, int N, int K);
 int pccnn_gemm_f32(int64_t M, int N, int K, const float* A, int64_t lda, const float* B, int64_t ldb,
                    float* C, int64_t ldc, int split, void* workspace, size_t workspace_bytes, void* stream);
 
+/* C[I, N] = A[rows, I]^T * B[rows, N] (the weight-gradient contraction dW = P^T g of
+ * pccnn_lib_ops/pcconvs/kpconv.cu:90-93): the reduction runs over the rows, split across CTAs,
+ * partial tiles are summed with float reductions (the order of the partial sums is not fixed). */
+size_t pccnn_gemm_tn_workspace_bytes(int64_t rows, int I, int N);
+int pccnn_gemm_tn_f32(int64_t rows, int I, int N, const float* A, int64_t lda, const float* B, int64_t ldb,
+                      float* C, int64_t ldc, int split, void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

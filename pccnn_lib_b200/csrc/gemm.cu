@@ -222,6 +222,133 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     }
 }
 
+// Shared-memory matrix descriptor of an MN-major bf16 tile: rows of the tile in memory are K
+// indices, each row holds 64 contiguous MN elements (128 bytes, 128-byte swizzle).  8-row K groups
+// are 1024 bytes apart (stride byte offset); the next 64 MN elements live `mn_group_bytes`
+// further (leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_group_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
+    d |= (uint64_t)(mn_group_bytes >> 4) << 16;        // leading byte offset
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+    d |= (uint64_t)1 << 46;                            // version
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+
+// C[I, N] += A[rows, I]^T * B[rows, N]: both operands are row-major with the reduction index as
+// the row, i.e. MN-major for the tensor core.  This is the weight gradient dW = P^T g
+// (pccnn_lib_ops/pcconvs/kpconv.cu:90-93 of the reference).  grid = (I tiles, N tiles, splits):
+// every CTA reduces its slab of rows in tensor memory and adds its tile to C with float
+// reductions, so C must be zeroed by the caller.  Same roles and bounded waits as the kernel above.
+template <int BN>
+__global__ void __launch_bounds__(128)
+gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                    float* __restrict__ C, int I, int N, int ldc, int k_blocks_total, int passes, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + kGemmStages * GemmSmem<BN>::kStage);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kGemmStages;
+    uint64_t* acc_ready = bars + 2 * kGemmStages;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kGemmStages + 1);
+    constexpr uint32_t kTmemCols = BN;
+    constexpr int kHalf = 64 * kGemmBK * 2;  // one 64-row x 64-column box: 8 KB
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i0 = blockIdx.x * kGemmBM, n0 = blockIdx.y * BN;
+    // slab of 64-row blocks owned by this split
+    const int per = (k_blocks_total + gridDim.z - 1) / gridDim.z;
+    const int kb_begin = blockIdx.z * per;
+    const int kb_end = min(k_blocks_total, kb_begin + per);
+    const int k_blocks = kb_end - kb_begin;
+    if (k_blocks <= 0) return;
+    const int total = k_blocks * passes;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGemmStages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        mbar_init(acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool ok = true;
+    if (warp == 0 && lane == 0) {
+        for (int it = 0; it < total && ok; ++it) {
+            const int s = it % kGemmStages, round = it / kGemmStages;
+            if (round > 0) ok = mbar_wait(empty + s, (round - 1) & 1);
+            if (!ok) break;
+            const int pass = it / k_blocks, kb = kb_begin + (it - pass * k_blocks);
+            const CUtensorMap* ma = (pass == 1) ? &map_a_lo : &map_a_hi;
+            const CUtensorMap* mb = (pass == 2) ? &map_b_lo : &map_b_hi;
+            uint8_t* sa = smem + s * GemmSmem<BN>::kStage;
+            mbar_expect_tx(full + s, GemmSmem<BN>::kStage);
+            tma_load_2d(sa, ma, full + s, i0, kb * 64);
+            tma_load_2d(sa + kHalf, ma, full + s, i0 + 64, kb * 64);
+#pragma unroll
+            for (int h = 0; h < BN / 64; ++h)
+                tma_load_2d(sa + GemmSmem<BN>::kA + h * kHalf, mb, full + s, n0 + h * 64, kb * 64);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // fp32 accumulate, bf16 x bf16, both operands MN-major (bits 15 and 16).
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kGemmBM >> 4) << 24);
+        for (int it = 0; it < total && ok; ++it) {
+            const int s = it % kGemmStages, round = it / kGemmStages;
+            ok = mbar_wait(full + s, round & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * GemmSmem<BN>::kStage);
+            const uint64_t da = umma_desc_mn_sw128(sa, kHalf), db = umma_desc_mn_sw128(sa + GemmSmem<BN>::kA, kHalf);
+#pragma unroll
+            for (int k = 0; k < 64 / 16; ++k) {
+                // 16 reduction rows = 2048 bytes further: +128 in 16-byte units.
+                tc_mma_bf16(tmem_base, da + 128 * k, db + 128 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit(empty + s);
+        }
+        if (ok) tc_commit(acc_ready);
+    }
+    if (!ok) atomicExch(status, 3);
+
+    __syncwarp();
+    bool ready = mbar_wait(acc_ready, 0);
+    if (!ready && lane == 0) atomicExch(status, 4);
+    tc_fence_after();
+    if (ready) {
+        const int row = i0 + warp * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+            if (row < I) {
+                float* dst = C + (size_t)row * ldc + n0 + c0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (n0 + c0 + j < N) atomicAdd(dst + j, __uint_as_float(r[j]));
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
 // ---- fp32 -> (hi, lo) bf16 split with zero padding ------------------------------------------
 __global__ void __launch_bounds__(256)
 split_bf16_kernel(int64_t rows, int cols, const float* __restrict__ src, int64_t ld_src, int ld_dst,
@@ -334,6 +461,45 @@ int gemm_bf16_nt(const GemmOperand& a, const GemmOperand& b, float* C, int64_t M
     return launch_gemm<256>(a, b, C, M, N, K_padded, ldc, status, s);
 }
 
+template <int BN>
+static int launch_gemm_tn(const GemmOperand& a, const GemmOperand& b, float* C, int64_t rows, int I, int N, int ldc,
+                          int* status, cudaStream_t s) {
+    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    const int passes = (a.lo && b.lo) ? 3 : 1;
+    if (int rc = make_map(&ma_hi, a.hi, rows, a.ld, 64)) return rc;
+    if (int rc = make_map(&ma_lo, passes == 3 ? a.lo : a.hi, rows, a.ld, 64)) return rc;
+    if (int rc = make_map(&mb_hi, b.hi, rows, b.ld, 64)) return rc;
+    if (int rc = make_map(&mb_lo, passes == 3 ? b.lo : b.hi, rows, b.ld, 64)) return rc;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(gemm_bf16_tn_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        GemmSmem<BN>::kBytes);
+    });
+    PCCNN_CUDA(attr_err);
+    const int k_blocks = (int)((rows + 63) / 64);
+    const int tiles = ((I + kGemmBM - 1) / kGemmBM) * ((N + BN - 1) / BN);
+    int splits = (2 * sm_count() + tiles - 1) / tiles;  // about two CTAs per SM in total
+    if (splits > k_blocks) splits = k_blocks;
+    if (splits < 1) splits = 1;
+    dim3 grid((unsigned)((I + kGemmBM - 1) / kGemmBM), (unsigned)((N + BN - 1) / BN), (unsigned)splits);
+    gemm_bf16_tn_kernel<BN><<<grid, 128, GemmSmem<BN>::kBytes, s>>>(ma_hi, ma_lo, mb_hi, mb_lo, C, I, N, ldc, k_blocks,
+                                                                  passes, status);
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
+int gemm_bf16_tn_accumulate(const GemmOperand& a, const GemmOperand& b, float* C, int64_t rows, int I, int N, int ldc,
+                            int* status, cudaStream_t s) {
+    PCCNN_CHECK_ARG(rows >= 0 && rows < 0x7fffffffLL && I > 0 && N > 0, "gemm_tn: bad shape");
+    PCCNN_CHECK_ARG(a.ld >= (I + 63) / 64 * 64 && b.ld >= (N + 63) / 64 * 64,
+                    "gemm_tn: operand rows must be padded to a multiple of 64 elements");
+    if (rows == 0) return PCCNN_OK;
+    if (N <= 64) return launch_gemm_tn<64>(a, b, C, rows, I, N, ldc, status, s);
+    if (N <= 128) return launch_gemm_tn<128>(a, b, C, rows, I, N, ldc, status, s);
+    return launch_gemm_tn<256>(a, b, C, rows, I, N, ldc, status, s);
+}
+
 int split_bf16(int64_t rows, int cols, const float* src, int64_t ld_src, int ld_dst, void* hi, void* lo,
                cudaStream_t s) {
     if (rows == 0) return PCCNN_OK;
@@ -388,6 +554,41 @@ int pccnn_gemm_f32(int64_t M, int N, int K, const float* A, int64_t lda, const f
     PCCNN_CUDA(cudaStreamSynchronize(s));
     if (host_status != 0) {
         set_error("gemm_f32: a bounded wait inside the tensor-core kernel ran out (status %d)", host_status);
+        return PCCNN_ERR_DEVICE;
+    }
+    return PCCNN_OK;
+}
+
+size_t pccnn_gemm_tn_workspace_bytes(int64_t rows, int I, int N) {
+    const int64_t ip = (I + 63) / 64 * 64, np_ = (N + 63) / 64 * 64;
+    return (size_t)(align_up((size_t)rows * ip * 2) * 2 + align_up((size_t)rows * np_ * 2) * 2 + 256);
+}
+
+int pccnn_gemm_tn_f32(int64_t rows, int I, int N, const float* A, int64_t lda, const float* B, int64_t ldb, float* C,
+                      int64_t ldc, int split, void* workspace, size_t workspace_bytes, void* stream) {
+    PCCNN_CHECK_ARG(rows >= 0 && I > 0 && N > 0, "gemm_tn_f32: bad shape");
+    PCCNN_CHECK_ARG(A && B && C, "gemm_tn_f32: null pointer");
+    if (!workspace || workspace_bytes < pccnn_gemm_tn_workspace_bytes(rows, I, N)) {
+        set_error("gemm_tn_f32: workspace too small");
+        return PCCNN_ERR_WORKSPACE;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const int ip = (I + 63) / 64 * 64, np_ = (N + 63) / 64 * 64;
+    char* ws = (char*)workspace;
+    const size_t a_bytes = align_up((size_t)rows * ip * 2), b_bytes = align_up((size_t)rows * np_ * 2);
+    GemmOperand a{ws, split ? ws + a_bytes : nullptr, ip};
+    GemmOperand b{ws + 2 * a_bytes, split ? ws + 2 * a_bytes + b_bytes : nullptr, np_};
+    int* status = (int*)(ws + 2 * a_bytes + 2 * b_bytes);
+    PCCNN_CUDA(cudaMemsetAsync(status, 0, 4, s));
+    for (int64_t r = 0; r < I; ++r) PCCNN_CUDA(cudaMemsetAsync(C + r * ldc, 0, (size_t)N * 4, s));
+    if (int rc = split_bf16(rows, I, A, lda, ip, a.hi, a.lo, s)) return rc;
+    if (int rc = split_bf16(rows, N, B, ldb, np_, b.hi, b.lo, s)) return rc;
+    if (int rc = gemm_bf16_tn_accumulate(a, b, C, rows, I, N, (int)ldc, status, s)) return rc;
+    int host_status = 0;
+    PCCNN_CUDA(cudaMemcpyAsync(&host_status, status, 4, cudaMemcpyDeviceToHost, s));
+    PCCNN_CUDA(cudaStreamSynchronize(s));
+    if (host_status != 0) {
+        set_error("gemm_tn_f32: a bounded wait inside the tensor-core kernel ran out (status %d)", host_status);
         return PCCNN_ERR_DEVICE;
     }
     return PCCNN_OK;

@@ -20,6 +20,11 @@ struct GemmOperand {
 int gemm_bf16_nt(const GemmOperand& a, const GemmOperand& b, float* C, int64_t M, int N, int K_padded, int ldc,
                  int* status, cudaStream_t s);
 
+// C[I, N] (fp32, zeroed by the caller or holding a running sum) += A[rows, I]^T * B[rows, N];
+// operand rows padded to a multiple of 64 elements.  Partial sums are added with float reductions.
+int gemm_bf16_tn_accumulate(const GemmOperand& a, const GemmOperand& b, float* C, int64_t rows, int I, int N, int ldc,
+                            int* status, cudaStream_t s);
+
 // hi = bf16(src), lo = bf16(src - hi); destination rows padded with zeros to ld_dst.  lo may be null.
 int split_bf16(int64_t rows, int cols, const float* src, int64_t ld_src, int ld_dst, void* hi, void* lo,
                cudaStream_t s);

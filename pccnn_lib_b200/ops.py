@@ -341,3 +341,22 @@ def mc_conv(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_proj, ax
                                        _p(start_ids), _p(radii), _p(axis_proj), _p(axis_bias), hidden, n_mlps,
                                        _p(weights), cout, _p(out), ws.data_ptr(), ws.numel(), _stream()), "mc_conv")
     return out
+
+
+def gemm_tn_f32(a, b, split=True):
+    """a[R, I]^T @ b[R, N] -> [I, N] float32 on the tensor cores (reduction over the rows): the
+    weight-gradient contraction of pcconvs/kpconv.cu:90-93 of the reference."""
+    a = _need(a, "a", torch.float32, 2)
+    b = _need(b, "b", torch.float32, 2)
+    if a.shape[0] != b.shape[0]:
+        raise RuntimeError("gemm_tn_f32: row counts differ")
+    r, i = a.shape
+    n = b.shape[1]
+    out = torch.zeros((i, n), dtype=torch.float32, device=a.device)
+    if r == 0 or i == 0 or n == 0:
+        return out
+    with torch.cuda.device(a.device):
+        ws = _workspace(_lib.pccnn_gemm_tn_workspace_bytes(r, i, n), a.device)
+        _capi.check(_lib.pccnn_gemm_tn_f32(r, i, n, _p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0),
+                                           1 if split else 0, ws.data_ptr(), ws.numel(), _stream()), "gemm_tn_f32")
+    return out

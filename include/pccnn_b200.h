@@ -208,6 +208,34 @@ int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, co
                   int hidden, int num_mlps, const float* weights, int cout, float* out,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* Gradients of the two convolutions for an upstream gradient in_grads [num_samples, cout].
+ * Every output is zero-filled here and accumulated with float reductions (like the reference,
+ * whose scatter steps use atomics), so results are reproducible only up to summation order.
+ * Scratch: pccnn_conv_grads_workspace_bytes(num_samples, cin, basis_size, cout).
+ *
+ * pccnn_kp_conv_grads replaces kpconv_grads()  pccnn_lib_ops/pcconvs/kpconv.cu:63-112
+ * (shared/feat_basis_proj_grads.cu:158-223, shared/kernel_pts_basis.cu:41-70, shared/pt_diff.cu:51-80);
+ * outputs: weights [K*cin, cout], features [num_pts, cin], kernel points [K, D], points [num_pts, D],
+ * samples [num_samples, D].
+ * pccnn_mc_conv_grads replaces mcconv_grads()  pccnn_lib_ops/pcconvs/mcconv.cu:73-143
+ * (shared/mlp_basis.cu:50-96); outputs: weights (shape of the weights), features, axis [D, hidden],
+ * bias [hidden], pdf [num_pts], points, samples. */
+size_t pccnn_conv_grads_workspace_bytes(int64_t num_samples, int cin, int basis_size, int cout);
+int pccnn_kp_conv_grads(int D, int64_t num_pts, const float* pts, const float* feats, int cin,
+                        int64_t num_samples, const float* samples, const int32_t* neighbors,
+                        const int32_t* start_ids, const float* radii, const float* kernel_pts,
+                        int num_kernel_pts, float sigma, const float* weights, int cout,
+                        const float* in_grads, float* out_weight_grads, float* out_feat_grads,
+                        float* out_kernel_pt_grads, float* out_pt_grads, float* out_sample_grads,
+                        void* workspace, size_t workspace_bytes, void* stream);
+int pccnn_mc_conv_grads(int D, int64_t num_pts, const float* pts, const float* pdf, const float* feats, int cin,
+                        int64_t num_samples, const float* samples, const int32_t* neighbors,
+                        const int32_t* start_ids, const float* radii, const float* axis, const float* bias,
+                        int hidden, int num_mlps, const float* weights, int cout, const float* in_grads,
+                        float* out_weight_grads, float* out_feat_grads, float* out_axis_grads,
+                        float* out_bias_grads, float* out_pdf_grads, float* out_pt_grads,
+                        float* out_sample_grads, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------- */
 /* Dense contraction on the tensor cores                                      */
 /* ------------------------------------------------------------------------- */

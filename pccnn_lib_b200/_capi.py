@@ -40,6 +40,13 @@ SIGNATURES = {
                                ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
     "pccnn_mc_conv": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                                _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
+    "pccnn_conv_grads_workspace_bytes": (_size, [_c_i64, _c_int, _c_int, _c_int]),
+    "pccnn_kp_conv_grads": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
+                                     ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _size,
+                                     _ptr]),
+    "pccnn_mc_conv_grads": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
+                                     _ptr, _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+                                     _ptr, _size, _ptr]),
     "pccnn_gemm_workspace_bytes": (_size, [_c_i64, _c_int, _c_int]),
     "pccnn_gemm_f32": (_c_int, [_c_i64, _c_int, _c_int, _ptr, _c_i64, _ptr, _c_i64, _ptr, _c_i64, _c_int, _ptr,
                                 _size, _ptr]),

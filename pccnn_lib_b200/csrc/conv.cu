@@ -25,7 +25,9 @@
 
 namespace pccnn {
 
-constexpr int kConvWarps = 4;
+// Warps per block: the two per-warp basis buffers of the backward kernel must fit in 48 KB.
+template <int KP>
+constexpr int conv_warps() { return KP >= 64 ? 2 : 4; }
 
 struct KPBasisArgs {
     const float* kernel_pts;  // [K, D]
@@ -58,6 +60,39 @@ struct KPBasis {
             b[k] = (k < K) ? fminf(fmaxf(val, 0.f), 1.f) : 0.f;
         }
     }
+    // Backward of eval (shared/kernel_pts_basis.cu:41-70 of the reference: mask 1 - dist/sigma >= 0,
+    // 1 / (dist + 1e-6)).  db = dL/db[k]; adds to d_off = dL/d(offset) and, through shared-memory
+    // float reductions, to s_grad laid out like the kernel points [K, D].
+    static constexpr int kGradFloats = KP * D;
+    __device__ static void grad(const float* sp, const KPBasisArgs& a, int K, const float (&d)[D], int /*n0*/,
+                                const float* db, float (&d_off)[D], float* s_grad, float& /*d_pdf*/) {
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+            if (k >= K) break;
+            float v[D], acc = 0.f;
+#pragma unroll
+            for (int x = 0; x < D; ++x) {
+                v[x] = sp[k * D + x] - d[x];
+                acc = fmaf(v[x], v[x], acc);
+            }
+            const float dist = sqrtf(fmaxf(acc, 0.f));
+            if (1.0f - dist * a.inv_sigma >= 0.f) {
+                const float gk = -db[k] * a.inv_sigma / (dist + 1e-6f);
+                if (gk != 0.f) {
+#pragma unroll
+                    for (int x = 0; x < D; ++x) {
+                        const float t = gk * v[x];
+                        atomicAdd(s_grad + k * D + x, t);
+                        d_off[x] -= t;
+                    }
+                }
+            }
+        }
+    }
+    __device__ static void flush(const float* s_grad, int K, float* g0, float* /*g1*/) {
+        for (int i = threadIdx.x; i < K * D; i += blockDim.x)
+            if (s_grad[i] != 0.f) atomicAdd(g0 + i, s_grad[i]);
+    }
 };
 
 template <int D, int KP>
@@ -84,16 +119,49 @@ struct MLPBasis {
             b[k] = (k < K) ? acc * inv_pdf : 0.f;
         }
     }
+    // Backward of eval (shared/mlp_basis.cu:50-96 of the reference).  s_grad holds the axis
+    // gradient [D, KP] followed by the bias gradient [KP].
+    static constexpr int kGradFloats = (D + 1) * KP;
+    __device__ static void grad(const float* sp, const MLPBasisArgs& a, int K, const float (&d)[D], int n0,
+                                const float* db, float (&d_off)[D], float* s_grad, float& d_pdf) {
+        const float inv_pdf = 1.0f / __ldg(a.pdf + n0);
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+            if (k >= K) break;
+            float pre = 0.f;
+#pragma unroll
+            for (int x = 0; x < D; ++x) pre = fmaf(d[x], sp[x * KP + k], pre);
+            pre += sp[D * KP + k];
+            const float act = pre > 0.f ? pre : 0.2f * pre;
+            d_pdf -= act * db[k] * inv_pdf * inv_pdf;
+            const float cur = db[k] * inv_pdf * (act > 0.f ? 1.0f : 0.2f);
+            if (cur != 0.f) {
+                atomicAdd(s_grad + D * KP + k, cur);
+#pragma unroll
+                for (int x = 0; x < D; ++x) {
+                    atomicAdd(s_grad + x * KP + k, d[x] * cur);
+                    d_off[x] = fmaf(cur, sp[x * KP + k], d_off[x]);
+                }
+            }
+        }
+    }
+    __device__ static void flush(const float* s_grad, int K, float* g_axis, float* g_bias) {
+        for (int i = threadIdx.x; i < (D + 1) * KP; i += blockDim.x) {
+            const int row = i / KP, k = i - row * KP;
+            if (k < K && s_grad[i] != 0.f) atomicAdd(row < D ? g_axis + row * K + k : g_bias + k, s_grad[i]);
+        }
+    }
 };
 
 // P[m, c*K + k] for the samples [m_begin, m_end), written as bf16 hi (+ lo) rows of ld_p elements.
 template <int D, int KP, class BASIS, class ARGS>
-__global__ void __launch_bounds__(kConvWarps * 32)
+__global__ void __launch_bounds__(conv_warps<KP>() * 32)
 project_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __restrict__ feats, int cin,
                const float* __restrict__ samples, const int2* __restrict__ neighbors,
                const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
                __nv_bfloat16* __restrict__ p_hi, __nv_bfloat16* __restrict__ p_lo, int ld_p) {
     constexpr int CPL = 64 / KP;  // channels per lane
+    constexpr int kConvWarps = conv_warps<KP>();
     __shared__ float s_params[BASIS::kParamFloats];
     __shared__ float s_basis[kConvWarps][32][KP + 1];
     __shared__ int s_n0[kConvWarps][32];
@@ -175,15 +243,202 @@ project_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __r
     }
 }
 
+// Sum over the 32 lanes of a KP-vector held by every lane.  Recursive halving: at each step a
+// lane hands half of its entries to its partner, so 32 lanes end up owning the KP sums between
+// them (entries [k0, k0 + n) on return; lanes that share entries hold identical sums).
+template <int KP>
+__device__ __forceinline__ void warp_reduce_scatter(float (&v)[KP], int lane, int& k0, int& n) {
+    n = KP;
+    k0 = 0;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        if (n > 1) {
+            n >>= 1;
+            const bool up = (lane & off) != 0;
+#pragma unroll
+            for (int q = 0; q < KP / 2; ++q) {
+                if (q < n) {
+                    const float send = up ? v[q] : v[q + n];
+                    const float keep = up ? v[q + n] : v[q];
+                    v[q] = keep + __shfl_xor_sync(kFullMask, send, off);
+                }
+            }
+            k0 += up ? n : 0;
+        } else {
+            v[0] += __shfl_xor_sync(kFullMask, v[0], off);
+        }
+    }
+}
+
+// Everything of the backward pass that runs per neighbor pair, given dP = g W^T for the samples
+// [m_begin, m_end) (pccnn_lib_ops/pcconvs/shared/feat_basis_proj_grads.cu:32-154, then the basis
+// and offset gradients of kernel_pts_basis.cu:41-70 / mlp_basis.cu:50-96 and pt_diff.cu:51-80 of
+// the reference, which are ~15 separate launches there):
+//     dF[n0, c]  += sum_k dP[m, c, k] * b[t, k]
+//     db[t, k]    = sum_c dP[m, c, k] * F[n0, c]   -> basis gradient -> d(offset) and parameter gradients
+//     dPts[n0]   += d(offset) / radii,   dSamples[m] = -sum_t d(offset) / radii
+// A warp owns a sample.  The lanes alternate between "32 neighbors" (basis, basis gradient) and
+// "32 channels x CPL" (the two contractions against the sample's dP row held in registers).
+template <int D, int KP, class BASIS, class ARGS>
+__global__ void __launch_bounds__(conv_warps<KP>() * 32)
+backward_pairs_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __restrict__ feats, int cin,
+                      const float* __restrict__ samples, const int2* __restrict__ neighbors,
+                      const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
+                      const float* __restrict__ d_proj, float* __restrict__ d_feat, float* __restrict__ d_pts,
+                      float* __restrict__ d_samples, float* __restrict__ d_param0, float* __restrict__ d_param1,
+                      float* __restrict__ d_pdf) {
+    constexpr int CPL = 64 / KP;
+    constexpr int kConvWarps = conv_warps<KP>();
+    __shared__ float s_params[BASIS::kParamFloats];
+    __shared__ float s_grad[BASIS::kGradFloats];
+    __shared__ float s_basis[kConvWarps][32][KP + 1];
+    __shared__ float s_db[kConvWarps][32][KP + 1];
+    __shared__ int s_n0[kConvWarps][32];
+    BASIS::load_params(s_params, args, K);
+    for (int i = threadIdx.x; i < BASIS::kGradFloats; i += blockDim.x) s_grad[i] = 0.f;
+    __syncthreads();
+
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    float inv[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) inv[d] = __frcp_rn(__ldg(radii + d));
+    const int inner = cin * K;
+
+    for (int m = m_begin + blockIdx.x * kConvWarps + warp; m < m_end; m += gridDim.x * kConvWarps) {
+        const int lo = (m > 0) ? __ldg(start_ids + m - 1) : 0;
+        const int hi = __ldg(start_ids + m);
+        float s[D], ds_acc[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            s[d] = __ldg(samples + (int64_t)m * D + d);
+            ds_acc[d] = 0.f;
+        }
+        const float* grow = d_proj + (size_t)(m - m_begin) * inner;
+
+        for (int t0 = lo; t0 < hi; t0 += 32) {
+            // Lanes as neighbors: offset and basis row of pair t0 + lane (kept for the gradient below).
+            const int t = t0 + lane;
+            int n0 = 0;
+            float d[D];
+#pragma unroll
+            for (int x = 0; x < D; ++x) d[x] = 0.f;
+            if (t < hi) {
+                n0 = __ldg(&neighbors[t]).x;
+                float b[KP];
+#pragma unroll
+                for (int x = 0; x < D; ++x) d[x] = (__ldg(pts + (int64_t)n0 * D + x) - s[x]) * inv[x];
+                BASIS::eval(s_params, args, K, d, n0, b);
+#pragma unroll
+                for (int k = 0; k < KP; ++k) s_basis[warp][lane][k] = b[k];
+                s_n0[warp][lane] = n0;
+            }
+#pragma unroll
+            for (int k = 0; k < KP; ++k) s_db[warp][lane][k] = 0.f;
+            __syncwarp();
+
+            // Lanes as channels.
+            const int cnt = min(32, hi - t0);
+            for (int cb = 0; cb < cin; cb += 32 * CPL) {
+                float g[CPL][KP];
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) {
+                    const int c = cb + i * 32 + lane;
+#pragma unroll
+                    for (int k = 0; k < KP; ++k) g[i][k] = (c < cin && k < K) ? __ldg(grow + (size_t)c * K + k) : 0.f;
+                }
+                for (int j = 0; j < cnt; ++j) {
+                    const int nj = s_n0[warp][j];
+                    const float* frow = feats + (int64_t)nj * cin + cb + lane;
+                    float f[CPL], df[CPL], pb[KP];
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        f[i] = (cb + i * 32 + lane < cin) ? __ldg(frow + i * 32) : 0.f;
+                        df[i] = 0.f;
+                    }
+#pragma unroll
+                    for (int k = 0; k < KP; ++k) {
+                        const float bk = s_basis[warp][j][k];
+                        float acc = 0.f;
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i) {
+                            df[i] = fmaf(g[i][k], bk, df[i]);
+                            acc = fmaf(g[i][k], f[i], acc);
+                        }
+                        pb[k] = acc;
+                    }
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        const int c = cb + i * 32 + lane;
+                        if (c < cin && df[i] != 0.f) atomicAdd(d_feat + (int64_t)nj * cin + c, df[i]);
+                    }
+                    int k0, n;
+                    warp_reduce_scatter<KP>(pb, lane, k0, n);
+                    // lanes whose low bits are zero speak for their group of identical sums
+                    if ((lane & ((32 / (KP < 32 ? KP : 32)) - 1)) == 0) {
+#pragma unroll
+                        for (int q = 0; q < (KP + 31) / 32; ++q) s_db[warp][j][k0 + q] += pb[q];
+                    }
+                }
+                __syncwarp();
+            }
+
+            // Lanes as neighbors again: basis gradient, offset gradient, point gradients.
+            if (t < hi) {
+                float d_off[D], dpdf = 0.f;
+#pragma unroll
+                for (int x = 0; x < D; ++x) d_off[x] = 0.f;
+                BASIS::grad(s_params, args, K, d, n0, s_db[warp][lane], d_off, s_grad, dpdf);
+#pragma unroll
+                for (int x = 0; x < D; ++x) {
+                    const float gx = d_off[x] * inv[x];
+                    if (gx != 0.f) atomicAdd(d_pts + (int64_t)n0 * D + x, gx);
+                    ds_acc[x] += gx;
+                }
+                if (d_pdf && dpdf != 0.f) atomicAdd(d_pdf + n0, dpdf);
+            }
+            __syncwarp();
+        }
+#pragma unroll
+        for (int x = 0; x < D; ++x) {
+            const float tot = warp_sum(ds_acc[x]);
+            if (lane == 0) d_samples[(int64_t)m * D + x] = -tot;
+        }
+    }
+    __syncthreads();
+    BASIS::flush(s_grad, K, d_param0, d_param1);
+}
+
+template <int D, class ARGS, template <int, int> class BASIS>
+static int launch_backward_pairs(int K, const ARGS& args, const float* pts, const float* feats, int cin,
+                                 const float* samples, const int32_t* neighbors, const int32_t* start_ids,
+                                 const float* radii, int m_begin, int m_end, const float* d_proj, float* d_feat,
+                                 float* d_pts, float* d_samples, float* d_param0, float* d_param1, float* d_pdf,
+                                 cudaStream_t s) {
+    const int count = m_end - m_begin;
+    if (count <= 0) return PCCNN_OK;
+#define PCCNN_BACKWARD(KP)                                                                                          \
+    backward_pairs_kernel<D, KP, BASIS<D, KP>, ARGS>                                                                \
+        <<<grid_for((int64_t)count * 32, conv_warps<KP>() * 32, 4), conv_warps<KP>() * 32, 0, s>>>(                  \
+        args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids, radii, m_begin, m_end, d_proj, d_feat, \
+        d_pts, d_samples, d_param0, d_param1, d_pdf)
+    if (K <= 8) PCCNN_BACKWARD(8);
+    else if (K <= 16) PCCNN_BACKWARD(16);
+    else if (K <= 32) PCCNN_BACKWARD(32);
+    else PCCNN_BACKWARD(64);
+#undef PCCNN_BACKWARD
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
 template <int D, class ARGS, template <int, int> class BASIS>
 static int launch_project(int K, const ARGS& args, const float* pts, const float* feats, int cin, const float* samples,
                           const int32_t* neighbors, const int32_t* start_ids, const float* radii, int m_begin,
                           int m_end, void* p_hi, void* p_lo, int ld_p, cudaStream_t s) {
     const int count = m_end - m_begin;
     if (count <= 0) return PCCNN_OK;
-    const unsigned grid = grid_for((int64_t)count * 32, kConvWarps * 32, 8);
 #define PCCNN_PROJECT(KP)                                                                                        \
-    project_kernel<D, KP, BASIS<D, KP>, ARGS><<<grid, kConvWarps * 32, 0, s>>>(                                   \
+    project_kernel<D, KP, BASIS<D, KP>, ARGS>                                                                    \
+        <<<grid_for((int64_t)count * 32, conv_warps<KP>() * 32, 8), conv_warps<KP>() * 32, 0, s>>>(                                   \
         args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids, radii, m_begin, m_end,             \
         (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo, ld_p)
     if (K <= 8) PCCNN_PROJECT(8);
@@ -276,6 +531,108 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
     return PCCNN_OK;
 }
 
+struct ConvBackwardLayout {
+    int ld_p, ld_g;
+    int64_t chunk;
+    size_t p_hi_off, p_lo_off, g_hi_off, g_lo_off, dproj_off, w_hi_off, w_lo_off, status_off, total;
+};
+
+static ConvBackwardLayout conv_backward_layout(int64_t num_samples, int cin, int K, int cout) {
+    ConvBackwardLayout L;
+    const int inner = cin * K;
+    L.ld_p = (inner + 63) / 64 * 64;
+    L.ld_g = (cout + 63) / 64 * 64;
+    L.chunk = num_samples < kConvChunk ? (num_samples > 0 ? num_samples : 1) : kConvChunk;
+    const size_t p_bytes = align_up((size_t)L.chunk * L.ld_p * 2);
+    const size_t g_bytes = align_up((size_t)L.chunk * L.ld_g * 2);
+    const size_t d_bytes = align_up((size_t)L.chunk * inner * 4);
+    const size_t w_bytes = align_up((size_t)inner * L.ld_g * 2);
+    L.p_hi_off = 0;
+    L.p_lo_off = p_bytes;
+    L.g_hi_off = 2 * p_bytes;
+    L.g_lo_off = L.g_hi_off + g_bytes;
+    L.dproj_off = L.g_lo_off + g_bytes;
+    L.w_hi_off = L.dproj_off + d_bytes;
+    L.w_lo_off = L.w_hi_off + w_bytes;
+    L.status_off = L.w_lo_off + w_bytes;
+    L.total = L.status_off + 256;
+    return L;
+}
+
+// Backward of conv_forward.  Per chunk of samples: recompute P, dW += P^T g and dP = g W^T on the
+// tensor cores, then the per-pair kernel.  All outputs are zeroed here and accumulated into.
+template <class ARGS, template <int, int> class BASIS>
+static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_t num_pts, const float* pts,
+                         const float* feats, int cin, int64_t num_samples, const float* samples,
+                         const int32_t* neighbors, const int32_t* start_ids, const float* radii, int num_mlps,
+                         const float* weights, int cout, const float* in_grads, float* d_weights, float* d_feat,
+                         float* d_param0, size_t param0_floats, float* d_param1, size_t param1_floats, float* d_pdf,
+                         float* d_pts, float* d_samples, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+    PCCNN_CHECK_ARG(D >= kMinDims && D <= kMaxDims, "%s: point dimension %d outside [2, 6]", who, D);
+    PCCNN_CHECK_ARG(K >= 1 && K <= 64, "%s: basis size %d outside [1, 64]", who, K);
+    PCCNN_CHECK_ARG(cin >= 1 && cout >= 1 && num_mlps >= 1 && cout % num_mlps == 0 && (cin * K) % num_mlps == 0,
+                    "%s: bad channel counts (cin %d, cout %d, mlps %d)", who, cin, cout, num_mlps);
+    PCCNN_CHECK_ARG(num_samples >= 0 && num_samples < 0x7fffffffLL && num_pts >= 0, "%s: bad sizes", who);
+    PCCNN_CHECK_ARG(d_weights && d_feat && d_param0 && d_pts && d_samples, "%s: null output", who);
+    const int inner = cin * K, inner_j = inner / num_mlps, cout_j = cout / num_mlps;
+    PCCNN_CHECK_ARG(num_mlps == 1 || (inner_j % 64 == 0 && cout_j % 64 == 0),
+                    "%s: with several MLPs, Cin*K and Cout per MLP must be multiples of 64", who);
+    PCCNN_CUDA(cudaMemsetAsync(d_weights, 0, (size_t)inner * cout_j * 4, s));
+    PCCNN_CUDA(cudaMemsetAsync(d_feat, 0, (size_t)num_pts * cin * 4, s));
+    PCCNN_CUDA(cudaMemsetAsync(d_param0, 0, param0_floats * 4, s));
+    if (d_param1) PCCNN_CUDA(cudaMemsetAsync(d_param1, 0, param1_floats * 4, s));
+    if (d_pdf) PCCNN_CUDA(cudaMemsetAsync(d_pdf, 0, (size_t)num_pts * 4, s));
+    PCCNN_CUDA(cudaMemsetAsync(d_pts, 0, (size_t)num_pts * D * 4, s));
+    PCCNN_CUDA(cudaMemsetAsync(d_samples, 0, (size_t)num_samples * D * 4, s));
+    if (num_samples == 0) return PCCNN_OK;
+    PCCNN_CHECK_ARG(pts && feats && samples && start_ids && radii && weights && in_grads, "%s: null pointer", who);
+    const ConvBackwardLayout L = conv_backward_layout(num_samples, cin, K, cout);
+    if (!workspace || workspace_bytes < L.total) {
+        set_error("%s: workspace of %zu bytes, need %zu", who, workspace_bytes, L.total);
+        return PCCNN_ERR_WORKSPACE;
+    }
+    char* ws = (char*)workspace;
+    int* status = (int*)(ws + L.status_off);
+    PCCNN_CUDA(cudaMemsetAsync(status, 0, 4, s));
+    // W_j as bf16 hi/lo rows [inner_j, ld_g] (reduction index of dP = g W^T is the output channel).
+    for (int j = 0; j < num_mlps; ++j) {
+        const size_t off = (size_t)j * inner_j * L.ld_g * 2;
+        if (int rc = split_bf16(inner_j, cout_j, weights + (size_t)j * inner_j * cout_j, cout_j, L.ld_g,
+                                ws + L.w_hi_off + off, ws + L.w_lo_off + off, s))
+            return rc;
+    }
+    float* d_proj = (float*)(ws + L.dproj_off);
+    for (int64_t m0 = 0; m0 < num_samples; m0 += L.chunk) {
+        const int64_t m1 = (m0 + L.chunk < num_samples) ? m0 + L.chunk : num_samples;
+        const int64_t rows = m1 - m0;
+        int rc = PCCNN_OK;
+        PCCNN_DISPATCH_DIM(D, (rc = launch_project<DIM, ARGS, BASIS>(K, args, pts, feats, cin, samples, neighbors,
+                                                                     start_ids, radii, (int)m0, (int)m1,
+                                                                     ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, s)));
+        if (rc) return rc;
+        if ((rc = split_bf16(rows, cout, in_grads + (size_t)m0 * cout, cout, L.ld_g, ws + L.g_hi_off, ws + L.g_lo_off, s)))
+            return rc;
+        for (int j = 0; j < num_mlps; ++j) {
+            GemmOperand p{ws + L.p_hi_off + (size_t)j * inner_j * 2, ws + L.p_lo_off + (size_t)j * inner_j * 2, L.ld_p};
+            GemmOperand g{ws + L.g_hi_off + (size_t)j * cout_j * 2, ws + L.g_lo_off + (size_t)j * cout_j * 2, L.ld_g};
+            GemmOperand w{ws + L.w_hi_off + (size_t)j * inner_j * L.ld_g * 2,
+                          ws + L.w_lo_off + (size_t)j * inner_j * L.ld_g * 2, L.ld_g};
+            // dW_j += P_j^T g_j
+            if ((rc = gemm_bf16_tn_accumulate(p, g, d_weights + (size_t)j * inner_j * cout_j, rows, inner_j, cout_j,
+                                              cout_j, status, s)))
+                return rc;
+            // dP_j = g_j W_j^T  ->  columns [j * inner_j, (j + 1) * inner_j) of the dP rows
+            const int kp = num_mlps == 1 ? L.ld_g : cout_j;
+            if ((rc = gemm_bf16_nt(g, w, d_proj + (size_t)j * inner_j, rows, inner_j, kp, inner, status, s))) return rc;
+        }
+        PCCNN_DISPATCH_DIM(D, (rc = launch_backward_pairs<DIM, ARGS, BASIS>(
+                                   K, args, pts, feats, cin, samples, neighbors, start_ids, radii, (int)m0, (int)m1,
+                                   d_proj, d_feat, d_pts, d_samples, d_param0, d_param1, d_pdf, s)));
+        if (rc) return rc;
+    }
+    return PCCNN_OK;
+}
+
 }  // namespace pccnn
 
 using namespace pccnn;
@@ -307,6 +664,41 @@ int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, co
     return conv_forward<MLPBasisArgs, MLPBasis>("mc_conv", D, hidden, args, num_pts, pts, feats, cin, num_samples,
                                                 samples, neighbors, start_ids, radii, num_mlps, weights, cout, out,
                                                 workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+size_t pccnn_conv_grads_workspace_bytes(int64_t num_samples, int cin, int basis_size, int cout) {
+    return conv_backward_layout(num_samples < 0 ? 0 : num_samples, cin, basis_size, cout).total;
+}
+
+int pccnn_kp_conv_grads(int D, int64_t num_pts, const float* pts, const float* feats, int cin, int64_t num_samples,
+                        const float* samples, const int32_t* neighbors, const int32_t* start_ids, const float* radii,
+                        const float* kernel_pts, int num_kernel_pts, float sigma, const float* weights, int cout,
+                        const float* in_grads, float* out_weight_grads, float* out_feat_grads,
+                        float* out_kernel_pt_grads, float* out_pt_grads, float* out_sample_grads, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+    PCCNN_CHECK_ARG(kernel_pts && sigma > 0.f, "kp_conv_grads: kernel points missing or sigma <= 0");
+    KPBasisArgs args{kernel_pts, 1.0f / sigma};
+    return conv_backward<KPBasisArgs, KPBasis>(
+        "kp_conv_grads", D, num_kernel_pts, args, num_pts, pts, feats, cin, num_samples, samples, neighbors, start_ids,
+        radii, 1, weights, cout, in_grads, out_weight_grads, out_feat_grads, out_kernel_pt_grads,
+        (size_t)num_kernel_pts * D, nullptr, 0, nullptr, out_pt_grads, out_sample_grads, workspace, workspace_bytes,
+        (cudaStream_t)stream);
+}
+
+int pccnn_mc_conv_grads(int D, int64_t num_pts, const float* pts, const float* pdf, const float* feats, int cin,
+                        int64_t num_samples, const float* samples, const int32_t* neighbors, const int32_t* start_ids,
+                        const float* radii, const float* axis, const float* bias, int hidden, int num_mlps,
+                        const float* weights, int cout, const float* in_grads, float* out_weight_grads,
+                        float* out_feat_grads, float* out_axis_grads, float* out_bias_grads, float* out_pdf_grads,
+                        float* out_pt_grads, float* out_sample_grads, void* workspace, size_t workspace_bytes,
+                        void* stream) {
+    PCCNN_CHECK_ARG(pdf && axis && bias && out_bias_grads && out_pdf_grads, "mc_conv_grads: null pointer");
+    MLPBasisArgs args{axis, bias, pdf};
+    return conv_backward<MLPBasisArgs, MLPBasis>(
+        "mc_conv_grads", D, hidden, args, num_pts, pts, feats, cin, num_samples, samples, neighbors, start_ids, radii,
+        num_mlps, weights, cout, in_grads, out_weight_grads, out_feat_grads, out_axis_grads, (size_t)D * hidden,
+        out_bias_grads, (size_t)hidden, out_pdf_grads, out_pt_grads, out_sample_grads, workspace, workspace_bytes,
+        (cudaStream_t)stream);
 }
 
 }  // extern "C"

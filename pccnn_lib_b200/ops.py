@@ -360,3 +360,53 @@ def gemm_tn_f32(a, b, split=True):
         _capi.check(_lib.pccnn_gemm_tn_f32(r, i, n, _p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0),
                                            1 if split else 0, ws.data_ptr(), ws.numel(), _stream()), "gemm_tn_f32")
     return out
+
+
+def kp_conv_grads(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights, in_grads):
+    """[dW, dFeat, dKernelPts, dPts, dSamples]; kpconv_grads() of pccnn_lib_ops/pcconvs/kpconv.cu:63-112."""
+    pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii)
+    kernel_pts = _need(kernel_pts, "kernel_pts", torch.float32, 2)
+    weights = _need(weights, "weights", torch.float32, 2)
+    in_grads = _need(in_grads, "in_grads", torch.float32, 2)
+    k, cin, cout = kernel_pts.shape[0], feats.shape[1], weights.shape[1]
+    m, n = samples.shape[0], pts.shape[0]
+    if weights.shape[0] != k * cin or tuple(in_grads.shape) != (m, cout):
+        raise RuntimeError("weights must be [K * Cin, Cout] and in_grads [M, Cout]")
+    dev = pts.device
+    d_w, d_f = torch.empty_like(weights), torch.empty_like(feats)
+    d_k, d_p, d_s = torch.empty_like(kernel_pts), torch.empty_like(pts), torch.empty_like(samples)
+    with torch.cuda.device(dev):
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, k, cout), dev)
+        _capi.check(_lib.pccnn_kp_conv_grads(d, n, _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
+                                             _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights),
+                                             cout, _p(in_grads), d_w.data_ptr(), d_f.data_ptr(), d_k.data_ptr(),
+                                             d_p.data_ptr(), d_s.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+                    "kp_conv_grads")
+    return [d_w, d_f, d_k, d_p, d_s]
+
+
+def mc_conv_grads(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_proj, axis_bias, weights, in_grads):
+    """[dW, dFeat, dAxis, dBias, dPdf, dPts, dSamples]; mcconv_grads() of pccnn_lib_ops/pcconvs/mcconv.cu:73-143."""
+    pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii)
+    pdf = _need(pdf, "pdf", torch.float32, 1)
+    axis_proj = _need(axis_proj, "axis_proj", torch.float32, 2)
+    axis_bias = _need(axis_bias, "axis_bias", torch.float32)
+    weights = _need(weights, "weights", torch.float32, 3)
+    in_grads = _need(in_grads, "in_grads", torch.float32, 2)
+    hidden, cin, n_mlps = axis_proj.shape[1], feats.shape[1], weights.shape[0]
+    cout = weights.shape[2] * n_mlps
+    m, n = samples.shape[0], pts.shape[0]
+    if tuple(in_grads.shape) != (m, cout):
+        raise RuntimeError("in_grads must be [M, Cout]")
+    dev = pts.device
+    d_w, d_f = torch.empty_like(weights), torch.empty_like(feats)
+    d_a, d_b, d_pdf = torch.empty_like(axis_proj), torch.empty_like(axis_bias), torch.empty_like(pdf)
+    d_p, d_s = torch.empty_like(pts), torch.empty_like(samples)
+    with torch.cuda.device(dev):
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, hidden, cout), dev)
+        _capi.check(_lib.pccnn_mc_conv_grads(d, n, _p(pts), _p(pdf), _p(feats), cin, m, _p(samples), _p(neighbors),
+                                             _p(start_ids), _p(radii), _p(axis_proj), _p(axis_bias), hidden, n_mlps,
+                                             _p(weights), cout, _p(in_grads), d_w.data_ptr(), d_f.data_ptr(),
+                                             d_a.data_ptr(), d_b.data_ptr(), d_pdf.data_ptr(), d_p.data_ptr(),
+                                             d_s.data_ptr(), ws.data_ptr(), ws.numel(), _stream()), "mc_conv_grads")
+    return [d_w, d_f, d_a, d_b, d_pdf, d_p, d_s]

@@ -45,6 +45,11 @@ def kp_case(clouds, c, normal_feats=False):
     k = c["k"]
     table_k = k if k in (8, 16, 32, 64) else 16
     kpts, sigma = prepare_kernel_points(c["dims"], table_k)
+    if True:
+        # The shell point(s) closest to the centre lie at distance exactly sigma from it (in the
+        # reference's tables too), so every self pair (offset 0) sits on the kink of the clamp and
+        # float32 / float64 evaluations pick different sides.  Pull the shell points in a little.
+        kpts = kpts * np.random.RandomState(1).uniform(0.85, 0.99, size=(kpts.shape[0], 1)).astype(np.float32)
     out["kernel_pts"], out["sigma"] = np.ascontiguousarray(kpts[:k]), sigma
     out["weights"] = out["rs"].normal(0.0, np.sqrt(2.0 / (c["cin"] * k)), size=(k * c["cin"], c["cout"])).astype(np.float32)
     return out

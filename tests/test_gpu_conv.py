@@ -51,3 +51,61 @@ def test_mcconv_forward(ref_clouds, c, num_mlps):
     # MCConv outputs scale with 1/pdf: compare relative to the output's magnitude as well
     scale = max(1.0, float(np.abs(expect).max()))
     assert close(got / scale, expect / scale)
+
+
+def grads_close(got, expect, tol=2e-4):
+    """Gradients are compared relative to the largest entry of the tensor: sums of thousands of
+    float reductions in arbitrary order against a float64 oracle."""
+    got, expect = np.asarray(got, np.float64), np.asarray(expect, np.float64)
+    scale = np.abs(expect).max() + 1e-30
+    return float(np.abs(got - expect).max()) <= tol * scale
+
+
+@pytest.mark.parametrize("c", KP_CASES + EXTRA_KP_CASES[:3], ids=_id)
+def test_kpconv_grads(ref_clouds, c):
+    from pccnn_lib_b200 import ops
+    case = kp_case(ref_clouds, c, normal_feats=True)
+    g = np.random.RandomState(9).normal(size=(case["samples"].shape[0], c["cout"])).astype(np.float32)
+    got = ops.kp_conv_grads(dev(case["pts"]), dev(case["feats"]), dev(case["samples"]), dev(case["neighbors"]),
+                            dev(case["start_ids"]), dev(case["radii"]), dev(case["kernel_pts"]), case["sigma"],
+                            dev(case["weights"]), dev(g))
+    expect = conv_oracle.kp_conv_grads(case["pts"], case["feats"], case["samples"], case["neighbors"],
+                                       case["start_ids"], case["radii"], case["kernel_pts"], case["sigma"],
+                                       case["weights"], g)
+    for name, a, b in zip(["weights", "features", "kernel_pts", "pts", "samples"], got, expect):
+        assert grads_close(a.cpu().numpy(), b.numpy()), name
+
+
+@pytest.mark.parametrize("c", MC_CASES, ids=_id)
+def test_mcconv_grads(ref_clouds, c):
+    from pccnn_lib_b200 import ops
+    case = mc_case(ref_clouds, c, normal_feats=True)
+    g = np.random.RandomState(10).normal(size=(case["samples"].shape[0], c["cout"])).astype(np.float32)
+    got = ops.mc_conv_grads(dev(case["pts"]), dev(case["pdf"]), dev(case["feats"]), dev(case["samples"]),
+                            dev(case["neighbors"]), dev(case["start_ids"]), dev(case["radii"]), dev(case["axis"]),
+                            dev(case["bias"]), dev(case["weights"]), dev(g))
+    expect = conv_oracle.mc_conv_grads(case["pts"], case["pdf"], case["feats"], case["samples"], case["neighbors"],
+                                       case["start_ids"], case["radii"], case["axis"], case["bias"], case["weights"], g)
+    for name, a, b in zip(["weights", "features", "axis", "bias", "pdf", "pts", "samples"], got, expect):
+        assert grads_close(a.cpu().numpy(), b.numpy().reshape(a.shape)), name
+
+
+def test_layers_run_end_to_end_with_autograd(ref_clouds):
+    # The mirrored classes: Pointcloud -> compute_pdf -> MCConv / KPConv -> backward through the op wrappers.
+    import pccnn_lib_b200 as lib
+    from conftest import ref_case
+    pts, batch_ids = ref_case(ref_clouds, 4, 250, 3)
+    device = torch.device("cuda:0")
+    pc = lib.pc.Pointcloud(pts, batch_ids, device=device)
+    feats = torch.randn(pts.shape[0], 8, device=device, requires_grad=True)
+    radius = np.full((3,), 0.2, np.float32)
+    pc.compute_pdf(np.full((3,), 0.1, np.float32))
+    torch.manual_seed(0)
+    kp = lib.pc.layers.KPConv(3, 8, 16, 16).to(device)
+    mc = lib.pc.layers.MCConv(3, 16, 8, 16).to(device)
+    out1, neighborhood = kp(pc, pc, feats, radius)
+    out2 = mc(pc, pc, out1, radius, neighborhood)
+    out2.square().mean().backward()
+    assert out2.shape == (pts.shape[0], 8) and torch.isfinite(out2).all()
+    for p in [feats, kp.conv_weights_, mc.conv_weights_, mc.proj_axis_, mc.proj_bias_]:
+        assert p.grad is not None and torch.isfinite(p.grad).all() and p.grad.abs().sum() > 0

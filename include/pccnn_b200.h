@@ -176,6 +176,29 @@ int pccnn_poisson_disk_sampling(int D, int64_t n, const int64_t* sorted_keys, co
                                 int64_t* out_count_host, void* workspace, size_t workspace_bytes,
                                 void* stream);
 
+/* Poisson-disk sampling for callers that cannot allocate device memory.  No counterpart in the
+ * reference (every op there allocates its own temporaries through torch).
+ *
+ * Some hosts may not call cudaMalloc while this library runs: a serving process that hands all
+ * device memory to a pool of its own at start-up, so that a later cudaMalloc would simply fail;
+ * a plugin whose execute callback is forbidden to allocate by the host's contract; a control
+ * loop with a latency budget, for which the device-wide synchronisation and driver locks of
+ * cudaMalloc / cudaFree are unacceptable.  This variant takes inputs and outputs only;
+ * its scratch is a fixed array inside the library (14 MiB per GPU that loads the library, held
+ * until the process exits), enough for n <= pccnn_poisson_disk_sampling_static_max_points()
+ * = 1 048 576 points.  Larger n is rejected with PCCNN_ERR_INVALID and a message that names the
+ * limit.  It calls neither cudaMalloc / cudaFree nor any allocating library routine.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ * that first call before starting any stream capture.  All calls share the one array, which
+ * keeps the previous call's contents: the function clears what it needs itself, but two calls
+ * that overlap on the GPU (different streams or threads) race on it -- run them one after another.
+ * Result and arguments are those of pccnn_poisson_disk_sampling. */
+int64_t pccnn_poisson_disk_sampling_static_max_points(void);
+int pccnn_poisson_disk_sampling_static(int D, int64_t n, const int64_t* sorted_keys, const int32_t* neighbors,
+                                       const int32_t* start_ids, const int32_t* grid_size,
+                                       int64_t* out_selected, int64_t* out_count_host, void* stream);
+
 /* ------------------------------------------------------------------------- */
 /* Point convolutions                                                         */
 /* ------------------------------------------------------------------------- */

@@ -15,6 +15,8 @@
 #include <cub/device/device_select.cuh>
 #include <thrust/iterator/counting_iterator.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace pccnn {
@@ -138,6 +140,49 @@ int pccnn_poisson_disk_sampling(int D, int64_t n, const int64_t* sorted_keys, co
     PCCNN_CUDA(cudaStreamSynchronize(s));
     *out_count_host = count;
     return PCCNN_OK;
+}
+
+// ---- variant for callers that cannot allocate device memory ---------------------------------
+// Scratch of the variant below: a fixed array inside the library image.  Every GPU that loads the
+// library keeps these bytes until the process exits.
+constexpr int64_t kStaticPdsMaxPoints = 1 << 20;
+constexpr size_t kStaticPdsBytes = (size_t)14 << 20;
+static __device__ __align__(256) unsigned char g_pds_static_scratch[kStaticPdsBytes];
+
+int64_t pccnn_poisson_disk_sampling_static_max_points(void) { return kStaticPdsMaxPoints; }
+
+int pccnn_poisson_disk_sampling_static(int D, int64_t n, const int64_t* sorted_keys, const int32_t* neighbors,
+                                       const int32_t* start_ids, const int32_t* grid_size, int64_t* out_selected,
+                                       int64_t* out_count_host, void* stream) {
+    PCCNN_CHECK_ARG(out_count_host, "poisson_disk_sampling_static: null out_count_host");
+    *out_count_host = 0;
+    if (n > kStaticPdsMaxPoints || pds_layout(n < 0 ? 0 : n).total > kStaticPdsBytes) {
+        set_error("poisson_disk_sampling_static: %lld points exceed the built-in scratch (at most %lld points); "
+                  "use pccnn_poisson_disk_sampling with a caller-provided workspace",
+                  (long long)n, (long long)kStaticPdsMaxPoints);
+        return PCCNN_ERR_INVALID;
+    }
+    // In host code the array's name is only a handle; the device address has to be asked for, once
+    // per device, with that device current.
+    static void* device_ptr[64];
+    static std::mutex mu;
+    int dev = 0;
+    PCCNN_CUDA(cudaGetDevice(&dev));
+    PCCNN_CHECK_ARG(dev >= 0 && dev < 64, "poisson_disk_sampling_static: device index %d not supported", dev);
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!device_ptr[dev]) {
+            void* p = nullptr;
+            PCCNN_CUDA(cudaGetSymbolAddress(&p, g_pds_static_scratch));
+            device_ptr[dev] = p;
+        }
+        scratch = device_ptr[dev];
+    }
+    // Same implementation as the workspace variant; it zeroes the selection flags and re-initialises
+    // the compaction state itself, so nothing of the previous call's contents is read.
+    return pccnn_poisson_disk_sampling(D, n, sorted_keys, neighbors, start_ids, grid_size, out_selected,
+                                       out_count_host, scratch, kStaticPdsBytes, stream);
 }
 
 }  // extern "C"

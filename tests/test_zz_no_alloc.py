@@ -1,0 +1,71 @@
+"""The allocation-free Poisson-disk entry point must return exactly what the workspace variant
+returns.  It exists for hosts that may not call cudaMalloc around this library (a server that gave
+all device memory to its own pool, a plugin callback that is forbidden to allocate, a loop with a
+latency budget), so the test drives it through the C ABI with
+nothing but input and output pointers, twice in a row on different inputs: the second call finds
+the first call's leftovers in the built-in scratch and must not be disturbed by them.
+
+This file sorts last on purpose: a run that stops at the first failure has then already run every
+other test.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ref_case
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(ref_clouds, batch, num_pts, radius):
+    from gpu_helpers import gpu_grid
+    from pccnn_lib_b200 import ops
+    pts, batch_ids = ref_case(ref_clouds, batch, num_pts, 3)
+    g = gpu_grid(pts, batch_ids, batch, np.full((3,), radius, np.float32))
+    neigh, start_ids = ops.find_neighbors(g["sorted_pts"], g["sorted_keys"], g["sorted_pts"], g["sorted_keys"],
+                                          g["grid_ds"], g["num_cells"], g["cell"], 0)
+    return g, neigh, start_ids
+
+
+def _run_both(g, neigh, start_ids):
+    from pccnn_lib_b200 import _capi
+    lib = _capi.lib
+    n = g["sorted_keys"].shape[0]
+    stream = torch.cuda.current_stream().cuda_stream
+    args = (3, n, g["sorted_keys"].data_ptr(), neigh.data_ptr(), start_ids.data_ptr(), g["num_cells"].data_ptr())
+
+    ref_out = torch.full((n,), -1, dtype=torch.int64, device="cuda")
+    ref_count = ctypes.c_int64(0)
+    ws = torch.empty(lib.pccnn_poisson_disk_sampling_workspace_bytes(n), dtype=torch.uint8, device="cuda")
+    _capi.check(lib.pccnn_poisson_disk_sampling(*args, ref_out.data_ptr(), ctypes.byref(ref_count), ws.data_ptr(),
+                                                ws.numel(), stream), "workspace variant")
+
+    out = torch.full((n,), -1, dtype=torch.int64, device="cuda")
+    count = ctypes.c_int64(0)
+    _capi.check(lib.pccnn_poisson_disk_sampling_static(*args, out.data_ptr(), ctypes.byref(count), stream),
+                "allocation-free variant")
+    torch.cuda.synchronize()
+    return ref_out[:ref_count.value].cpu(), out[:count.value].cpu()
+
+
+def test_allocation_free_variant_matches_on_two_calls_in_a_row(ref_clouds):
+    first = _case(ref_clouds, 8, 1000, 0.1)
+    second = _case(ref_clouds, 16, 700, 0.05)
+    for case in (first, second):
+        expect, got = _run_both(*case)
+        assert expect.numel() > 0
+        assert torch.equal(expect, got)  # integer output: exact
+
+
+def test_allocation_free_variant_rejects_sizes_beyond_its_scratch():
+    from pccnn_lib_b200 import _capi
+    lib = _capi.lib
+    limit = lib.pccnn_poisson_disk_sampling_static_max_points()
+    assert limit == 1 << 20
+    count = ctypes.c_int64(7)
+    rc = lib.pccnn_poisson_disk_sampling_static(3, limit + 1, None, None, None, None, None, ctypes.byref(count), None)
+    assert rc == 1 and count.value == 0
+    message = _capi.last_error()
+    assert "exceed" in message and str(limit) in message

@@ -353,6 +353,161 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+# ---- convolution workloads (the other configurations of the baseline; run with --workload) ------
+def scene_cloud(seed, num_pts):
+    """Room-like scene: floor and four walls of a 20 x 20 x 3 m box plus 50-200 primitives resting
+    on the floor, sampling density modulated 1-4x by a smooth field over (x, y)."""
+    rs = np.random.RandomState(5000 + seed)
+    parts = []
+    n_struct = num_pts // 2
+    per = n_struct // 5
+    xy = rs.uniform(0, 20, size=(per, 2))
+    parts.append(np.concatenate([xy, np.zeros((per, 1))], 1))
+    for wall in range(4):
+        u, h = rs.uniform(0, 20, size=(per, 1)), rs.uniform(0, 3, size=(per, 1))
+        fixed = np.full((per, 1), 0.0 if wall % 2 == 0 else 20.0)
+        parts.append(np.concatenate([u, fixed, h] if wall < 2 else [fixed, u, h], 1))
+    k = rs.randint(50, 201)
+    n_obj = num_pts - 5 * per
+    counts = np.full(k, n_obj // k)
+    counts[0] += n_obj - counts.sum()
+    for i in range(k):
+        s = rs.uniform(0.2, 1.5)
+        c = np.array([rs.uniform(1, 19), rs.uniform(1, 19), s])
+        v = rs.normal(size=(int(counts[i]), 3))
+        if rs.rand() < 0.5:
+            p = v / np.linalg.norm(v, axis=1, keepdims=True) * s
+        else:
+            p = rs.uniform(-s, s, size=(int(counts[i]), 3))
+            ax = rs.randint(0, 3, size=int(counts[i]))
+            p[np.arange(int(counts[i])), ax] = np.where(rs.rand(int(counts[i])) < 0.5, -s, s)
+        parts.append(p + c)
+    pts = np.concatenate(parts, 0)
+    # density field: keep a point with probability field/4, then resample to the requested size
+    field = 2.5 + 1.5 * np.sin(pts[:, 0] * 0.3) * np.cos(pts[:, 1] * 0.3)
+    keep = rs.rand(pts.shape[0]) < field / 4.0
+    pts = pts[keep]
+    pts = pts[rs.randint(0, pts.shape[0], size=num_pts)] + rs.normal(0, 0.004, size=(num_pts, 3))
+    return pts.astype(np.float32)
+
+
+CONV_WORKLOADS = {
+    # name: (description, builder kwargs)
+    "kpconv_cfg0": dict(desc="KPConv single layer forward: 1 cloud x 4096 uniform points, Cin 16, Cout 32, 16 kernel "
+                             "points, radius 0.1", kind="kp", clouds=1, pts=4096, gen="cube", radius=0.1, cin=16,
+                        cout=32, k=16, backward=False, pool=None),
+    "mcconv_cfg2": dict(desc="MCConv forward+backward: 32 clouds x 32768 surface points, outputs Poisson-disk radius "
+                             "0.03, conv radius 0.075, Cin 64, Cout 128, hidden 16, pdf bandwidth 0.015", kind="mc",
+                        clouds=32, pts=32768, gen="surface", radius=0.075, cin=64, cout=128, k=16, backward=True,
+                        pool=0.03, bw=0.015),
+    "kpconv_scene": dict(desc="KPConv forward+backward on one room-like scene of 2M points, radius 0.1 m, Cin 128, "
+                              "Cout 128, 16 kernel points (one GPU's share of the large-scene configuration)",
+                         kind="kp", clouds=1, pts=2000000, gen="scene", radius=0.1, cin=128, cout=128, k=16,
+                         backward=True, pool=None),
+    "mcconv_scene": dict(desc="MCConv forward+backward on one room-like scene of 2M points, radius 0.1 m, Cin 128, "
+                              "Cout 128, hidden 16, pdf bandwidth 0.02 m", kind="mc", clouds=1, pts=2000000,
+                         gen="scene", radius=0.1, cin=128, cout=128, k=16, backward=True, pool=None, bw=0.02),
+}
+
+
+def run_conv_workload(args):
+    import torch
+    import pccnn_lib_b200 as lib
+    from pccnn_lib_b200 import ops
+    from pccnn_lib_b200.pc.layers import prepare_kernel_points
+    w = CONV_WORKLOADS[args.workload]
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    rs = np.random.RandomState(77)
+    if w["gen"] == "cube":
+        pts = np.random.RandomState(1000).rand(w["pts"], 3).astype(np.float32)
+        ids = np.zeros(w["pts"], np.int32)
+    elif w["gen"] == "surface":
+        pts, ids = make_batch(0, w["clouds"], w["pts"])
+    else:
+        pts, ids = scene_cloud(0, w["pts"]), np.zeros(w["pts"], np.int32)
+    radius = np.full((3,), w["radius"], np.float32)
+    pc = lib.pc.Pointcloud(pts, ids, device=device)
+    t0 = time.perf_counter()
+    pc_out = pc
+    if w["pool"]:
+        pool = lib.pc.PointPooling(pc, np.full((3,), w["pool"], np.float32))
+        pc_out = lib.pc.Pointcloud(pool.pool_tensor(pc.pts_), pool.pool_tensor(pc.batch_ids_))
+    bb = lib.pc.BoundingBox(pc)
+    grid = lib.pc.Grid(pc, bb, radius)
+    grid.compute_cell_ids()
+    grid.build_ds()
+    nb = lib.pc.Neighborhood(grid, pc_out, 0)
+    pdf = None
+    if w["kind"] == "mc":
+        pc.compute_pdf(np.full((3,), w["bw"], np.float32))
+        pdf = (pc.pts_unnorm_pdf_ * float(np.prod(radius))).contiguous()
+    torch.cuda.synchronize()
+    setup_s = time.perf_counter() - t0
+    n, m, t = pts.shape[0], pc_out.pts_.shape[0], nb.neighbors_.shape[0]
+    cin, cout, k = w["cin"], w["cout"], w["k"]
+    feats = torch.as_tensor(rs.normal(size=(n, cin)).astype(np.float32), device=device)
+    rad = torch.as_tensor(radius, device=device)
+    grads = torch.as_tensor(rs.normal(size=(m, cout)).astype(np.float32), device=device)
+    if w["kind"] == "kp":
+        kp, sigma = prepare_kernel_points(3, k)
+        kpts = torch.as_tensor(kp, device=device)
+        weights = torch.as_tensor(rs.normal(0, np.sqrt(1.0 / (15 * cin)), size=(k * cin, cout)).astype(np.float32), device=device)
+        fwd = lambda: ops.kp_conv(pc.pts_, feats, pc_out.pts_, nb.neighbors_, nb.start_ids_, rad, kpts, sigma, weights)
+        bwd = lambda: ops.kp_conv_grads(pc.pts_, feats, pc_out.pts_, nb.neighbors_, nb.start_ids_, rad, kpts, sigma, weights, grads)
+    else:
+        axis = torch.as_tensor(rs.normal(0, np.sqrt(1 / 3.0), size=(3, k)).astype(np.float32), device=device)
+        bias = torch.zeros((1, k), dtype=torch.float32, device=device)
+        weights = torch.as_tensor(rs.normal(0, np.sqrt(1.0 / (cin * k)), size=(1, k * cin, cout)).astype(np.float32), device=device)
+        fwd = lambda: ops.mc_conv(pc.pts_, pdf, feats, pc_out.pts_, nb.neighbors_, nb.start_ids_, rad, axis, bias, weights)
+        bwd = lambda: ops.mc_conv_grads(pc.pts_, pdf, feats, pc_out.pts_, nb.neighbors_, nb.start_ids_, rad, axis, bias, weights, grads)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    warm = max(args.warmup, 3)
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    fwd_ms = timed(fwd, args.steps, warm)
+    bwd_ms = timed(bwd, args.steps, warm) if w["backward"] else 0.0
+    clocks = sampler.finish()
+    # the contraction alone, on the same shapes, for the tensor-core roofline
+    inner = cin * k
+    a = torch.randn(min(m, 1 << 17), inner, device=device)
+    bmat = torch.randn(cout, inner, device=device)
+    gemm_ms = timed(lambda: ops.gemm_f32(a, bmat, split=True), args.steps, warm)
+    # (includes the fp32 -> bf16 split of both operands; the tensor-core kernel is a part of it)
+    flops = 2.0 * a.shape[0] * inner * cout * 3
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    tc_peak = float(json.load(open(peaks_path))["bf16_tflops"]) if os.path.exists(peaks_path) else 1590.0
+    step_ms = fwd_ms + bwd_ms
+    line = {
+        "metric": "conv-layer points/s (%s)" % ("forward+backward" if w["backward"] else "forward"),
+        "value": m / (step_ms * 1e-3), "unit": "points/s", "n_gpus": 1, "steps": args.steps, "warmup": warm,
+        "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 (bf16 hi/lo split on tensor cores, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": w["desc"], "points": n, "samples": m, "pairs": t, "neighbors_per_sample": t / max(m, 1),
+                   "forward_ms": fwd_ms, "backward_ms": bwd_ms, "setup_s_untimed": setup_s,
+                   "useful_contraction_flop_per_step": 2.0 * m * inner * cout * (3 if w["backward"] else 1),
+                   "projection_flop_per_step": 2.0 * t * inner * (2 if w["backward"] else 1)},
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "gemm_bf16_kernel (3 bf16 passes) incl. operand split",
+                     "achieved": round(flops / (gemm_ms * 1e-3) / 1e12, 2), "peak": tc_peak, "unit": "TFLOP/s",
+                     "frac": round(flops / (gemm_ms * 1e-3) / 1e12 / tc_peak, 4), "traffic": None,
+                     "rows": int(a.shape[0]), "ms": gemm_ms},
+    }
+    print(json.dumps(line))
+
+
 # ---- CPU arm ------------------------------------------------------------------------------------
 def cpu_step(pts, batch_ids, num_clouds):
     """The same step on the CPU oracle.  Returns the number of neighbor pairs."""
@@ -417,10 +572,14 @@ def main():
     ap.add_argument("--clouds", type=int, default=CLOUDS_PER_RANK,
                     help="clouds per GPU (default: the full workload; smaller values are for profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
+    ap.add_argument("--workload", default="neighbors_kde", choices=["neighbors_kde"] + sorted(CONV_WORKLOADS),
+                    help="neighbors_kde is the headline workload; the others time one convolution layer")
     args = ap.parse_args()
     globals()["CLOUDS_PER_RANK"] = args.clouds
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "neighbors_kde":
+        run_conv_workload(args)
     else:
         run_b200(args)
 

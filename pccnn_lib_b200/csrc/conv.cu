@@ -64,11 +64,12 @@ struct KPBasis {
     // 1 / (dist + 1e-6)).  db = dL/db[k]; adds to d_off = dL/d(offset) and, through shared-memory
     // float reductions, to s_grad laid out like the kernel points [K, D].
     static constexpr int kGradFloats = KP * D;
+    // Called by all 32 lanes (inactive lanes pass active = false): the parameter gradients of the 32
+    // pairs are summed with shuffles and lane 0 adds one value per entry to s_grad.
     __device__ static void grad(const float* sp, const KPBasisArgs& a, int K, const float (&d)[D], int /*n0*/,
-                                const float* db, float (&d_off)[D], float* s_grad, float& /*d_pdf*/) {
-#pragma unroll
-        for (int k = 0; k < KP; ++k) {
-            if (k >= K) break;
+                                bool active, const float* db, float (&d_off)[D], float* s_grad, float& /*d_pdf*/) {
+        const int lane = lane_id();
+        for (int k = 0; k < K; ++k) {
             float v[D], acc = 0.f;
 #pragma unroll
             for (int x = 0; x < D; ++x) {
@@ -76,16 +77,15 @@ struct KPBasis {
                 acc = fmaf(v[x], v[x], acc);
             }
             const float dist = sqrtf(fmaxf(acc, 0.f));
-            if (1.0f - dist * a.inv_sigma >= 0.f) {
-                const float gk = -db[k] * a.inv_sigma / (dist + 1e-6f);
-                if (gk != 0.f) {
+            float gk = 0.f;
+            if (active && 1.0f - dist * a.inv_sigma >= 0.f) gk = -db[k] * a.inv_sigma / (dist + 1e-6f);
+            if (!__any_sync(kFullMask, gk != 0.f)) continue;
 #pragma unroll
-                    for (int x = 0; x < D; ++x) {
-                        const float t = gk * v[x];
-                        atomicAdd(s_grad + k * D + x, t);
-                        d_off[x] -= t;
-                    }
-                }
+            for (int x = 0; x < D; ++x) {
+                const float t = gk * v[x];
+                d_off[x] -= t;
+                const float tot = warp_sum(t);
+                if (lane == 0) atomicAdd(s_grad + k * D + x, tot);
             }
         }
     }
@@ -123,25 +123,26 @@ struct MLPBasis {
     // gradient [D, KP] followed by the bias gradient [KP].
     static constexpr int kGradFloats = (D + 1) * KP;
     __device__ static void grad(const float* sp, const MLPBasisArgs& a, int K, const float (&d)[D], int n0,
-                                const float* db, float (&d_off)[D], float* s_grad, float& d_pdf) {
-        const float inv_pdf = 1.0f / __ldg(a.pdf + n0);
-#pragma unroll
-        for (int k = 0; k < KP; ++k) {
-            if (k >= K) break;
+                                bool active, const float* db, float (&d_off)[D], float* s_grad, float& d_pdf) {
+        const int lane = lane_id();
+        const float inv_pdf = active ? 1.0f / __ldg(a.pdf + n0) : 0.f;
+        for (int k = 0; k < K; ++k) {
             float pre = 0.f;
 #pragma unroll
             for (int x = 0; x < D; ++x) pre = fmaf(d[x], sp[x * KP + k], pre);
             pre += sp[D * KP + k];
             const float act = pre > 0.f ? pre : 0.2f * pre;
-            d_pdf -= act * db[k] * inv_pdf * inv_pdf;
-            const float cur = db[k] * inv_pdf * (act > 0.f ? 1.0f : 0.2f);
-            if (cur != 0.f) {
-                atomicAdd(s_grad + D * KP + k, cur);
+            const float dbk = active ? db[k] : 0.f;
+            d_pdf -= act * dbk * inv_pdf * inv_pdf;
+            const float cur = dbk * inv_pdf * (act > 0.f ? 1.0f : 0.2f);
+            if (!__any_sync(kFullMask, cur != 0.f)) continue;
+            const float tot_b = warp_sum(cur);
+            if (lane == 0) atomicAdd(s_grad + D * KP + k, tot_b);
 #pragma unroll
-                for (int x = 0; x < D; ++x) {
-                    atomicAdd(s_grad + x * KP + k, d[x] * cur);
-                    d_off[x] = fmaf(cur, sp[x * KP + k], d_off[x]);
-                }
+            for (int x = 0; x < D; ++x) {
+                d_off[x] = fmaf(cur, sp[x * KP + k], d_off[x]);
+                const float tot = warp_sum(d[x] * cur);
+                if (lane == 0) atomicAdd(s_grad + x * KP + k, tot);
             }
         }
     }
@@ -154,16 +155,17 @@ struct MLPBasis {
 };
 
 // P[m, c*K + k] for the samples [m_begin, m_end), written as bf16 hi (+ lo) rows of ld_p elements.
-template <int D, int KP, class BASIS, class ARGS>
+template <int D, int KP, int CPL, class BASIS, class ARGS>
 __global__ void __launch_bounds__(conv_warps<KP>() * 32)
 project_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __restrict__ feats, int cin,
                const float* __restrict__ samples, const int2* __restrict__ neighbors,
                const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
                __nv_bfloat16* __restrict__ p_hi, __nv_bfloat16* __restrict__ p_lo, int ld_p) {
-    constexpr int CPL = 64 / KP;  // channels per lane
+    // CPL = channels per lane: at most 64 / KP, fewer when Cin does not fill 32 * CPL channels
     constexpr int kConvWarps = conv_warps<KP>();
     __shared__ float s_params[BASIS::kParamFloats];
-    __shared__ float s_basis[kConvWarps][32][KP + 1];
+    // rows of KP + 4 floats: 16-byte aligned, and 128-bit stores of 8 consecutive lanes hit distinct banks
+    __shared__ __align__(16) float s_basis[kConvWarps][32][KP + 4];
     __shared__ int s_n0[kConvWarps][32];
     BASIS::load_params(s_params, args, K);
     __syncthreads();
@@ -199,22 +201,36 @@ project_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __r
                     for (int x = 0; x < D; ++x) d[x] = (__ldg(pts + (int64_t)n0 * D + x) - s[x]) * inv[x];
                     BASIS::eval(s_params, args, K, d, n0, b);
 #pragma unroll
-                    for (int k = 0; k < KP; ++k) s_basis[warp][lane][k] = b[k];
+                    for (int k = 0; k < KP; k += 4)
+                        *reinterpret_cast<float4*>(&s_basis[warp][lane][k]) = make_float4(b[k], b[k + 1], b[k + 2], b[k + 3]);
                     s_n0[warp][lane] = n0;
                 }
                 __syncwarp();
-                // Lanes as channels: stream the feature rows of the staged neighbors.
+                // Lanes as channels: stream the feature rows of the staged neighbors, four neighbors
+                // per step so that 4 * CPL independent loads are in flight before the FMAs need them.
                 const int cnt = min(32, hi - t0);
-                for (int j = 0; j < cnt; ++j) {
-                    const float* frow = feats + (int64_t)s_n0[warp][j] * cin + cb + lane;
-                    float f[CPL];
+                for (int j0 = 0; j0 < cnt; j0 += 4) {
+                    float f[4][CPL];
 #pragma unroll
-                    for (int i = 0; i < CPL; ++i) f[i] = (cb + i * 32 + lane < cin) ? __ldg(frow + i * 32) : 0.f;
+                    for (int u = 0; u < 4; ++u) {
+                        const int j = min(j0 + u, cnt - 1);
+                        const float* frow = feats + (int64_t)s_n0[warp][j] * cin + cb + lane;
 #pragma unroll
-                    for (int k = 0; k < KP; ++k) {
-                        const float bk = s_basis[warp][j][k];
+                        for (int i = 0; i < CPL; ++i)
+                            f[u][i] = (j0 + u < cnt && cb + i * 32 + lane < cin) ? __ldg(frow + i * 32) : 0.f;
+                    }
 #pragma unroll
-                        for (int i = 0; i < CPL; ++i) acc[i][k] = fmaf(f[i], bk, acc[i][k]);
+                    for (int u = 0; u < 4; ++u) {
+                        const int j = min(j0 + u, cnt - 1);
+#pragma unroll
+                        for (int k = 0; k < KP; k += 4) {
+                            const float4 b4 = *reinterpret_cast<const float4*>(&s_basis[warp][j][k]);
+                            const float bk[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                                for (int i = 0; i < CPL; ++i) acc[i][k + q] = fmaf(f[u][i], bk[q], acc[i][k + q]);
+                        }
                     }
                 }
                 __syncwarp();
@@ -279,7 +295,7 @@ __device__ __forceinline__ void warp_reduce_scatter(float (&v)[KP], int lane, in
 //     dPts[n0]   += d(offset) / radii,   dSamples[m] = -sum_t d(offset) / radii
 // A warp owns a sample.  The lanes alternate between "32 neighbors" (basis, basis gradient) and
 // "32 channels x CPL" (the two contractions against the sample's dP row held in registers).
-template <int D, int KP, class BASIS, class ARGS>
+template <int D, int KP, int CPL, class BASIS, class ARGS>
 __global__ void __launch_bounds__(conv_warps<KP>() * 32)
 backward_pairs_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __restrict__ feats, int cin,
                       const float* __restrict__ samples, const int2* __restrict__ neighbors,
@@ -287,11 +303,10 @@ backward_pairs_kernel(ARGS args, int K, const float* __restrict__ pts, const flo
                       const float* __restrict__ d_proj, float* __restrict__ d_feat, float* __restrict__ d_pts,
                       float* __restrict__ d_samples, float* __restrict__ d_param0, float* __restrict__ d_param1,
                       float* __restrict__ d_pdf) {
-    constexpr int CPL = 64 / KP;
     constexpr int kConvWarps = conv_warps<KP>();
     __shared__ float s_params[BASIS::kParamFloats];
     __shared__ float s_grad[BASIS::kGradFloats];
-    __shared__ float s_basis[kConvWarps][32][KP + 1];
+    __shared__ __align__(16) float s_basis[kConvWarps][32][KP + 4];
     __shared__ float s_db[kConvWarps][32][KP + 1];
     __shared__ int s_n0[kConvWarps][32];
     BASIS::load_params(s_params, args, K);
@@ -329,7 +344,8 @@ backward_pairs_kernel(ARGS args, int K, const float* __restrict__ pts, const flo
                 for (int x = 0; x < D; ++x) d[x] = (__ldg(pts + (int64_t)n0 * D + x) - s[x]) * inv[x];
                 BASIS::eval(s_params, args, K, d, n0, b);
 #pragma unroll
-                for (int k = 0; k < KP; ++k) s_basis[warp][lane][k] = b[k];
+                for (int k = 0; k < KP; k += 4)
+                    *reinterpret_cast<float4*>(&s_basis[warp][lane][k]) = make_float4(b[k], b[k + 1], b[k + 2], b[k + 3]);
                 s_n0[warp][lane] = n0;
             }
 #pragma unroll
@@ -343,51 +359,74 @@ backward_pairs_kernel(ARGS args, int K, const float* __restrict__ pts, const flo
 #pragma unroll
                 for (int i = 0; i < CPL; ++i) {
                     const int c = cb + i * 32 + lane;
+                    if (K == KP && (KP % 4) == 0) {
 #pragma unroll
-                    for (int k = 0; k < KP; ++k) g[i][k] = (c < cin && k < K) ? __ldg(grow + (size_t)c * K + k) : 0.f;
+                        for (int k = 0; k < KP; k += 4) {
+                            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (c < cin) v = __ldg(reinterpret_cast<const float4*>(grow + (size_t)c * K + k));
+                            g[i][k] = v.x; g[i][k + 1] = v.y; g[i][k + 2] = v.z; g[i][k + 3] = v.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < KP; ++k) g[i][k] = (c < cin && k < K) ? __ldg(grow + (size_t)c * K + k) : 0.f;
+                    }
                 }
-                for (int j = 0; j < cnt; ++j) {
-                    const int nj = s_n0[warp][j];
-                    const float* frow = feats + (int64_t)nj * cin + cb + lane;
-                    float f[CPL], df[CPL], pb[KP];
+                for (int j0 = 0; j0 < cnt; j0 += 2) {
+                    float f[2][CPL];
+                    int nj[2];
 #pragma unroll
-                    for (int i = 0; i < CPL; ++i) {
-                        f[i] = (cb + i * 32 + lane < cin) ? __ldg(frow + i * 32) : 0.f;
-                        df[i] = 0.f;
+                    for (int u = 0; u < 2; ++u) {
+                        nj[u] = s_n0[warp][min(j0 + u, cnt - 1)];
+                        const float* frow = feats + (int64_t)nj[u] * cin + cb + lane;
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i)
+                            f[u][i] = (j0 + u < cnt && cb + i * 32 + lane < cin) ? __ldg(frow + i * 32) : 0.f;
                     }
 #pragma unroll
-                    for (int k = 0; k < KP; ++k) {
-                        const float bk = s_basis[warp][j][k];
-                        float acc = 0.f;
+                    for (int u = 0; u < 2; ++u) {
+                        if (j0 + u >= cnt) break;
+                        const int j = j0 + u;
+                        float df[CPL], pb[KP];
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i) df[i] = 0.f;
+#pragma unroll
+                        for (int k = 0; k < KP; k += 4) {
+                            const float4 b4 = *reinterpret_cast<const float4*>(&s_basis[warp][j][k]);
+                            const float bk[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                float acc = 0.f;
+#pragma unroll
+                                for (int i = 0; i < CPL; ++i) {
+                                    df[i] = fmaf(g[i][k + q], bk[q], df[i]);
+                                    acc = fmaf(g[i][k + q], f[u][i], acc);
+                                }
+                                pb[k + q] = acc;
+                            }
+                        }
 #pragma unroll
                         for (int i = 0; i < CPL; ++i) {
-                            df[i] = fmaf(g[i][k], bk, df[i]);
-                            acc = fmaf(g[i][k], f[i], acc);
+                            const int c = cb + i * 32 + lane;
+                            if (c < cin && df[i] != 0.f) atomicAdd(d_feat + (int64_t)nj[u] * cin + c, df[i]);
                         }
-                        pb[k] = acc;
-                    }
+                        int k0, n;
+                        warp_reduce_scatter<KP>(pb, lane, k0, n);
+                        // lanes whose low bits are zero speak for their group of identical sums
+                        if ((lane & ((32 / (KP < 32 ? KP : 32)) - 1)) == 0) {
 #pragma unroll
-                    for (int i = 0; i < CPL; ++i) {
-                        const int c = cb + i * 32 + lane;
-                        if (c < cin && df[i] != 0.f) atomicAdd(d_feat + (int64_t)nj * cin + c, df[i]);
-                    }
-                    int k0, n;
-                    warp_reduce_scatter<KP>(pb, lane, k0, n);
-                    // lanes whose low bits are zero speak for their group of identical sums
-                    if ((lane & ((32 / (KP < 32 ? KP : 32)) - 1)) == 0) {
-#pragma unroll
-                        for (int q = 0; q < (KP + 31) / 32; ++q) s_db[warp][j][k0 + q] += pb[q];
+                            for (int q = 0; q < (KP + 31) / 32; ++q) s_db[warp][j][k0 + q] += pb[q];
+                        }
                     }
                 }
                 __syncwarp();
             }
 
             // Lanes as neighbors again: basis gradient, offset gradient, point gradients.
-            if (t < hi) {
-                float d_off[D], dpdf = 0.f;
+            float d_off[D], dpdf = 0.f;
 #pragma unroll
-                for (int x = 0; x < D; ++x) d_off[x] = 0.f;
-                BASIS::grad(s_params, args, K, d, n0, s_db[warp][lane], d_off, s_grad, dpdf);
+            for (int x = 0; x < D; ++x) d_off[x] = 0.f;
+            BASIS::grad(s_params, args, K, d, n0, t < hi, s_db[warp][lane], d_off, s_grad, dpdf);
+            if (t < hi) {
 #pragma unroll
                 for (int x = 0; x < D; ++x) {
                     const float gx = d_off[x] * inv[x];
@@ -416,16 +455,25 @@ static int launch_backward_pairs(int K, const ARGS& args, const float* pts, cons
                                  cudaStream_t s) {
     const int count = m_end - m_begin;
     if (count <= 0) return PCCNN_OK;
-#define PCCNN_BACKWARD(KP)                                                                                          \
-    backward_pairs_kernel<D, KP, BASIS<D, KP>, ARGS>                                                                \
+#define PCCNN_BACKWARD_C(KP, CPL)                                                                                   \
+    backward_pairs_kernel<D, KP, CPL, BASIS<D, KP>, ARGS>                                                           \
         <<<grid_for((int64_t)count * 32, conv_warps<KP>() * 32, 4), conv_warps<KP>() * 32, 0, s>>>(                  \
         args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids, radii, m_begin, m_end, d_proj, d_feat, \
         d_pts, d_samples, d_param0, d_param1, d_pdf)
+#define PCCNN_BACKWARD(KP)                                                                                          \
+    do {                                                                                                            \
+        constexpr int kMax = 64 / KP;                                                                               \
+        if (kMax >= 8 && cin > 128) PCCNN_BACKWARD_C(KP, (kMax >= 8 ? 8 : kMax));                                    \
+        else if (kMax >= 4 && cin > 64) PCCNN_BACKWARD_C(KP, (kMax >= 4 ? 4 : kMax));                                \
+        else if (kMax >= 2 && cin > 32) PCCNN_BACKWARD_C(KP, (kMax >= 2 ? 2 : kMax));                                \
+        else PCCNN_BACKWARD_C(KP, 1);                                                                               \
+    } while (0)
     if (K <= 8) PCCNN_BACKWARD(8);
     else if (K <= 16) PCCNN_BACKWARD(16);
     else if (K <= 32) PCCNN_BACKWARD(32);
     else PCCNN_BACKWARD(64);
 #undef PCCNN_BACKWARD
+#undef PCCNN_BACKWARD_C
     PCCNN_LAUNCH_CHECK();
     return PCCNN_OK;
 }
@@ -436,16 +484,26 @@ static int launch_project(int K, const ARGS& args, const float* pts, const float
                           int m_end, void* p_hi, void* p_lo, int ld_p, cudaStream_t s) {
     const int count = m_end - m_begin;
     if (count <= 0) return PCCNN_OK;
-#define PCCNN_PROJECT(KP)                                                                                        \
-    project_kernel<D, KP, BASIS<D, KP>, ARGS>                                                                    \
-        <<<grid_for((int64_t)count * 32, conv_warps<KP>() * 32, 8), conv_warps<KP>() * 32, 0, s>>>(                                   \
-        args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids, radii, m_begin, m_end,             \
-        (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo, ld_p)
+    // channels per lane: the largest power of two <= 64 / KP that Cin can still fill
+#define PCCNN_PROJECT_C(KP, CPL)                                                                   \
+    project_kernel<D, KP, CPL, BASIS<D, KP>, ARGS>                                                 \
+        <<<grid_for((int64_t)count * 32, conv_warps<KP>() * 32, 8), conv_warps<KP>() * 32, 0, s>>>( \
+            args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids, radii, m_begin,  \
+            m_end, (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo, ld_p)
+#define PCCNN_PROJECT(KP)                                                        \
+    do {                                                                         \
+        constexpr int kMax = 64 / KP;                                            \
+        if (kMax >= 8 && cin > 128) PCCNN_PROJECT_C(KP, (kMax >= 8 ? 8 : kMax)); \
+        else if (kMax >= 4 && cin > 64) PCCNN_PROJECT_C(KP, (kMax >= 4 ? 4 : kMax)); \
+        else if (kMax >= 2 && cin > 32) PCCNN_PROJECT_C(KP, (kMax >= 2 ? 2 : kMax)); \
+        else PCCNN_PROJECT_C(KP, 1);                                             \
+    } while (0)
     if (K <= 8) PCCNN_PROJECT(8);
     else if (K <= 16) PCCNN_PROJECT(16);
     else if (K <= 32) PCCNN_PROJECT(32);
     else PCCNN_PROJECT(64);
 #undef PCCNN_PROJECT
+#undef PCCNN_PROJECT_C
     PCCNN_LAUNCH_CHECK();
     return PCCNN_OK;
 }

@@ -32,6 +32,9 @@ POINTS_PER_CLOUD = 100000
 RADIUS = 0.05
 BANDWIDTH = 0.01
 MAX_PAIRS_PER_CALL = (1 << 31) - 1  # int32 CSR offsets of the reference format
+# DRAM bytes per neighbor pair of the three heavy kernels, from one ncu capture of a 6-cloud case
+# (profiles/neighbors_kernel_pdf_kernel_6clouds_ncu.md); traffic grows in proportion to the pairs.
+NCU_DRAM_BYTES_PER_PAIR = {"neighbors_store": 10.30, "neighbors_count": 0.33, "kde": 8.10}
 
 
 # ---- synthetic clouds --------------------------------------------------------------------------
@@ -158,9 +161,11 @@ class Step:
         marks.append(self._mark())
         keys = ops.compute_keys(pts, batch_ids, mn, nc, self.cell)
         marks.append(self._mark())
-        skeys, sids, spts = ops.sort_keys(keys, 64, pts)
+        cells = nc.tolist()  # the one small device-to-host read the reference's wrapper also does
+        key_bits = max(1, int(np.ceil(np.log2(float(self.num_batches) * cells[0] * cells[1] * cells[2] + 1))))
+        skeys, sids, spts = ops.sort_keys(keys, key_bits, pts)
         marks.append(self._mark())
-        shape = [self.num_batches] + nc[0:2].tolist() + [2]
+        shape = [self.num_batches] + cells[0:2] + [2]
         ds = ops.build_grid_ds(skeys, nc, shape)
         marks.append(self._mark())
         state = ops.find_neighbors_count(spts, skeys, spts, skeys, ds, nc, self.cell, 0)
@@ -222,7 +227,8 @@ def run_b200(args):
     from pccnn_lib_b200 import _capi  # noqa: F401  (fails loudly if the CUDA library is missing)
 
     # Host data: this rank's clouds, in pinned memory for the end-to-end arm.
-    h_pts, h_ids = make_batch(rank * CLOUDS_PER_RANK, CLOUDS_PER_RANK)
+    # Every rank draws the same 16 clouds, so per-GPU work is identical at every N (weak scaling).
+    h_pts, h_ids = make_batch(0, CLOUDS_PER_RANK)
     hp = torch.from_numpy(h_pts).pin_memory()
     hb = torch.from_numpy(h_ids).pin_memory()
     d_pts, d_ids = hp.to(device), hb.to(device)
@@ -292,6 +298,7 @@ def run_b200(args):
         return pairs, ms, clocks
 
     warm = max(args.warmup, 3)
+    local_pairs = one_step(True)  # this rank's pairs per step
     pairs, ms, clocks = timed(True, args.steps, warm, True)
     stage_ms = step.stage_ms()
     e_pairs, e_ms, _ = timed(False, args.steps, warm, False)
@@ -308,7 +315,7 @@ def run_b200(args):
         peak, peak_src = 6650.0, "fallback"
 
     n_pts = CLOUDS_PER_RANK * POINTS_PER_CLOUD
-    t_rank = pairs / world / args.steps  # pairs of one step on one rank
+    t_rank = float(local_pairs)  # pairs of one step on this rank
     # Algorithmic bytes per launch: 8 B per pair written (store) / read (KDE) plus the per-point streams.
     algo = {
         "neighbors_store": 8.0 * t_rank + n_pts * (12 + 8 + 4),
@@ -321,7 +328,8 @@ def run_b200(args):
     dom_ms = stage_ms[dominant] * n_sub
     achieved = algo[dominant] / (dom_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "peak_source": peak_src, "traffic": None,
+                "frac": round(achieved / peak, 4), "peak_source": peak_src,
+                "traffic": round(NCU_DRAM_BYTES_PER_PAIR[dominant] * t_rank), "algorithmic_bytes": round(algo[dominant]),
                 "ms_per_launch_set": round(dom_ms, 4),
                 "stage_ms": {k: round(v * n_sub, 4) for k, v in stage_ms.items()}}
 
@@ -339,7 +347,8 @@ def run_b200(args):
                    "clouds_per_gpu": CLOUDS_PER_RANK, "points_per_cloud": POINTS_PER_CLOUD,
                    "pairs_per_step_per_gpu": t_rank, "neighbors_per_point": t_rank / n_pts,
                    "sub_batches_for_int32_offsets": n_sub, "l2": "inputs larger than L2 (neighbor list)",
-                   "library_kernels": "cub radix sort and scan"},
+                   "library_kernels": "cub radix sort and scan",
+                   "sharding": "every rank processes its own batch of 16 clouds (same seeds on every rank); no collective on the data path"},
         "clocks": clocks,
         "e2e": {"value": e_pairs / (e_ms * 1e-3), "unit": "pairs/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e_ms / args.steps,

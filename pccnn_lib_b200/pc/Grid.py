@@ -1,3 +1,5 @@
+import math
+
 import torch
 
 from .. import ops
@@ -35,7 +37,13 @@ class Grid(object):
                 pts = self.pointcloud_.pts_.detach()
                 self.cell_ids_ = ComputeKeys.apply(pts, self.pointcloud_.batch_ids_, self.bounding_box_.min_,
                                                    self.num_cells_, self.cell_size_)
-                self.sorted_cell_ids_, self.sorted_ids_, self.sorted_pts_ = ops.sort_keys(self.cell_ids_, 64, pts)
+                # keys are below batch * cells: sort only the bits that can be set
+                cells = self.num_cells_.tolist()
+                span = float(int(self.pointcloud_.batch_size_))
+                for c in cells:
+                    span *= c
+                key_bits = min(64, max(1, int(math.ceil(math.log2(span + 1)))))
+                self.sorted_cell_ids_, self.sorted_ids_, self.sorted_pts_ = ops.sort_keys(self.cell_ids_, key_bits, pts)
 
     def build_ds(self):
         if self.cell_ids_ is None or self.sorted_ids_ is None:

@@ -1,0 +1,80 @@
+"""The mirrored geometry classes (Pointcloud, BoundingBox, Grid, Neighborhood, PointPooling) driven
+like the reference's tests drive them, compared with the oracle pipelines of test_oracle_pins."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import ref_case
+from test_oracle_pins import oracle_neighborhood, oracle_pdf, oracle_pooling
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("batch_size,num_pts,num_dims,radius,max_neighs",
+                         [(16, 100, 3, 1.0, 0), (4, 1000, 2, 0.2, 0), (4, 1000, 3, 0.2, 4), (4, 1000, 6, 0.2, 0)])
+def test_neighborhood_class_matches_oracle(ref_clouds, batch_size, num_pts, num_dims, radius, max_neighs):
+    import pccnn_lib_b200 as lib
+    pts, batch_ids = ref_case(ref_clouds, batch_size, num_pts, num_dims)
+    device = torch.device("cuda:0")
+    pc = lib.pc.Pointcloud(pts, batch_ids, device=device)
+    cell = np.full((num_dims,), radius, np.float32)
+    bb = lib.pc.BoundingBox(pc)
+    grid = lib.pc.Grid(pc, bb, cell)
+    grid.compute_cell_ids()
+    grid.build_ds()
+    neigh = lib.pc.Neighborhood(grid, pc, max_neighs)
+    expect_n, expect_s, g = oracle_neighborhood(pts, batch_ids, batch_size, radius, max_neighs)
+    assert np.array_equal(grid.cell_ids_.cpu().numpy(), g["keys"])
+    assert np.array_equal(grid.sorted_ids_.cpu().numpy(), g["sorted_ids"])
+    assert np.array_equal(grid.grid_ds_.cpu().numpy(), g["grid_ds"])
+    assert neigh.neighbors_.dtype == torch.int32 and neigh.start_ids_.dtype == torch.int32
+    assert np.array_equal(neigh.start_ids_.cpu().numpy(), expect_s)
+    assert np.array_equal(neigh.neighbors_.cpu().numpy(), expect_n)
+
+
+@pytest.mark.parametrize("batch_size,num_pts,num_dims,radius", [(4, 1000, 2, 0.1), (4, 1000, 3, 0.1), (21, 100, 6, 3.0)])
+def test_point_pooling_class_matches_oracle(ref_clouds, batch_size, num_pts, num_dims, radius):
+    import pccnn_lib_b200 as lib
+    pts, batch_ids = ref_case(ref_clouds, batch_size, num_pts, num_dims)
+    pc = lib.pc.Pointcloud(pts, batch_ids, device=torch.device("cuda:0"))
+    pool = lib.pc.PointPooling(pc, np.full((num_dims,), radius, np.float32))
+    expect = oracle_pooling(pts, batch_ids, batch_size, radius)
+    assert pool.pooling_ids_.dtype == torch.int64
+    assert np.array_equal(pool.pooling_ids_.cpu().numpy(), expect)
+    pooled = pool.pool_tensor(pc.pts_)
+    assert np.array_equal(pooled.cpu().numpy(), pts[expect])
+    # cell_average mode is torch-only in the reference; check it against a NumPy mean per cell
+    avg = lib.pc.PointPooling(pc, np.full((num_dims,), radius, np.float32), "cell_average")
+    got = avg.pool_tensor(pc.pts_).cpu().numpy()
+    ids = avg.pooling_ids_.cpu().numpy()
+    want = np.stack([pts[ids == c].mean(0) for c in range(avg.num_pooling_pts_)])
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("batch_size,num_pts,num_dims,bandwidth", [(4, 1000, 2, 0.02), (4, 1000, 3, 0.025)])
+def test_pointcloud_pdf_matches_oracle_and_backpropagates(ref_clouds, batch_size, num_pts, num_dims, bandwidth):
+    import pccnn_lib_b200 as lib
+    pts, batch_ids = ref_case(ref_clouds, batch_size, num_pts, num_dims)
+    pc = lib.pc.Pointcloud(pts, batch_ids, device=torch.device("cuda:0"), requires_grad=True)
+    pc.compute_pdf(np.full((num_dims,), bandwidth, np.float32))
+    expect, unnorm, _, _ = oracle_pdf(pts, batch_ids, batch_size, bandwidth)
+    assert np.allclose(pc.pts_pdf_.detach().cpu().numpy(), expect, rtol=1e-5, atol=0)
+    assert np.allclose(pc.pts_unnorm_pdf_.detach().cpu().numpy(), unnorm, rtol=1e-5, atol=0)
+    pc.pts_pdf_.mean().backward()
+    assert pc.pts_.grad is not None and torch.isfinite(pc.pts_.grad).all() and pc.pts_.grad.abs().sum() > 0
+    assert tuple(pc.global_pooling(pc.pts_.detach(), "max").shape) == (batch_size, num_dims)
+
+
+def test_reference_module_names_resolve_to_this_package():
+    import sys
+    import pccnn_lib_b200
+    pccnn_lib_b200.install_as_reference_modules()
+    import pccnn_lib_ops
+    import pccnn_lib
+    assert pccnn_lib_ops.compute_keys is pccnn_lib_b200.ops.compute_keys
+    assert pccnn_lib.pc.KPConv is pccnn_lib_b200.pc.layers.KPConv
+    for name in ("build_grid_ds", "compute_keys", "find_neighbors", "compute_pdf", "compute_pdf_grads",
+                 "poisson_disk_sampling", "kp_conv", "kp_conv_grads", "mc_conv", "mc_conv_grads"):
+        assert callable(getattr(pccnn_lib_ops, name))
+    for m in ("pccnn_lib_ops", "pccnn_lib", "pccnn_lib.pc", "pccnn_lib.op_wrappers"):
+        sys.modules.pop(m, None)

@@ -424,7 +424,10 @@ def run_conv_workload(args):
     import pccnn_lib_b200 as lib
     from pccnn_lib_b200 import ops
     from pccnn_lib_b200.pc.layers import prepare_kernel_points
-    w = CONV_WORKLOADS[args.workload]
+    w = dict(CONV_WORKLOADS[args.workload])
+    if args.points:
+        w["pts"] = args.points  # smaller instance of the same workload, for profiler captures
+        w["desc"] += " [reduced to %d points per cloud]" % args.points
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)
     rs = np.random.RandomState(77)
@@ -589,6 +592,8 @@ def main():
     ap.add_argument("--clouds", type=int, default=CLOUDS_PER_RANK,
                     help="clouds per GPU (default: the full workload; smaller values are for profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
+    ap.add_argument("--points", type=int, default=0,
+                    help="convolution workloads: points per cloud (default: the workload's own size)")
     ap.add_argument("--presort", action="store_true",
                     help="convolution workloads: store the points in grid-cell order instead of random order")
     ap.add_argument("--workload", default="neighbors_kde", choices=["neighbors_kde"] + sorted(CONV_WORKLOADS),

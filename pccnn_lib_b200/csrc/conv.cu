@@ -209,8 +209,9 @@ project_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __r
                 // Lanes as channels: stream the feature rows of the staged neighbors, four neighbors
                 // per step so that 4 * CPL independent loads are in flight before the FMAs need them.
                 const int cnt = min(32, hi - t0);
-                for (int j0 = 0; j0 < cnt; j0 += 4) {
-                    float f[4][CPL];
+                // Software pipeline: the loads of the next four neighbors are issued before the FMAs
+                // of the current four, so L2 latency overlaps the arithmetic inside one warp.
+                auto load4 = [&](int j0, float (&f)[4][CPL]) {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const int j = min(j0 + u, cnt - 1);
@@ -219,6 +220,11 @@ project_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __r
                         for (int i = 0; i < CPL; ++i)
                             f[u][i] = (j0 + u < cnt && cb + i * 32 + lane < cin) ? __ldg(frow + i * 32) : 0.f;
                     }
+                };
+                float fa[4][CPL], fb[4][CPL];
+                load4(0, fa);
+                for (int j0 = 0; j0 < cnt; j0 += 8) {
+                    if (j0 + 4 < cnt) load4(j0 + 4, fb);
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const int j = min(j0 + u, cnt - 1);
@@ -229,7 +235,22 @@ project_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __r
 #pragma unroll
                             for (int q = 0; q < 4; ++q)
 #pragma unroll
-                                for (int i = 0; i < CPL; ++i) acc[i][k + q] = fmaf(f[u][i], bk[q], acc[i][k + q]);
+                                for (int i = 0; i < CPL; ++i) acc[i][k + q] = fmaf(fa[u][i], bk[q], acc[i][k + q]);
+                        }
+                    }
+                    if (j0 + 4 >= cnt) break;
+                    if (j0 + 8 < cnt) load4(j0 + 8, fa);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int j = min(j0 + 4 + u, cnt - 1);
+#pragma unroll
+                        for (int k = 0; k < KP; k += 4) {
+                            const float4 b4 = *reinterpret_cast<const float4*>(&s_basis[warp][j][k]);
+                            const float bk[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                                for (int i = 0; i < CPL; ++i) acc[i][k + q] = fmaf(fb[u][i], bk[q], acc[i][k + q]);
                         }
                     }
                 }

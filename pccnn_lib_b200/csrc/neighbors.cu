@@ -282,15 +282,19 @@ neighbors_kernel(int num_pts, const float* __restrict__ pts, const int64_t* __re
                     const unsigned cur = words;
                     if (k + kReplay < k1) words = load_words(k + kReplay);
                     const int n_sub = min(kReplay, k1 - k);
-                    for (int gi = 0; gi < n_sub; ++gi) {
+                    // Both loops are unrolled so that every shuffle has a constant source lane; groups
+                    // past the end of a short round hold zero words and emit nothing.
+#pragma unroll
+                    for (int gi = 0; gi < kReplay; ++gi) {
+                        if (gi >= n_sub) break;
                         const int kk = k + gi;
                         int found = __shfl_sync(kFullMask, my_found, kk);
                         const int m = __shfl_sync(kFullMask, my_sample, kk);
                         const int base = __shfl_sync(kFullMask, my_base, kk);
                         const int total = (MODE == kStoreLimited) ? __shfl_sync(kFullMask, my_total, kk) : 0;
-                        for (int ci = 0; ci < n_chunks; ++ci) {
+#pragma unroll
+                        for (int ci = 0; ci < kChunks; ++ci) {
                             const unsigned bal = __shfl_sync(kFullMask, cur, gi * kChunks + ci);
-                            if (bal == 0u) continue;
                             if ((bal >> lane) & 1u) {
                                 const int j = slot_ids[ci * 32 + lane];
                                 const int id = pt_index_map ? (int)__ldg(pt_index_map + j) : j;

@@ -260,13 +260,33 @@ project_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __r
             for (int i = 0; i < CPL; ++i) {
                 const int c = cb + i * 32 + lane;
                 if (c < cin) {
+                    if (K == KP && (KP % 8) == 0) {
+                        // K bf16 values of one channel are contiguous and 16-byte aligned: 128-bit stores
+                        // (a 2-byte store per value would cost one memory transaction each).
 #pragma unroll
-                    for (int k = 0; k < KP; ++k) {
-                        if (k < K) {
-                            const float v = acc[i][k];
-                            const __nv_bfloat16 h = __float2bfloat16_rn(v);
-                            p_hi[row + (size_t)c * K + k] = h;
-                            if (p_lo) p_lo[row + (size_t)c * K + k] = __float2bfloat16_rn(v - __bfloat162float(h));
+                        for (int k = 0; k < KP; k += 8) {
+                            uint32_t hw[4], lw[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float v0 = acc[i][k + 2 * q], v1 = acc[i][k + 2 * q + 1];
+                                const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+                                const __nv_bfloat162 l2 = __floats2bfloat162_rn(v0 - __low2float(h2), v1 - __high2float(h2));
+                                hw[q] = *reinterpret_cast<const uint32_t*>(&h2);
+                                lw[q] = *reinterpret_cast<const uint32_t*>(&l2);
+                            }
+                            *reinterpret_cast<uint4*>(p_hi + row + (size_t)c * K + k) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                            if (p_lo)
+                                *reinterpret_cast<uint4*>(p_lo + row + (size_t)c * K + k) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < KP; ++k) {
+                            if (k < K) {
+                                const float v = acc[i][k];
+                                const __nv_bfloat16 h = __float2bfloat16_rn(v);
+                                p_hi[row + (size_t)c * K + k] = h;
+                                if (p_lo) p_lo[row + (size_t)c * K + k] = __float2bfloat16_rn(v - __bfloat162float(h));
+                            }
                         }
                     }
                 }

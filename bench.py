@@ -583,12 +583,66 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_reference_gpu(args):
+    """Second comparator: the reference's own (generic SIMT) kernels, compiled unmodified for sm_100 by
+    oracle/build_reference.py, on the same workload and GPU.  Not the contract's reference arm (that
+    one is the CPU); printed with impl = "reference_gpu"."""
+    import importlib.util
+    import torch
+    so = os.path.join(ROOT, "oracle", "_ref", "pccnn_lib_ops.so")
+    if not os.path.exists(so):
+        print(json.dumps({"impl": "reference_gpu", "unavailable": "oracle/_ref/pccnn_lib_ops.so has not been built"}))
+        return
+    spec = importlib.util.spec_from_file_location("pccnn_lib_ops", so)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    device = torch.device("cuda", 0)
+    pts_h, ids_h = make_batch(0, CLOUDS_PER_RANK)
+    pts, ids = torch.as_tensor(pts_h, device=device), torch.as_tensor(ids_h, device=device)
+    cell = torch.full((3,), RADIUS, dtype=torch.float32, device=device)
+    bw = torch.full((3,), BANDWIDTH, dtype=torch.float32, device=device)
+
+    def step():
+        # the caller-side code of the reference (pc/BoundingBox.py, pc/Grid.py, pc/Neighborhood.py) with torch ops
+        idx = ids.to(torch.int64).unsqueeze(1).expand(-1, 3)
+        mx = torch.full((CLOUDS_PER_RANK, 3), -float("inf"), device=device).scatter_reduce(0, idx, pts, "amax") + 1e-6
+        mn = torch.full((CLOUDS_PER_RANK, 3), float("inf"), device=device).scatter_reduce(0, idx, pts, "amin") - 1e-6
+        nc = torch.max(((mx - mn) / cell).to(torch.int32) + 1, dim=0)[0]
+        keys = ref.compute_keys(pts, ids, mn, nc, cell)
+        order = torch.argsort(keys)
+        skeys = torch.index_select(keys, 0, order)
+        spts = torch.index_select(pts, 0, order)
+        ds = ref.build_grid_ds(skeys, nc, [CLOUDS_PER_RANK] + nc[0:2].tolist() + [2])
+        neigh, ends = ref.find_neighbors(spts, skeys, spts, skeys, ds, nc, cell, 0)
+        pdf = ref.compute_pdf(3, bw, spts, neigh, ends)
+        return neigh.shape[0], pdf
+
+    for _ in range(max(args.warmup, 1)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    pairs = 0
+    for _ in range(args.steps):
+        pairs += step()[0]
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    print(json.dumps({"impl": "reference_gpu", "metric": "neighbor pairs/s (radius search + KDE)",
+                      "value": pairs / (ms * 1e-3), "unit": "pairs/s", "n_gpus": 1, "steps": args.steps,
+                      "ms_per_step": ms / args.steps, "higher_is_better": True,
+                      "config": {"workload": "neighbor search + KDE: %d clouds x 100k surface points, radius 0.05"
+                                             % CLOUDS_PER_RANK,
+                                 "note": "unmodified reference kernels built for sm_100 (generic SIMT), torch ops for "
+                                         "bbox / argsort / gathers as in the reference's Python classes"}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_gpu"])
     ap.add_argument("--clouds", type=int, default=CLOUDS_PER_RANK,
                     help="clouds per GPU (default: the full workload; smaller values are for profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
@@ -602,6 +656,8 @@ def main():
     globals()["CLOUDS_PER_RANK"] = args.clouds
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference_gpu":
+        run_reference_gpu(args)
     elif args.workload != "neighbors_kde":
         run_conv_workload(args)
     else:

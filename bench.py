@@ -469,6 +469,15 @@ def run_conv_workload(args):
     feats = torch.as_tensor(rs.normal(size=(n, cin)).astype(np.float32), device=device)
     rad = torch.as_tensor(radius, device=device)
     grads = torch.as_tensor(rs.normal(size=(m, cout)).astype(np.float32), device=device)
+    if args.impl == "reference_gpu":
+        import importlib.util
+        so = os.path.join(ROOT, "oracle", "_ref", "pccnn_lib_ops.so")
+        if not os.path.exists(so):
+            print(json.dumps({"impl": "reference_gpu", "unavailable": "oracle/_ref/pccnn_lib_ops.so has not been built"}))
+            return
+        spec = importlib.util.spec_from_file_location("pccnn_lib_ops", so)
+        ops = importlib.util.module_from_spec(spec)  # the reference's operators under the same names
+        spec.loader.exec_module(ops)
     if w["kind"] == "kp":
         kp, sigma = prepare_kernel_points(3, k)
         kpts = torch.as_tensor(kp, device=device)
@@ -500,7 +509,15 @@ def run_conv_workload(args):
     fwd_ms = timed(fwd, args.steps, warm)
     bwd_ms = timed(bwd, args.steps, warm) if w["backward"] else 0.0
     clocks = sampler.finish()
+    if args.impl == "reference_gpu":
+        step_ms = fwd_ms + bwd_ms
+        print(json.dumps({"impl": "reference_gpu", "metric": "conv-layer points/s", "value": m / (step_ms * 1e-3),
+                          "unit": "points/s", "ms_per_step": step_ms, "clocks": clocks,
+                          "config": {"workload": w["desc"], "forward_ms": fwd_ms, "backward_ms": bwd_ms, "samples": m,
+                                     "pairs": t, "note": "unmodified reference kernels + cuBLAS, built for sm_100"}}))
+        return
     # the contraction alone, on the same shapes, for the tensor-core roofline
+    from pccnn_lib_b200 import ops
     inner = cin * k
     a = torch.randn(min(m, 1 << 17), inner, device=device)
     bmat = torch.randn(cout, inner, device=device)
@@ -526,6 +543,85 @@ def run_conv_workload(args):
                      "rows": int(a.shape[0]), "ms": gemm_ms},
     }
     print(json.dumps(line))
+
+
+def run_encoder_workload(args):
+    """KPConv 5-level encoder, inference, bf16 features and weights with fp32 accumulation: 64 clouds x 50k
+    surface points, Poisson-disk radii 0.02 ... 0.32, convolution radius 2.5 x the sampling radius, channels
+    3-64-128-256-512-1024, 16 kernel points.  No normalisation or activation between levels (the reference
+    ships no model).  One step = all poolings, neighborhoods and convolutions of the five levels."""
+    import torch
+    import pccnn_lib_b200 as lib
+    from pccnn_lib_b200 import ops
+    from pccnn_lib_b200.pc.layers import prepare_kernel_points
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    clouds = args.clouds if args.clouds != CLOUDS_PER_RANK or args.clouds == 64 else 64
+    num_pts = args.points or 50000
+    pts, ids = make_batch(0, clouds, num_pts)
+    rs = np.random.RandomState(3)
+    channels = [3, 64, 128, 256, 512, 1024]
+    kp, sigma = prepare_kernel_points(3, 16)
+    kpts = torch.as_tensor(kp, device=device)
+    weights = [torch.as_tensor(rs.normal(0, np.sqrt(2.0 / (channels[l] * 16)), size=(16 * channels[l], channels[l + 1]))
+                               .astype(np.float32), device=device).to(torch.bfloat16) for l in range(5)]
+    feats0 = torch.as_tensor(rs.normal(size=(pts.shape[0], 3)).astype(np.float32), device=device).to(torch.bfloat16)
+    d_pts, d_ids = torch.as_tensor(pts, device=device), torch.as_tensor(ids, device=device)
+    stats = {}
+
+    def step(record=False):
+        pc, feats = lib.pc.Pointcloud(d_pts, d_ids), feats0
+        conv_ms = []
+        for level in range(5):
+            r_pool = 0.02 * (2 ** level)
+            pool = lib.pc.PointPooling(pc, np.full((3,), r_pool, np.float32))
+            pc_out = lib.pc.Pointcloud(pool.pool_tensor(pc.pts_), pool.pool_tensor(pc.batch_ids_))
+            radius = torch.full((3,), 2.5 * r_pool, dtype=torch.float32, device=device)
+            grid = lib.pc.Grid(pc, lib.pc.BoundingBox(pc), radius)
+            grid.compute_cell_ids()
+            grid.build_ds()
+            nb = lib.pc.Neighborhood(grid, pc_out, 0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            feats = ops.kp_conv(pc.pts_, feats, pc_out.pts_, nb.neighbors_, nb.start_ids_, radius, kpts, sigma,
+                                weights[level])
+            e1.record()
+            if record:
+                stats.setdefault("levels", []).append(dict(points=int(pc.pts_.shape[0]), samples=int(pc_out.pts_.shape[0]),
+                                                           pairs=int(nb.neighbors_.shape[0])))
+            conv_ms.append((e0, e1))
+            pc = pc_out
+        return feats, conv_ms
+
+    step(record=True)
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    marks = []
+    for _ in range(args.steps):
+        out, conv_ms = step()
+        marks.append(conv_ms)
+    t1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.finish()
+    ms = t0.elapsed_time(t1) / args.steps
+    conv = [float(np.mean([m[l][0].elapsed_time(m[l][1]) for m in marks])) for l in range(5)]
+    flops = sum(2.0 * lv["samples"] * 16 * channels[l] * channels[l + 1] for l, lv in enumerate(stats["levels"]))
+    print(json.dumps({
+        "metric": "conv-layer points/s (5-level KPConv encoder, inference)", "value": pts.shape[0] / (ms * 1e-3),
+        "unit": "points/s", "n_gpus": 1, "steps": args.steps, "warmup": warm, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": run_encoder_workload.__doc__.split("  One step")[0].replace("\n    ", " "),
+                   "clouds": clouds, "points_per_cloud": num_pts, "levels": stats["levels"], "conv_ms_per_level": conv,
+                   "conv_ms_total": sum(conv), "geometry_ms": ms - sum(conv), "contraction_flop_per_step": flops,
+                   "finite_output": bool(torch.isfinite(out.float()).all())},
+        "clocks": clocks}))
 
 
 # ---- CPU arm ------------------------------------------------------------------------------------
@@ -650,14 +746,18 @@ def main():
                     help="convolution workloads: points per cloud (default: the workload's own size)")
     ap.add_argument("--presort", action="store_true",
                     help="convolution workloads: store the points in grid-cell order instead of random order")
-    ap.add_argument("--workload", default="neighbors_kde", choices=["neighbors_kde"] + sorted(CONV_WORKLOADS),
+    ap.add_argument("--workload", default="neighbors_kde", choices=["neighbors_kde", "kpconv_encoder_cfg3"] + sorted(CONV_WORKLOADS),
                     help="neighbors_kde is the headline workload; the others time one convolution layer")
     args = ap.parse_args()
     globals()["CLOUDS_PER_RANK"] = args.clouds
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference_gpu" and args.workload != "neighbors_kde":
+        run_conv_workload(args)
     elif args.impl == "reference_gpu":
         run_reference_gpu(args)
+    elif args.workload == "kpconv_encoder_cfg3":
+        run_encoder_workload(args)
     elif args.workload != "neighbors_kde":
         run_conv_workload(args)
     else:

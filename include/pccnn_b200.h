@@ -221,6 +221,16 @@ int pccnn_kp_conv(int D, int64_t num_pts, const float* pts, const float* feats, 
                   int num_kernel_pts, float sigma, const float* weights, int cout, float* out,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* KPConv forward for bf16 features, bf16 weights and bf16 output (3-D points): one bf16 tensor-core
+ * pass with fp32 accumulation; the projected operand is rounded to bf16 once.  Matches an fp32
+ * evaluation within 1e-2 relative.  No counterpart in the reference, which dispatches float and
+ * double only (pcconvs/shared/feat_basis_utils.cuh:41). */
+int pccnn_kp_conv_bf16(int D, int64_t num_pts, const float* pts, const void* feats_bf16, int cin,
+                       int64_t num_samples, const float* samples, const int32_t* neighbors,
+                       const int32_t* start_ids, const float* radii, const float* kernel_pts,
+                       int num_kernel_pts, float sigma, const void* weights_bf16, int cout, void* out_bf16,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* MCConv forward: basis b[t,:] = leaky_relu_{0.2}(d_t . axis + bias) / pdf[n0(t)], axis [D, hidden],
  * bias [hidden], weights [num_mlps, hidden / num_mlps * cin, cout / num_mlps] (hidden counts the
  * units of all MLPs together, as the reference's proj_axis_ does).

@@ -41,6 +41,8 @@ SIGNATURES = {
     "pccnn_conv_workspace_bytes": (_size, [_c_i64, _c_int, _c_int, _c_int]),
     "pccnn_kp_conv": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
                                ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
+    "pccnn_kp_conv_bf16": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
+                                    ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
     "pccnn_mc_conv": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                                _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
     "pccnn_conv_grads_workspace_bytes": (_size, [_c_i64, _c_int, _c_int, _c_int]),

@@ -155,9 +155,12 @@ struct MLPBasis {
 };
 
 // P[m, c*K + k] for the samples [m_begin, m_end), written as bf16 hi (+ lo) rows of ld_p elements.
-template <int D, int KP, int CPL, class BASIS, class ARGS>
+__device__ __forceinline__ float load_feat(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float load_feat(const __nv_bfloat16* p) { return __bfloat162float(__ldg(p)); }
+
+template <int D, int KP, int CPL, class BASIS, class ARGS, class FT>
 __global__ void __launch_bounds__(conv_warps<KP>() * 32)
-project_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __restrict__ feats, int cin,
+project_kernel(ARGS args, int K, const float* __restrict__ pts, const FT* __restrict__ feats, int cin,
                const float* __restrict__ samples, const int2* __restrict__ neighbors,
                const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
                __nv_bfloat16* __restrict__ p_hi, __nv_bfloat16* __restrict__ p_lo, int ld_p) {
@@ -215,10 +218,10 @@ project_kernel(ARGS args, int K, const float* __restrict__ pts, const float* __r
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const int j = min(j0 + u, cnt - 1);
-                        const float* frow = feats + (int64_t)s_n0[warp][j] * cin + cb + lane;
+                        const FT* frow = feats + (int64_t)s_n0[warp][j] * cin + cb + lane;
 #pragma unroll
                         for (int i = 0; i < CPL; ++i)
-                            f[u][i] = (j0 + u < cnt && cb + i * 32 + lane < cin) ? __ldg(frow + i * 32) : 0.f;
+                            f[u][i] = (j0 + u < cnt && cb + i * 32 + lane < cin) ? load_feat(frow + i * 32) : 0.f;
                     }
                 };
                 float fa[4][CPL], fb[4][CPL];
@@ -519,15 +522,15 @@ static int launch_backward_pairs(int K, const ARGS& args, const float* pts, cons
     return PCCNN_OK;
 }
 
-template <int D, class ARGS, template <int, int> class BASIS>
-static int launch_project(int K, const ARGS& args, const float* pts, const float* feats, int cin, const float* samples,
+template <int D, class ARGS, template <int, int> class BASIS, class FT = float>
+static int launch_project(int K, const ARGS& args, const float* pts, const FT* feats, int cin, const float* samples,
                           const int32_t* neighbors, const int32_t* start_ids, const float* radii, int m_begin,
                           int m_end, void* p_hi, void* p_lo, int ld_p, cudaStream_t s) {
     const int count = m_end - m_begin;
     if (count <= 0) return PCCNN_OK;
     // channels per lane: the largest power of two <= 64 / KP that Cin can still fill
 #define PCCNN_PROJECT_C(KP, CPL)                                                                   \
-    project_kernel<D, KP, CPL, BASIS<D, KP>, ARGS>                                                 \
+    project_kernel<D, KP, CPL, BASIS<D, KP>, ARGS, FT>                                             \
         <<<grid_for((int64_t)count * 32, conv_warps<KP>() * 32, 8), conv_warps<KP>() * 32, 0, s>>>( \
             args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids, radii, m_begin,  \
             m_end, (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo, ld_p)
@@ -575,10 +578,16 @@ static ConvLayout conv_layout(int64_t num_samples, int cin, int K, int cout) {
 
 template <class ARGS, template <int, int> class BASIS>
 static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t num_pts, const float* pts,
-                        const float* feats, int cin, int64_t num_samples, const float* samples,
+                        const void* feats_any, int cin, int64_t num_samples, const float* samples,
                         const int32_t* neighbors, const int32_t* start_ids, const float* radii, int num_mlps,
-                        const float* weights, int cout, float* out, void* workspace, size_t workspace_bytes,
-                        cudaStream_t s) {
+                        const void* weights_any, int cout, void* out_any, void* workspace, size_t workspace_bytes,
+                        cudaStream_t s, bool io_bf16 = false) {
+    // io_bf16: features, weights and output are bf16 (inference configuration): one tensor-core pass,
+    // P kept as a single bf16 plane, fp32 accumulation.
+    const float* feats = (const float*)feats_any;
+    const float* weights = (const float*)weights_any;
+    float* out = (float*)out_any;
+    PCCNN_CHECK_ARG(!io_bf16 || D == 3, "%s: bf16 features are supported for 3-D points only", who);
     PCCNN_CHECK_ARG(D >= kMinDims && D <= kMaxDims, "%s: point dimension %d outside [2, 6]", who, D);
     PCCNN_CHECK_ARG(K >= 1 && K <= 64, "%s: basis size %d outside [1, 64]", who, K);
     PCCNN_CHECK_ARG(cin >= 1 && cout >= 1 && num_mlps >= 1 && cout % num_mlps == 0 && (cin * K) % num_mlps == 0,
@@ -602,16 +611,27 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
     PCCNN_CUDA(cudaMemsetAsync(ws + L.w_hi_off, 0, L.status_off - L.w_hi_off, s));
     for (int j = 0; j < num_mlps; ++j) {
         const size_t off = (size_t)j * cout_j * L.ld_p * 2;
-        if (int rc = split_bf16_transpose(inner_j, cout_j, weights + (size_t)j * inner_j * cout_j, cout_j, L.ld_p,
-                                          ws + L.w_hi_off + off, ws + L.w_lo_off + off, s))
-            return rc;
+        int rc;
+        if (io_bf16)
+            rc = transpose_bf16(inner_j, cout_j, (const __nv_bfloat16*)weights_any + (size_t)j * inner_j * cout_j, cout_j,
+                                L.ld_p, ws + L.w_hi_off + off, s);
+        else
+            rc = split_bf16_transpose(inner_j, cout_j, weights + (size_t)j * inner_j * cout_j, cout_j, L.ld_p,
+                                      ws + L.w_hi_off + off, ws + L.w_lo_off + off, s);
+        if (rc) return rc;
     }
     for (int64_t m0 = 0; m0 < num_samples; m0 += L.chunk) {
         const int64_t m1 = (m0 + L.chunk < num_samples) ? m0 + L.chunk : num_samples;
         int rc = PCCNN_OK;
-        PCCNN_DISPATCH_DIM(D, (rc = launch_project<DIM, ARGS, BASIS>(K, args, pts, feats, cin, samples, neighbors,
-                                                                     start_ids, radii, (int)m0, (int)m1,
-                                                                     ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, s)));
+        if (io_bf16) {
+            rc = launch_project<3, ARGS, BASIS, __nv_bfloat16>(K, args, pts, (const __nv_bfloat16*)feats_any, cin, samples,
+                                                               neighbors, start_ids, radii, (int)m0, (int)m1,
+                                                               ws + L.p_hi_off, nullptr, L.ld_p, s);
+        } else {
+            PCCNN_DISPATCH_DIM(D, (rc = launch_project<DIM, ARGS, BASIS>(K, args, pts, feats, cin, samples, neighbors,
+                                                                         start_ids, radii, (int)m0, (int)m1,
+                                                                         ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, s)));
+        }
         if (rc) return rc;
         for (int j = 0; j < num_mlps; ++j) {
             // Slice j of the P rows (offset j * inner_j, 16-byte aligned because inner_j % 8 == 0 is checked
@@ -620,11 +640,11 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
             const size_t b_off = (size_t)j * cout_j * L.ld_p * 2;
             PCCNN_CHECK_ARG(num_mlps == 1 || inner_j % 64 == 0, "%s: Cin*K per MLP must be a multiple of 64", who);
             const int kp = num_mlps == 1 ? L.ld_p : inner_j;
-            GemmOperand a{ws + L.p_hi_off + a_off, ws + L.p_lo_off + a_off, L.ld_p};
-            GemmOperand b{ws + L.w_hi_off + b_off, ws + L.w_lo_off + b_off, L.ld_p};
-            if (int rc2 = gemm_bf16_nt(a, b, out + (size_t)m0 * cout + (size_t)j * cout_j, m1 - m0, cout_j, kp, cout,
-                                       status, s))
-                return rc2;
+            GemmOperand a{ws + L.p_hi_off + a_off, io_bf16 ? nullptr : ws + L.p_lo_off + a_off, L.ld_p};
+            GemmOperand b{ws + L.w_hi_off + b_off, io_bf16 ? nullptr : ws + L.w_lo_off + b_off, L.ld_p};
+            float* c_ptr = io_bf16 ? (float*)((__nv_bfloat16*)out_any + (size_t)m0 * cout + (size_t)j * cout_j)
+                                   : out + (size_t)m0 * cout + (size_t)j * cout_j;
+            if (int rc2 = gemm_bf16_nt(a, b, c_ptr, m1 - m0, cout_j, kp, cout, status, s, io_bf16 ? 1 : 0)) return rc2;
         }
     }
     return PCCNN_OK;
@@ -751,6 +771,17 @@ int pccnn_kp_conv(int D, int64_t num_pts, const float* pts, const float* feats, 
     return conv_forward<KPBasisArgs, KPBasis>("kp_conv", D, num_kernel_pts, args, num_pts, pts, feats, cin, num_samples,
                                               samples, neighbors, start_ids, radii, 1, weights, cout, out, workspace,
                                               workspace_bytes, (cudaStream_t)stream);
+}
+
+int pccnn_kp_conv_bf16(int D, int64_t num_pts, const float* pts, const void* feats_bf16, int cin, int64_t num_samples,
+                       const float* samples, const int32_t* neighbors, const int32_t* start_ids, const float* radii,
+                       const float* kernel_pts, int num_kernel_pts, float sigma, const void* weights_bf16, int cout,
+                       void* out_bf16, void* workspace, size_t workspace_bytes, void* stream) {
+    PCCNN_CHECK_ARG(kernel_pts && sigma > 0.f, "kp_conv_bf16: kernel points missing or sigma <= 0");
+    KPBasisArgs args{kernel_pts, 1.0f / sigma};
+    return conv_forward<KPBasisArgs, KPBasis>("kp_conv_bf16", D, num_kernel_pts, args, num_pts, pts, feats_bf16, cin,
+                                              num_samples, samples, neighbors, start_ids, radii, 1, weights_bf16, cout,
+                                              out_bf16, workspace, workspace_bytes, (cudaStream_t)stream, true);
 }
 
 int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, const float* feats, int cin,

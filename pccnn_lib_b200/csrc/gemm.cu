@@ -117,7 +117,8 @@ template <int BN>
 __global__ void __launch_bounds__(128)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                 float* __restrict__ C, int M, int N, int ldc, int k_blocks, int passes, int* status) {
+                 float* __restrict__ C, int M, int N, int ldc, int k_blocks, int passes, int c_is_bf16,
+                 int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + kGemmStages * GemmSmem<BN>::kStage);
@@ -198,7 +199,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         for (int c0 = 0; c0 < BN; c0 += 32) {
             uint32_t r[32];
             tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
-            if (row < M) {
+            if (row < M && c_is_bf16) {
+                // bf16 output (inference configuration): C is a __nv_bfloat16 matrix, ldc in elements
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (size_t)row * ldc + n0 + c0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    const int col = n0 + c0 + j;
+                    if (col + 7 < N && ((((uintptr_t)(dst + j)) & 15) == 0)) {
+                        uint32_t wv[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * q]),
+                                                                            __uint_as_float(r[j + 2 * q + 1]));
+                            wv[q] = *reinterpret_cast<const uint32_t*>(&h2);
+                        }
+                        *reinterpret_cast<uint4*>(dst + j) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            if (col + e < N) dst[j + e] = __float2bfloat16_rn(__uint_as_float(r[j + e]));
+                    }
+                }
+            } else if (row < M) {
                 float* dst = C + (size_t)row * ldc + n0 + c0;
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
@@ -381,6 +403,19 @@ split_bf16_transpose_kernel(int rows, int cols, const float* __restrict__ src, i
     }
 }
 
+// dst[c, r] = src[r, c] for bf16 matrices; destination rows padded with zeros to ld_dst.
+__global__ void __launch_bounds__(256)
+transpose_bf16_kernel(int rows, int cols, const __nv_bfloat16* __restrict__ src, int64_t ld_src, int ld_dst,
+                      __nv_bfloat16* __restrict__ dst) {
+    const int64_t total = (int64_t)cols * ld_dst;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t c = i / ld_dst;
+        const int r = (int)(i - c * ld_dst);
+        dst[i] = (r < rows) ? src[(int64_t)r * ld_src + c] : __float2bfloat16_rn(0.f);
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -427,7 +462,7 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t ld
 
 template <int BN>
 static int launch_gemm(const GemmOperand& a, const GemmOperand& b, float* C, int64_t M, int N, int K_padded, int ldc,
-                       int* status, cudaStream_t s) {
+                       int c_is_bf16, int* status, cudaStream_t s) {
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     const int passes = (a.lo && b.lo) ? 3 : 1;
     if (int rc = make_map(&ma_hi, a.hi, M, a.ld, kGemmBM)) return rc;
@@ -443,22 +478,22 @@ static int launch_gemm(const GemmOperand& a, const GemmOperand& b, float* C, int
     PCCNN_CUDA(attr_err);
     dim3 grid((unsigned)((M + kGemmBM - 1) / kGemmBM), (unsigned)((N + BN - 1) / BN));
     gemm_bf16_kernel<BN><<<grid, 128, GemmSmem<BN>::kBytes, s>>>(ma_hi, ma_lo, mb_hi, mb_lo, C, (int)M, N, ldc,
-                                                               K_padded / kGemmBK, passes, status);
+                                                               K_padded / kGemmBK, passes, c_is_bf16, status);
     PCCNN_LAUNCH_CHECK();
     return PCCNN_OK;
 }
 
 int gemm_bf16_nt(const GemmOperand& a, const GemmOperand& b, float* C, int64_t M, int N, int K_padded, int ldc,
-                 int* status, cudaStream_t s) {
+                 int* status, cudaStream_t s, int c_is_bf16) {
     PCCNN_CHECK_ARG(M >= 0 && M < 0x7fffffffLL && N > 0 && K_padded > 0 && K_padded % kGemmBK == 0,
                     "gemm: bad shape M=%lld N=%d K=%d", (long long)M, N, K_padded);
     PCCNN_CHECK_ARG(a.ld >= K_padded && b.ld >= K_padded, "gemm: leading dimensions smaller than K");
     if (M == 0) return PCCNN_OK;
-    if (N <= 16) return launch_gemm<16>(a, b, C, M, N, K_padded, ldc, status, s);
-    if (N <= 32) return launch_gemm<32>(a, b, C, M, N, K_padded, ldc, status, s);
-    if (N <= 64) return launch_gemm<64>(a, b, C, M, N, K_padded, ldc, status, s);
-    if (N <= 128) return launch_gemm<128>(a, b, C, M, N, K_padded, ldc, status, s);
-    return launch_gemm<256>(a, b, C, M, N, K_padded, ldc, status, s);
+    if (N <= 16) return launch_gemm<16>(a, b, C, M, N, K_padded, ldc, c_is_bf16, status, s);
+    if (N <= 32) return launch_gemm<32>(a, b, C, M, N, K_padded, ldc, c_is_bf16, status, s);
+    if (N <= 64) return launch_gemm<64>(a, b, C, M, N, K_padded, ldc, c_is_bf16, status, s);
+    if (N <= 128) return launch_gemm<128>(a, b, C, M, N, K_padded, ldc, c_is_bf16, status, s);
+    return launch_gemm<256>(a, b, C, M, N, K_padded, ldc, c_is_bf16, status, s);
 }
 
 template <int BN>
@@ -498,6 +533,14 @@ int gemm_bf16_tn_accumulate(const GemmOperand& a, const GemmOperand& b, float* C
     if (N <= 64) return launch_gemm_tn<64>(a, b, C, rows, I, N, ldc, status, s);
     if (N <= 128) return launch_gemm_tn<128>(a, b, C, rows, I, N, ldc, status, s);
     return launch_gemm_tn<256>(a, b, C, rows, I, N, ldc, status, s);
+}
+
+int transpose_bf16(int rows, int cols, const void* src, int64_t ld_src, int ld_dst, void* dst, cudaStream_t s) {
+    if (rows == 0 || cols == 0) return PCCNN_OK;
+    transpose_bf16_kernel<<<grid_for((int64_t)cols * ld_dst, 256, 8), 256, 0, s>>>(
+        rows, cols, (const __nv_bfloat16*)src, ld_src, ld_dst, (__nv_bfloat16*)dst);
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
 }
 
 int split_bf16(int64_t rows, int cols, const float* src, int64_t ld_src, int ld_dst, void* hi, void* lo,

@@ -17,8 +17,12 @@ struct GemmOperand {
 // C[M, N] (fp32, row stride ldc) = A[M, K] * B[N, K]^T.  Three passes when both operands carry a
 // lo part, one otherwise.  `status` is a device int the kernel sets non-zero if a bounded wait
 // ran out.
+// c_is_bf16 != 0: C points to a bf16 matrix (ldc in elements) and the result is rounded to bf16.
 int gemm_bf16_nt(const GemmOperand& a, const GemmOperand& b, float* C, int64_t M, int N, int K_padded, int ldc,
-                 int* status, cudaStream_t s);
+                 int* status, cudaStream_t s, int c_is_bf16 = 0);
+
+// dst[c, r] = src[r, c] for bf16 matrices, destination rows zero-padded to ld_dst elements.
+int transpose_bf16(int rows, int cols, const void* src, int64_t ld_src, int ld_dst, void* dst, cudaStream_t s);
 
 // C[I, N] (fp32, zeroed by the caller or holding a running sum) += A[rows, I]^T * B[rows, N];
 // operand rows padded to a multiple of 64 elements.  Partial sums are added with float reductions.

@@ -286,9 +286,9 @@ def gemm_f32(a, b, split=True):
 
 
 # ---- point convolutions ----------------------------------------------------------------------
-def _conv_common(pts, feats, samples, neighbors, start_ids, radii):
+def _conv_common(pts, feats, samples, neighbors, start_ids, radii, feat_dtype=torch.float32):
     pts = _need(pts, "pts", torch.float32, 2)
-    feats = _need(feats, "features", torch.float32, 2)
+    feats = _need(feats, "features", feat_dtype, 2)
     samples = _need(samples, "samples", torch.float32, 2)
     neighbors = _need(neighbors, "neighbors", torch.int32, 2)
     start_ids = _need(start_ids, "start_ids", torch.int32, 1)
@@ -304,7 +304,10 @@ def _conv_common(pts, feats, samples, neighbors, start_ids, radii):
 
 
 def kp_conv(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights):
-    """KPConv forward -> [M, Cout]; kpconv() of pccnn_lib_ops/pcconvs/kpconv.cu:32-60 of the reference."""
+    """KPConv forward -> [M, Cout]; kpconv() of pccnn_lib_ops/pcconvs/kpconv.cu:32-60 of the reference.
+    bfloat16 features with bfloat16 weights select the single-pass inference path (bfloat16 output)."""
+    if isinstance(feats, torch.Tensor) and feats.dtype == torch.bfloat16:
+        return _kp_conv_bf16(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights)
     pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii)
     kernel_pts = _need(kernel_pts, "kernel_pts", torch.float32, 2)
     weights = _need(weights, "weights", torch.float32, 2)
@@ -318,6 +321,24 @@ def kp_conv(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma,
         _capi.check(_lib.pccnn_kp_conv(d, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
                                        _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
                                        _p(out), ws.data_ptr(), ws.numel(), _stream()), "kp_conv")
+    return out
+
+
+def _kp_conv_bf16(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights):
+    pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii,
+                                                                        torch.bfloat16)
+    kernel_pts = _need(kernel_pts, "kernel_pts", torch.float32, 2)
+    weights = _need(weights, "weights", torch.bfloat16, 2)
+    k, cin, cout = kernel_pts.shape[0], feats.shape[1], weights.shape[1]
+    if d != 3 or kernel_pts.shape[1] != d or weights.shape[0] != k * cin:
+        raise RuntimeError("bfloat16 KPConv needs 3-D points, kernel_pts [K, 3] and weights [K * Cin, Cout]")
+    m = samples.shape[0]
+    out = torch.empty((m, cout), dtype=torch.bfloat16, device=pts.device)
+    with torch.cuda.device(pts.device):
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
+        _capi.check(_lib.pccnn_kp_conv_bf16(d, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
+                                            _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights),
+                                            cout, _p(out), ws.data_ptr(), ws.numel(), _stream()), "kp_conv_bf16")
     return out
 
 

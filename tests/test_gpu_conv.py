@@ -109,3 +109,21 @@ def test_layers_run_end_to_end_with_autograd(ref_clouds):
     assert out2.shape == (pts.shape[0], 8) and torch.isfinite(out2).all()
     for p in [feats, kp.conv_weights_, mc.conv_weights_, mc.proj_axis_, mc.proj_bias_]:
         assert p.grad is not None and torch.isfinite(p.grad).all() and p.grad.abs().sum() > 0
+
+
+@pytest.mark.parametrize("c", [KP_CASES[0], EXTRA_KP_CASES[0], EXTRA_KP_CASES[2]], ids=_id)
+def test_kpconv_bf16_inference_path(ref_clouds, c):
+    # bf16 features / weights / output, fp32 accumulation: within 1e-2 of the float64 oracle evaluated on
+    # the bf16-rounded inputs (relative to the output's magnitude).
+    from pccnn_lib_b200 import ops
+    case = kp_case(ref_clouds, c, normal_feats=True)
+    feats = dev(case["feats"]).to(torch.bfloat16)
+    weights = dev(case["weights"]).to(torch.bfloat16)
+    got = ops.kp_conv(dev(case["pts"]), feats, dev(case["samples"]), dev(case["neighbors"]), dev(case["start_ids"]),
+                      dev(case["radii"]), dev(case["kernel_pts"]), case["sigma"], weights)
+    assert got.dtype == torch.bfloat16
+    expect = conv_oracle.kp_conv(case["pts"], feats.float().cpu().numpy(), case["samples"], case["neighbors"],
+                                 case["start_ids"], case["radii"], case["kernel_pts"], case["sigma"],
+                                 weights.float().cpu().numpy()).numpy()
+    scale = np.abs(expect).max()
+    assert np.abs(got.float().cpu().numpy() - expect).max() <= 1e-2 * scale

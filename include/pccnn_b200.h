@@ -282,6 +282,13 @@ size_t pccnn_gemm_workspace_bytes(int64_t M, int N, int K);
 int pccnn_gemm_f32(int64_t M, int N, int K, const float* A, int64_t lda, const float* B, int64_t ldb,
                    float* C, int64_t ldc, int split, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The tensor-core kernel alone, on operands that are already bf16: A [M, lda], B [N, ldb] with K
+ * contiguous, K a multiple of 64 and lda, ldb >= K multiples of 64; a_lo / b_lo are the optional
+ * low parts of the split (both or neither).  Asynchronous; *status_dev (device int, zeroed by the
+ * caller) becomes non-zero if a bounded wait inside the kernel ran out. */
+int pccnn_gemm_bf16(int64_t M, int N, int K, const void* a_hi, const void* a_lo, int64_t lda, const void* b_hi,
+                    const void* b_lo, int64_t ldb, float* C, int64_t ldc, int* status_dev, void* stream);
+
 /* C[I, N] = A[rows, I]^T * B[rows, N] (the weight-gradient contraction dW = P^T g of
  * pccnn_lib_ops/pcconvs/kpconv.cu:90-93): the reduction runs over the rows, split across CTAs,
  * partial tiles are summed with float reductions (the order of the partial sums is not fixed). */

@@ -55,6 +55,7 @@ SIGNATURES = {
     "pccnn_gemm_workspace_bytes": (_size, [_c_i64, _c_int, _c_int]),
     "pccnn_gemm_f32": (_c_int, [_c_i64, _c_int, _c_int, _ptr, _c_i64, _ptr, _c_i64, _ptr, _c_i64, _c_int, _ptr,
                                 _size, _ptr]),
+    "pccnn_gemm_bf16": (_c_int, [_c_i64, _c_int, _c_int, _ptr, _ptr, _c_i64, _ptr, _ptr, _c_i64, _ptr, _c_i64, _ptr, _ptr]),
     "pccnn_gemm_tn_workspace_bytes": (_size, [_c_i64, _c_int, _c_int]),
     "pccnn_gemm_tn_f32": (_c_int, [_c_i64, _c_int, _c_int, _ptr, _c_i64, _ptr, _c_i64, _ptr, _c_i64, _c_int, _ptr,
                                    _size, _ptr]),

@@ -11,14 +11,15 @@
 //
 // Kernel: one CTA per 128 x BN output tile, 128 threads.
 //   warp 0, one lane : TMA producer  -- cp.async.bulk.tensor 2-D loads of 128 x 64 (A) and BN x 64 (B)
-//                      bf16 boxes, 128-byte swizzle, into a 3-stage ring, completion on mbarriers
-//   warp 1, one lane : MMA issuer    -- tcgen05.mma.cta_group::1.kind::f16, four K=16 steps per stage,
+//                      bf16 boxes, 128-byte swizzle, into a 2-4 stage ring, completion on mbarriers;
+//                      with the split a stage carries the hi and lo planes of both operands
+//   warp 1, one lane : MMA issuer    -- tcgen05.mma.cta_group::1.kind::f16, four K=16 steps per stage
+//                      (x3 products with the split, all from the same shared-memory tiles),
 //                      accumulator [128 lanes x BN columns] fp32 in tensor memory; tcgen05.commit
 //                      releases the stage and finally signals the epilogue
 //   all four warps   : epilogue      -- tcgen05.ld 32 lanes x 32 columns per warp and step, plain
 //                      global stores of whole 128-byte row segments
-// Three stages of (16 + BN/8) KB let two CTAs share an SM, so one CTA's epilogue overlaps the
-// other's main loop.  Every wait is bounded: on expiry the kernel records a status word,
+// Every wait is bounded: on expiry the kernel records a status word,
 // leaves its loops, releases tensor memory and returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -113,27 +114,41 @@ struct GemmSmem {
     static constexpr int kBytes = kGemmStages * kStage + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
-template <int BN>
+// Stage of the NT kernel: with the hi/lo split one stage holds A_hi, A_lo, B_hi, B_lo of one K block, so
+// the three products hi*hi + lo*hi + hi*lo reuse each tile from shared memory (two thirds of the
+// L2 -> SM traffic of three separate passes).
+template <int BN, bool SPLIT>
+struct NtSmem {
+    static constexpr int kA = kGemmBM * kGemmBK * 2;
+    static constexpr int kB = BN * kGemmBK * 2;
+    static constexpr int kStage = (SPLIT ? 2 : 1) * (kA + kB);
+    static constexpr int kStagesRaw = (200 * 1024) / kStage;
+    static constexpr int kStages = kStagesRaw > 4 ? 4 : (kStagesRaw < 2 ? 2 : kStagesRaw);
+    static constexpr int kBytes = kStages * kStage + 1024 + 256;
+};
+
+template <int BN, bool SPLIT>
 __global__ void __launch_bounds__(128)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                 float* __restrict__ C, int M, int N, int ldc, int k_blocks, int passes, int c_is_bf16,
-                 int* status) {
+                 float* __restrict__ C, int M, int N, int ldc, int k_blocks, int c_is_bf16, int* status) {
+    using SM = NtSmem<BN, SPLIT>;
+    constexpr int kStages = SM::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(smem + kGemmStages * GemmSmem<BN>::kStage);
-    uint64_t* full = bars;                       // [stages] TMA -> MMA
-    uint64_t* empty = bars + kGemmStages;        // [stages] MMA -> TMA
-    uint64_t* acc_ready = bars + 2 * kGemmStages;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kGemmStages + 1);
+    uint64_t* bars = (uint64_t*)(smem + kStages * SM::kStage);
+    uint64_t* full = bars;                   // [stages] TMA -> MMA
+    uint64_t* empty = bars + kStages;        // [stages] MMA -> TMA
+    uint64_t* acc_ready = bars + 2 * kStages;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kStages + 1);
     constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;  // power of two >= 32
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * kGemmBM, n0 = blockIdx.y * BN;
-    const int total = k_blocks * passes;
+    const int total = k_blocks;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kGemmStages; ++s) {
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, 1);
         }
@@ -153,34 +168,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
 
     bool ok = true;
     if (warp == 0 && lane == 0) {
-        // ---- TMA producer
+        // ---- TMA producer: one K block per stage, all operand planes of it
         for (int it = 0; it < total && ok; ++it) {
-            const int s = it % kGemmStages, round = it / kGemmStages;
+            const int s = it % kStages, round = it / kStages;
             if (round > 0) ok = mbar_wait(empty + s, (round - 1) & 1);
             if (!ok) break;
-            const int pass = it / k_blocks, kb = it - pass * k_blocks;
-            const CUtensorMap* ma = (pass == 1) ? &map_a_lo : &map_a_hi;
-            const CUtensorMap* mb = (pass == 2) ? &map_b_lo : &map_b_hi;
-            uint8_t* sa = smem + s * GemmSmem<BN>::kStage;
-            mbar_expect_tx(full + s, GemmSmem<BN>::kStage);
-            tma_load_2d(sa, ma, full + s, kb * kGemmBK, m0);
-            tma_load_2d(sa + GemmSmem<BN>::kA, mb, full + s, kb * kGemmBK, n0);
+            uint8_t* st = smem + s * SM::kStage;
+            mbar_expect_tx(full + s, SM::kStage);
+            tma_load_2d(st, &map_a_hi, full + s, it * kGemmBK, m0);
+            tma_load_2d(st + SM::kA, &map_b_hi, full + s, it * kGemmBK, n0);
+            if (SPLIT) {
+                tma_load_2d(st + SM::kA + SM::kB, &map_a_lo, full + s, it * kGemmBK, m0);
+                tma_load_2d(st + 2 * SM::kA + SM::kB, &map_b_lo, full + s, it * kGemmBK, n0);
+            }
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer.  Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major.
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                    ((uint32_t)(kGemmBM >> 4) << 24);
         for (int it = 0; it < total && ok; ++it) {
-            const int s = it % kGemmStages, round = it / kGemmStages;
+            const int s = it % kStages, round = it / kStages;
             ok = mbar_wait(full + s, round & 1);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t sa = smem_u32(smem + s * GemmSmem<BN>::kStage);
-            const uint64_t da = umma_desc_k_sw128(sa), db = umma_desc_k_sw128(sa + GemmSmem<BN>::kA);
+            const uint32_t st = smem_u32(smem + s * SM::kStage);
+            const uint64_t da_hi = umma_desc_k_sw128(st), db_hi = umma_desc_k_sw128(st + SM::kA);
+            const uint64_t da_lo = umma_desc_k_sw128(st + SM::kA + SM::kB);
+            const uint64_t db_lo = umma_desc_k_sw128(st + 2 * SM::kA + SM::kB);
 #pragma unroll
             for (int k = 0; k < kGemmBK / 16; ++k) {
                 // 16 bf16 = 32 bytes further along K inside the swizzle row: +2 in 16-byte units.
-                tc_mma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                tc_mma_bf16(tmem_base, da_hi + 2 * k, db_hi + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                if (SPLIT) {
+                    tc_mma_bf16(tmem_base, da_lo + 2 * k, db_hi + 2 * k, idesc, 1u);
+                    tc_mma_bf16(tmem_base, da_hi + 2 * k, db_lo + 2 * k, idesc, 1u);
+                }
             }
             tc_commit(empty + s);  // arrives once the MMAs above have finished reading the stage
         }
@@ -460,27 +482,35 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t ld
     return PCCNN_OK;
 }
 
+template <int BN, bool SPLIT>
+static int launch_gemm_impl(const CUtensorMap& ma_hi, const CUtensorMap& ma_lo, const CUtensorMap& mb_hi,
+                            const CUtensorMap& mb_lo, float* C, int64_t M, int N, int K_padded, int ldc, int c_is_bf16,
+                            int* status, cudaStream_t s) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<BN, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        NtSmem<BN, SPLIT>::kBytes);
+    });
+    PCCNN_CUDA(attr_err);
+    dim3 grid((unsigned)((M + kGemmBM - 1) / kGemmBM), (unsigned)((N + BN - 1) / BN));
+    gemm_bf16_kernel<BN, SPLIT><<<grid, 128, NtSmem<BN, SPLIT>::kBytes, s>>>(ma_hi, ma_lo, mb_hi, mb_lo, C, (int)M, N, ldc,
+                                                                          K_padded / kGemmBK, c_is_bf16, status);
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
 template <int BN>
 static int launch_gemm(const GemmOperand& a, const GemmOperand& b, float* C, int64_t M, int N, int K_padded, int ldc,
                        int c_is_bf16, int* status, cudaStream_t s) {
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
-    const int passes = (a.lo && b.lo) ? 3 : 1;
+    const bool split = a.lo && b.lo;
     if (int rc = make_map(&ma_hi, a.hi, M, a.ld, kGemmBM)) return rc;
-    if (int rc = make_map(&ma_lo, passes == 3 ? a.lo : a.hi, M, a.ld, kGemmBM)) return rc;
+    if (int rc = make_map(&ma_lo, split ? a.lo : a.hi, M, a.ld, kGemmBM)) return rc;
     if (int rc = make_map(&mb_hi, b.hi, N, b.ld, BN)) return rc;
-    if (int rc = make_map(&mb_lo, passes == 3 ? b.lo : b.hi, N, b.ld, BN)) return rc;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        GemmSmem<BN>::kBytes);
-    });
-    PCCNN_CUDA(attr_err);
-    dim3 grid((unsigned)((M + kGemmBM - 1) / kGemmBM), (unsigned)((N + BN - 1) / BN));
-    gemm_bf16_kernel<BN><<<grid, 128, GemmSmem<BN>::kBytes, s>>>(ma_hi, ma_lo, mb_hi, mb_lo, C, (int)M, N, ldc,
-                                                               K_padded / kGemmBK, passes, c_is_bf16, status);
-    PCCNN_LAUNCH_CHECK();
-    return PCCNN_OK;
+    if (int rc = make_map(&mb_lo, split ? b.lo : b.hi, N, b.ld, BN)) return rc;
+    if (split) return launch_gemm_impl<BN, true>(ma_hi, ma_lo, mb_hi, mb_lo, C, M, N, K_padded, ldc, c_is_bf16, status, s);
+    return launch_gemm_impl<BN, false>(ma_hi, ma_lo, mb_hi, mb_lo, C, M, N, K_padded, ldc, c_is_bf16, status, s);
 }
 
 int gemm_bf16_nt(const GemmOperand& a, const GemmOperand& b, float* C, int64_t M, int N, int K_padded, int ldc,
@@ -600,6 +630,15 @@ int pccnn_gemm_f32(int64_t M, int N, int K, const float* A, int64_t lda, const f
         return PCCNN_ERR_DEVICE;
     }
     return PCCNN_OK;
+}
+
+int pccnn_gemm_bf16(int64_t M, int N, int K, const void* a_hi, const void* a_lo, int64_t lda, const void* b_hi,
+                    const void* b_lo, int64_t ldb, float* C, int64_t ldc, int* status_dev, void* stream) {
+    PCCNN_CHECK_ARG(a_hi && b_hi && C && status_dev, "gemm_bf16: null pointer");
+    PCCNN_CHECK_ARG((a_lo == nullptr) == (b_lo == nullptr), "gemm_bf16: give the lo parts of both operands or of neither");
+    GemmOperand a{const_cast<void*>(a_hi), const_cast<void*>(a_lo), lda};
+    GemmOperand b{const_cast<void*>(b_hi), const_cast<void*>(b_lo), ldb};
+    return gemm_bf16_nt(a, b, C, M, N, K, (int)ldc, status_dev, (cudaStream_t)stream);
 }
 
 size_t pccnn_gemm_tn_workspace_bytes(int64_t rows, int I, int N) {

@@ -364,6 +364,31 @@ def mc_conv(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_proj, ax
     return out
 
 
+def gemm_bf16(a_hi, b_hi, a_lo=None, b_lo=None, out=None, status=None):
+    """The tensor-core kernel alone on bf16 operands a [M, K], b [N, K] (K a multiple of 64, optional
+    low parts for the three-product split) -> [M, N] float32.  Asynchronous; `status` (int32 tensor
+    of one element) is set non-zero by the kernel if one of its bounded waits ran out."""
+    a_hi = _need(a_hi, "a_hi", torch.bfloat16, 2)
+    b_hi = _need(b_hi, "b_hi", torch.bfloat16, 2)
+    if (a_lo is None) != (b_lo is None):
+        raise RuntimeError("gemm_bf16: give the low parts of both operands or of neither")
+    if a_lo is not None:
+        a_lo = _need(a_lo, "a_lo", torch.bfloat16, 2)
+        b_lo = _need(b_lo, "b_lo", torch.bfloat16, 2)
+    m, k = a_hi.shape
+    n = b_hi.shape[0]
+    if k % 64 or b_hi.shape[1] != k:
+        raise RuntimeError("gemm_bf16: K must match and be a multiple of 64")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=a_hi.device)
+    if status is None:
+        status = torch.zeros((1,), dtype=torch.int32, device=a_hi.device)
+    with torch.cuda.device(a_hi.device):
+        _capi.check(_lib.pccnn_gemm_bf16(m, n, k, _p(a_hi), _p(a_lo), a_hi.stride(0), _p(b_hi), _p(b_lo), b_hi.stride(0),
+                                         _p(out), out.stride(0), _p(status), _stream()), "gemm_bf16")
+    return out
+
+
 def gemm_tn_f32(a, b, split=True):
     """a[R, I]^T @ b[R, N] -> [I, N] float32 on the tensor cores (reduction over the rows): the
     weight-gradient contraction of pcconvs/kpconv.cu:90-93 of the reference."""

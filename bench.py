@@ -579,16 +579,21 @@ def run_encoder_workload(args):
 
     def step(record=False):
         pc, feats = lib.pc.Pointcloud(d_pts, d_ids), feats0
-        conv_ms = []
+        conv_ms, geo = [], []
         for level in range(5):
             r_pool = 0.02 * (2 ** level)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ev[0].record()
             pool = lib.pc.PointPooling(pc, np.full((3,), r_pool, np.float32))
             pc_out = lib.pc.Pointcloud(pool.pool_tensor(pc.pts_), pool.pool_tensor(pc.batch_ids_))
+            ev[1].record()
             radius = torch.full((3,), 2.5 * r_pool, dtype=torch.float32, device=device)
             grid = lib.pc.Grid(pc, lib.pc.BoundingBox(pc), radius)
             grid.compute_cell_ids()
             grid.build_ds()
             nb = lib.pc.Neighborhood(grid, pc_out, 0)
+            ev[2].record()
+            geo.append(ev)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             feats = ops.kp_conv(pc.pts_, feats, pc_out.pts_, nb.neighbors_, nb.start_ids_, radius, kpts, sigma,
@@ -599,7 +604,7 @@ def run_encoder_workload(args):
                                                            pairs=int(nb.neighbors_.shape[0])))
             conv_ms.append((e0, e1))
             pc = pc_out
-        return feats, conv_ms
+        return feats, (conv_ms, geo)
 
     step(record=True)
     warm = max(args.warmup, 3)
@@ -618,7 +623,9 @@ def run_encoder_workload(args):
     torch.cuda.synchronize()
     clocks = sampler.finish()
     ms = t0.elapsed_time(t1) / args.steps
-    conv = [float(np.mean([m[l][0].elapsed_time(m[l][1]) for m in marks])) for l in range(5)]
+    conv = [float(np.mean([m[0][l][0].elapsed_time(m[0][l][1]) for m in marks])) for l in range(5)]
+    pooling = [float(np.mean([m[1][l][0].elapsed_time(m[1][l][1]) for m in marks])) for l in range(5)]
+    neighborhoods = [float(np.mean([m[1][l][1].elapsed_time(m[1][l][2]) for m in marks])) for l in range(5)]
     flops = sum(2.0 * lv["samples"] * 16 * channels[l] * channels[l + 1] for l, lv in enumerate(stats["levels"]))
     print(json.dumps({
         "metric": "conv-layer points/s (5-level KPConv encoder, inference)", "value": pts.shape[0] / (ms * 1e-3),
@@ -627,7 +634,8 @@ def run_encoder_workload(args):
         "data": "synthetic",
         "config": {"workload": run_encoder_workload.__doc__.split("  One step")[0].replace("\n    ", " "),
                    "clouds": clouds, "points_per_cloud": num_pts, "levels": stats["levels"], "conv_ms_per_level": conv,
-                   "conv_ms_total": sum(conv), "geometry_ms": ms - sum(conv), "contraction_flop_per_step": flops,
+                   "conv_ms_total": sum(conv), "geometry_ms": ms - sum(conv),
+                   "pooling_ms_per_level": pooling, "neighborhood_ms_per_level": neighborhoods, "contraction_flop_per_step": flops,
                    "finite_output": bool(torch.isfinite(out.float()).all())},
         "clocks": clocks}))
 

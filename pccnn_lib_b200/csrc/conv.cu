@@ -330,6 +330,79 @@ __device__ __forceinline__ void warp_reduce_scatter(float (&v)[KP], int lane, in
     }
 }
 
+// Projection for narrow inputs (Cin * KP <= 64, e.g. the xyz or constant features of a first
+// layer).  With lanes as channels almost every lane would idle; here the lanes stay neighbors for
+// the whole sample: each accumulates its own pairs' f[c] * b[k] products for ALL (c, k) in
+// registers, and one reduce-scatter over the warp leaves every lane with two finished entries of
+// the sample's P row, which is then written with one coalesced store per plane.
+template <int D, int KP, class BASIS, class ARGS, class FT>
+__global__ void __launch_bounds__(128)
+project_narrow_kernel(ARGS args, int K, const float* __restrict__ pts, const FT* __restrict__ feats, int cin,
+                      const float* __restrict__ samples, const int2* __restrict__ neighbors,
+                      const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
+                      __nv_bfloat16* __restrict__ p_hi, __nv_bfloat16* __restrict__ p_lo, int ld_p) {
+    constexpr int CS = 64 / KP;  // channel slots
+    __shared__ float s_params[BASIS::kParamFloats];
+    BASIS::load_params(s_params, args, K);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    float inv[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) inv[d] = __frcp_rn(__ldg(radii + d));
+    const int inner = cin * K;
+
+    for (int m = m_begin + blockIdx.x * 4 + warp; m < m_end; m += gridDim.x * 4) {
+        const int lo = (m > 0) ? __ldg(start_ids + m - 1) : 0;
+        const int hi = __ldg(start_ids + m);
+        float s[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) s[d] = __ldg(samples + (int64_t)m * D + d);
+        float acc[64];
+#pragma unroll
+        for (int e = 0; e < 64; ++e) acc[e] = 0.f;
+        for (int t = lo + lane; t < hi; t += 32) {
+            const int n0 = __ldg(&neighbors[t]).x;
+            float d[D], b[KP], f[CS];
+#pragma unroll
+            for (int c = 0; c < CS; ++c) f[c] = (c < cin) ? load_feat(feats + (int64_t)n0 * cin + c) : 0.f;
+#pragma unroll
+            for (int x = 0; x < D; ++x) d[x] = (__ldg(pts + (int64_t)n0 * D + x) - s[x]) * inv[x];
+            BASIS::eval(s_params, args, K, d, n0, b);
+#pragma unroll
+            for (int c = 0; c < CS; ++c)
+#pragma unroll
+                for (int k = 0; k < KP; ++k) acc[c * KP + k] = fmaf(f[c], b[k], acc[c * KP + k]);
+        }
+        int e0, n;
+        warp_reduce_scatter<64>(acc, lane, e0, n);  // n == 2: this lane owns entries e0 and e0 + 1 (c = e / KP, k = e % KP)
+        const size_t row = (size_t)(m - m_begin) * ld_p;
+        if (K == KP) {
+            // entry e sits at column e; columns past Cin * K up to ld_p (= 64) are the zero slots c >= Cin
+            const float v0 = acc[0], v1 = acc[1];
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+            *reinterpret_cast<__nv_bfloat162*>(p_hi + row + e0) = h2;
+            if (p_lo)
+                *reinterpret_cast<__nv_bfloat162*>(p_lo + row + e0) =
+                    __floats2bfloat162_rn(v0 - __low2float(h2), v1 - __high2float(h2));
+        } else {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int e = e0 + q, c = e / KP, k = e - c * KP;
+                if (c < cin && k < K) {
+                    const float v = acc[q];
+                    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+                    p_hi[row + (size_t)c * K + k] = h;
+                    if (p_lo) p_lo[row + (size_t)c * K + k] = __float2bfloat16_rn(v - __bfloat162float(h));
+                }
+            }
+            for (int c = inner + lane; c < ld_p; c += 32) {
+                p_hi[row + c] = __float2bfloat16_rn(0.f);
+                if (p_lo) p_lo[row + c] = __float2bfloat16_rn(0.f);
+            }
+        }
+    }
+}
+
 // Everything of the backward pass that runs per neighbor pair, given dP = g W^T for the samples
 // [m_begin, m_end) (pccnn_lib_ops/pcconvs/shared/feat_basis_proj_grads.cu:32-154, then the basis
 // and offset gradients of kernel_pts_basis.cu:41-70 / mlp_basis.cu:50-96 and pt_diff.cu:51-80 of
@@ -537,7 +610,12 @@ static int launch_project(int K, const ARGS& args, const float* pts, const FT* f
 #define PCCNN_PROJECT(KP)                                                        \
     do {                                                                         \
         constexpr int kMax = 64 / KP;                                            \
-        if (kMax >= 8 && cin > 128) PCCNN_PROJECT_C(KP, (kMax >= 8 ? 8 : kMax)); \
+        if (cin <= kMax)                                                         \
+            project_narrow_kernel<D, KP, BASIS<D, KP>, ARGS, FT>                 \
+                <<<grid_for((int64_t)count * 32, 128, 8), 128, 0, s>>>(          \
+                    args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids, radii, m_begin, \
+                    m_end, (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo, ld_p);     \
+        else if (kMax >= 8 && cin > 128) PCCNN_PROJECT_C(KP, (kMax >= 8 ? 8 : kMax)); \
         else if (kMax >= 4 && cin > 64) PCCNN_PROJECT_C(KP, (kMax >= 4 ? 4 : kMax)); \
         else if (kMax >= 2 && cin > 32) PCCNN_PROJECT_C(KP, (kMax >= 2 ? 2 : kMax)); \
         else PCCNN_PROJECT_C(KP, 1);                                             \

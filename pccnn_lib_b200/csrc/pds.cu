@@ -7,11 +7,12 @@
 // run in parallel; inside a cell the points are taken in ascending sorted position and a
 // point is selected iff none of its radius neighbors has been selected before.
 //
-// Design: the reference spends one thread per cell and walks points x neighbors serially.
-// Here a warp owns a cell: the points stay sequential (that is the algorithm) but the lanes
-// scan a point's neighbor rows 32 at a time with coalesced loads and stop at the first
-// selected neighbor.  Cell boundaries and the final index list come from device-wide stream
-// compaction; nothing is copied from the host between passes.
+// Design: the reference spends one thread per cell and walks points x neighbors serially, each
+// step waiting on dependent loads.  Here a warp owns a cell and takes 32 of its points at a time:
+// the lanes scan their points' neighbor lists in parallel (all memory latency overlaps), and the
+// order-dependent part (a point is rejected if an EARLIER point of the same group that is its
+// neighbor was selected) runs on bit masks in registers.  Cell boundaries and the final index
+// list come from device-wide stream compaction; nothing is copied from the host between passes.
 #include <cub/device/device_select.cuh>
 #include <thrust/iterator/counting_iterator.h>
 
@@ -21,7 +22,6 @@
 
 namespace pccnn {
 
-constexpr int kPdsWarps = 4;
 
 __global__ void cell_flags_kernel(int n, const int64_t* __restrict__ keys, int32_t* __restrict__ flags) {
     const int stride = gridDim.x * blockDim.x;
@@ -29,41 +29,221 @@ __global__ void cell_flags_kernel(int n, const int64_t* __restrict__ keys, int32
         flags[i] = (i == 0 || keys[i] != keys[i - 1]) ? 1 : 0;
 }
 
+// Cells are routed once, before the passes: `code` holds the pass a cell belongs to (bit d = parity of
+// its index in dimension d) and bit 7 marks a "crowded" cell, which also goes on the `crowded` list.
+// Crowded = more than 32 points, or neighbor lists adding up to kCrowdedEntries or more: a single warp
+// would be busy with such a cell long after the rest of the pass has finished.
+constexpr int kCrowdedMaxPoints = 512;
+constexpr int kCrowdedEntries = 1024;
+constexpr int kPdsThreads = 512;
+constexpr unsigned kCrowdedBit = 0x80u;
+
 template <int D>
-__global__ void __launch_bounds__(kPdsWarps * 32)
-pds_pass_kernel(int pass, int n, const int64_t* __restrict__ keys, const int32_t* __restrict__ cell_starts,
-                const int32_t* __restrict__ num_cells_ptr, const int2* __restrict__ neighbors,
-                const int32_t* __restrict__ start_ids, const int32_t* __restrict__ grid_size, int32_t* used) {
+__global__ void cell_route_kernel(int n, const int64_t* __restrict__ keys, const int32_t* __restrict__ cell_starts,
+                                  const int32_t* __restrict__ start_ids, const int32_t* __restrict__ grid_size,
+                                  int32_t* counters, unsigned char* __restrict__ code, int32_t* __restrict__ crowded,
+                                  int crowded_capacity) {
     const GridDesc<D> g = load_grid<D>(grid_size);
-    const int num_cells = *num_cells_ptr;
+    const int num_cells = counters[0];
+    const int stride = gridDim.x * blockDim.x;
+    for (int cell = blockIdx.x * blockDim.x + threadIdx.x; cell < num_cells; cell += stride) {
+        const int first = cell_starts[cell];
+        const int last = (cell + 1 < num_cells) ? cell_starts[cell + 1] : n;
+        int c[D];
+        key_to_cell<D>(keys[first], g, c);
+        unsigned v = 0;
+#pragma unroll
+        for (int d = 0; d < D; ++d) v |= (unsigned)(c[d] & 1) << d;
+        const int count = last - first;
+        const int entries = start_ids[last - 1] - (first > 0 ? start_ids[first - 1] : 0);
+        if ((count > 32 || entries >= kCrowdedEntries) && count <= kCrowdedMaxPoints) {
+            const int slot = atomicAdd(counters + 2, 1);
+            if (slot < crowded_capacity) {
+                crowded[slot] = cell;
+                v |= kCrowdedBit;
+            }
+        }
+        code[cell] = (unsigned char)v;
+    }
+}
+
+// The in-order decisions of up to 32 consecutive points of one cell, [p0, group_end), given for the
+// lane's point p = p0 + lane its `blocked` flag (a neighbor decided earlier is selected) and the mask
+// of its neighbors inside the group.  Registers and shuffles only.  Returns the selected mask.
+__device__ __forceinline__ unsigned decide_group(int count, bool blocked, unsigned in_group) {
+    unsigned selected = 0u;
+    for (int q = 0; q < count; ++q) {
+        const bool take = !blocked && (in_group & selected) == 0u;  // meaningful in lane q
+        selected |= __shfl_sync(kFullMask, take ? 1u : 0u, q) << q;
+    }
+    return selected;
+}
+
+// One group of up to 32 consecutive points of a cell, [p0, p0 + count): lane `slot0 + i` holds point
+// p0 + i.  Scans the lane's neighbor list once, noting (a) whether a neighbor decided earlier (other
+// cells, earlier passes, earlier groups of the cell) is selected and (b) which points of the group are
+// its neighbors.  No early exit and no short-circuit: the loads of different neighbors stay
+// independent of one another, so many are in flight at once.
+__device__ __forceinline__ void scan_own_list(int p, int p0, int count, int slot0, const int2* __restrict__ neighbors,
+                                              const int32_t* __restrict__ start_ids, volatile int32_t* vused,
+                                              bool& blocked, unsigned& in_group) {
+    const int lo = (p > 0) ? __ldg(start_ids + p - 1) : 0;
+    const int hi = __ldg(start_ids + p);
+#pragma unroll 4
+    for (int t = lo; t < hi; ++t) {
+        const int j = __ldg(&neighbors[t]).x;
+        const bool same_group = j >= p0 && j < p0 + count;
+        if (same_group) in_group |= 1u << (j - p0 + slot0);
+        const int flag = vused[same_group ? p : j];  // own flag is still 0: a harmless read
+        blocked = blocked | (flag != 0);
+    }
+}
+
+// Warp role: cells of this pass that are not on the crowded list, 32 cells looked at at a time.  Most
+// cells hold a handful of points, so the points of SEVERAL cells share the 32 lanes of a round: cells
+// of one pass never interact, and inside a round a lane's in-group mask only covers its own cell.
+__device__ void pds_sparse_cells(int pass, int n, int warp_index, int warps_total, int num_cells,
+                                 const int32_t* __restrict__ cell_starts, const unsigned char* __restrict__ code,
+                                 const int2* __restrict__ neighbors, const int32_t* __restrict__ start_ids,
+                                 int32_t* used) {
     const int lane = lane_id();
     volatile int32_t* vused = used;
-    const int warps_total = gridDim.x * kPdsWarps;
-    for (int cell = blockIdx.x * kPdsWarps + (threadIdx.x >> 5); cell < num_cells; cell += warps_total) {
-        const int first = __ldg(cell_starts + cell);
-        const int last = (cell + 1 < num_cells) ? __ldg(cell_starts + cell + 1) : n;
-        int c[D];
-        key_to_cell<D>(__ldg(keys + first), g, c);
-        bool mine = true;
+    for (int base = warp_index * 32; base < num_cells; base += warps_total * 32) {
+        const int cell = base + lane;
+        const bool want = cell < num_cells && __ldg(code + cell) == (unsigned)pass;
+        int my_first = 0, my_count = 0;
+        if (want) {
+            my_first = __ldg(cell_starts + cell);
+            my_count = ((cell + 1 < num_cells) ? __ldg(cell_starts + cell + 1) : n) - my_first;
+        }
+        // Cells with more than 32 points (beyond the crowded kernel's capacity): alone, group after group.
+        unsigned big = __ballot_sync(kFullMask, my_count > 32);
+        while (big) {
+            const int src = __ffs(big) - 1;
+            big &= big - 1;
+            const int first = __shfl_sync(kFullMask, my_first, src);
+            const int last = first + __shfl_sync(kFullMask, my_count, src);
+            for (int p0 = first; p0 < last; p0 += 32) {
+                const int p = p0 + lane, count = min(32, last - p0);
+                bool blocked = false;
+                unsigned in_group = 0u;
+                if (p < last) scan_own_list(p, p0, count, 0, neighbors, start_ids, vused, blocked, in_group);
+                const unsigned selected = decide_group(count, blocked, in_group);
+                if (p < last && ((selected >> lane) & 1u)) vused[p] = 1;
+                __syncwarp();  // orders the stores before the next group's loads in this warp
+            }
+        }
+        if (my_count > 32) my_count = 0;
+        // Exclusive prefix sum of the remaining counts: lane i's cell would start at slot my_off.
+        int my_off = my_count;
 #pragma unroll
-        for (int d = 0; d < D; ++d) mine = mine && ((c[d] & 1) == ((pass >> d) & 1));
-        if (!mine) continue;
-        for (int p = first; p < last; ++p) {
-            const int lo = (p > 0) ? __ldg(start_ids + p - 1) : 0;
-            const int hi = __ldg(start_ids + p);
-            bool blocked = false;
-            for (int t0 = lo; t0 < hi; t0 += 32) {
-                const int t = t0 + lane;
-                bool b = false;
-                if (t < hi) b = vused[__ldg(&neighbors[t]).x] != 0;
-                if (__any_sync(kFullMask, b)) {
-                    blocked = true;
-                    break;
+        for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(kFullMask, my_off, d);
+            if (lane >= d) my_off += v;
+        }
+        my_off -= my_count;
+        unsigned todo = __ballot_sync(kFullMask, my_count > 0);
+        while (todo) {
+            // this round: the longest run of remaining cells whose points fit 32 slots
+            const int lead = __ffs(todo) - 1;
+            const int off0 = __shfl_sync(kFullMask, my_off, lead);
+            const bool in_round = my_count > 0 && lane >= lead && my_off + my_count - off0 <= 32;
+            const unsigned round = __ballot_sync(kFullMask, in_round);
+            todo &= ~round;
+            int p = -1, p0 = 0, count = 0, slot0 = 0;
+            for (unsigned cells = round; cells; cells &= cells - 1) {
+                const int src = __ffs(cells) - 1;
+                const int o = __shfl_sync(kFullMask, my_off, src) - off0;
+                const int c = __shfl_sync(kFullMask, my_count, src);
+                const int f = __shfl_sync(kFullMask, my_first, src);
+                if (lane >= o && lane < o + c) {
+                    p = f + lane - o;
+                    p0 = f;
+                    count = c;
+                    slot0 = o;
                 }
             }
-            if (!blocked && lane == 0) vused[p] = 1;
-            __syncwarp();  // orders the store before the next point's loads in this warp
+            bool blocked = true;  // lanes without a point never select
+            unsigned in_group = 0u;
+            if (p >= 0) {
+                blocked = false;
+                scan_own_list(p, p0, count, slot0, neighbors, start_ids, vused, blocked, in_group);
+            }
+            const unsigned selected = decide_group(32, blocked, in_group);
+            if (p >= 0 && ((selected >> lane) & 1u)) vused[p] = 1;
         }
+    }
+}
+
+// Block role: crowded cells, one thread block per cell.  Everything that does not depend on the order
+// of the cell's points is done first, by all warps: a warp streams the neighbor list of a point with
+// coalesced loads and records (a) whether a selected point outside the cell is among them and (b) the
+// neighbors inside the cell, as one row of a bit matrix in shared memory.  The in-order decisions
+// are then a walk of warp 0 over that matrix: lane w keeps word w of the selected set.
+__device__ void pds_crowded_cells(int pass, int n, int block_index, int blocks_total, int num_cells, int num_crowded,
+                                  const int32_t* __restrict__ cell_starts, const unsigned char* __restrict__ code,
+                                  const int32_t* __restrict__ crowded, const int2* __restrict__ neighbors,
+                                  const int32_t* __restrict__ start_ids, int32_t* used, unsigned* s_adj,
+                                  unsigned char* s_blocked) {
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    for (int i = block_index; i < num_crowded; i += blocks_total) {
+        const int cell = __ldg(crowded + i);
+        if ((__ldg(code + cell) & ~kCrowdedBit) != (unsigned)pass) continue;  // uniform over the block
+        const int first = __ldg(cell_starts + cell);
+        const int last = (cell + 1 < num_cells) ? __ldg(cell_starts + cell + 1) : n;
+        const int count = last - first, words = (count + 31) >> 5;
+        for (int k = threadIdx.x; k < count * words; k += kPdsThreads) s_adj[k] = 0u;
+        for (int k = threadIdx.x; k < count; k += kPdsThreads) s_blocked[k] = 0;
+        __syncthreads();
+        for (int q = warp; q < count; q += kPdsThreads / 32) {
+            const int p = first + q;
+            const int lo = (p > 0) ? __ldg(start_ids + p - 1) : 0;
+            const int hi = __ldg(start_ids + p);
+            bool flag = false;
+#pragma unroll 8
+            for (int t = lo + lane; t < hi; t += 32) {
+                const int j = __ldg(&neighbors[t]).x;
+                const bool inside = j >= first && j < last;
+                if (inside) atomicOr(&s_adj[q * words + ((j - first) >> 5)], 1u << ((j - first) & 31));
+                flag = flag | (used[inside ? p : j] != 0);  // points of this cell are all undecided: 0
+            }
+            if (__any_sync(kFullMask, flag) && lane == 0) s_blocked[q] = 1;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            unsigned selected = 0u;  // lane w: points [32 w, 32 w + 32) of the cell
+            for (int q = 0; q < count; ++q) {
+                const unsigned row = (lane < words) ? s_adj[q * words + lane] : 0u;
+                const bool hit = __any_sync(kFullMask, (row & selected) != 0u);
+                if (!hit && !s_blocked[q] && lane == (q >> 5)) selected |= 1u << (q & 31);
+            }
+            while (selected) {
+                used[first + lane * 32 + __ffs(selected) - 1] = 1;
+                selected &= selected - 1;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// One launch per pass.  The first `crowded_blocks` blocks take the crowded cells, the others the rest;
+// the two kinds of cell never interact inside a pass, so the roles overlap freely.
+__global__ void __launch_bounds__(kPdsThreads)
+pds_pass_kernel(int pass, int n, int crowded_blocks, const int32_t* __restrict__ cell_starts,
+                const int32_t* __restrict__ counters, const unsigned char* __restrict__ code,
+                const int32_t* __restrict__ crowded, int crowded_capacity, const int2* __restrict__ neighbors,
+                const int32_t* __restrict__ start_ids, int32_t* used) {
+    __shared__ unsigned s_adj[kCrowdedMaxPoints * (kCrowdedMaxPoints / 32)];
+    __shared__ unsigned char s_blocked[kCrowdedMaxPoints];
+    const int num_cells = counters[0];
+    if ((int)blockIdx.x < crowded_blocks) {
+        pds_crowded_cells(pass, n, blockIdx.x, crowded_blocks, num_cells, min(counters[2], crowded_capacity), cell_starts,
+                          code, crowded, neighbors, start_ids, used, s_adj, s_blocked);
+    } else {
+        constexpr int kWarps = kPdsThreads / 32;
+        pds_sparse_cells(pass, n, ((int)blockIdx.x - crowded_blocks) * kWarps + (threadIdx.x >> 5),
+                         ((int)gridDim.x - crowded_blocks) * kWarps, num_cells, cell_starts, code, neighbors, start_ids,
+                         used);
     }
 }
 
@@ -116,7 +296,14 @@ int pccnn_poisson_disk_sampling(int D, int64_t n, const int64_t* sorted_keys, co
     int32_t* flags = (int32_t*)(ws + L.flags_off);
     int32_t* cells = (int32_t*)(ws + L.cells_off);
     int32_t* used = (int32_t*)(ws + L.used_off);
-    int32_t* counters = (int32_t*)(ws + L.counters_off);  // [0] = occupied cells, [1] = selected points
+    int32_t* counters = (int32_t*)(ws + L.counters_off);  // [0] = occupied cells, [1] = selected points, [2] = crowded cells
+    // The cell-boundary flags are dead once the cell list exists; their 4 n bytes then hold one routing
+    // byte per cell (at most n cells) and, behind those, the crowded-cell list.  A cell that finds the
+    // list full stays with the warp-per-cell kernel, which handles any cell.
+    unsigned char* code = (unsigned char*)flags;
+    const size_t code_bytes = align_up((size_t)n);
+    int32_t* crowded = (int32_t*)(ws + L.flags_off + code_bytes);
+    const int crowded_capacity = (int)((L.cells_off - L.flags_off > code_bytes ? L.cells_off - L.flags_off - code_bytes : 0) / 4);
     const int nn = (int)n;
 
     cell_flags_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>(nn, sorted_keys, flags);
@@ -125,11 +312,17 @@ int pccnn_poisson_disk_sampling(int D, int64_t n, const int64_t* sorted_keys, co
     PCCNN_CUDA(cub::DeviceSelect::Flagged(ws + L.cub_off, cub_bytes, thrust::counting_iterator<int32_t>(0), flags,
                                           cells, counters, nn, s));
     PCCNN_CUDA(cudaMemsetAsync(used, 0, (size_t)n * 4, s));
-    const unsigned grid = grid_for(n * 32, kPdsWarps * 32, 16);
+    PCCNN_CUDA(cudaMemsetAsync(counters + 2, 0, 4, s));
+    PCCNN_DISPATCH_DIM(D, (cell_route_kernel<DIM><<<grid_for(n, 256, 8), 256, 0, s>>>(
+                              nn, sorted_keys, cells, start_ids, grid_size, counters, code, crowded, crowded_capacity)));
+    PCCNN_LAUNCH_CHECK();
+    // two blocks of each role per SM: 2048 threads and 4 x 33 KB of shared memory, all resident at once
+    const int crowded_blocks = 2 * sm_count();
+    const unsigned sparse_blocks = grid_for((n + 31) / 32 * 32, kPdsThreads, 2);
     for (int pass = 0; pass < (1 << D); ++pass) {
-        PCCNN_DISPATCH_DIM(D, (pds_pass_kernel<DIM><<<grid, kPdsWarps * 32, 0, s>>>(
-                                  pass, nn, sorted_keys, cells, counters, (const int2*)neighbors, start_ids,
-                                  grid_size, used)));
+        pds_pass_kernel<<<crowded_blocks + sparse_blocks, kPdsThreads, 0, s>>>(
+            pass, nn, crowded_blocks, cells, counters, code, crowded, crowded_capacity, (const int2*)neighbors, start_ids,
+            used);
         PCCNN_LAUNCH_CHECK();
     }
     cub_bytes = L.cub_bytes;

@@ -15,12 +15,17 @@ KP_CASES = [dict(seed=33, batch=4, n=100, dims=3, cin=32, cout=64, k=16, radius=
 MC_CASES = [dict(seed=33, batch=4, n=100, dims=3, cin=32, cout=64, k=16, radius=0.25, bw=0.1),
             dict(seed=33, batch=4, n=250, dims=3, cin=32, cout=4, k=16, radius=0.125, bw=0.1),
             dict(seed=33, batch=4, n=250, dims=2, cin=32, cout=4, k=16, radius=0.125, bw=0.1),
-            dict(seed=33, batch=4, n=250, dims=4, cin=32, cout=4, k=16, radius=0.25, bw=0.1)]
+            dict(seed=33, batch=4, n=250, dims=4, cin=32, cout=4, k=16, radius=0.25, bw=0.1),
+            dict(seed=34, batch=2, n=300, dims=3, cin=3, cout=8, k=16, radius=0.2, bw=0.1)]
 # shapes the reference cannot run: odd kernel-point count, channels not a multiple of 8, pooled samples
 EXTRA_KP_CASES = [dict(seed=5, batch=3, n=400, dims=3, cin=3, cout=64, k=16, radius=0.2),
                   dict(seed=6, batch=2, n=300, dims=3, cin=20, cout=10, k=15, radius=0.2),
                   dict(seed=7, batch=2, n=500, dims=3, cin=70, cout=130, k=32, radius=0.15, pooled=True),
-                  dict(seed=8, batch=2, n=300, dims=3, cin=16, cout=300, k=64, radius=0.2)]
+                  dict(seed=8, batch=2, n=300, dims=3, cin=16, cout=300, k=64, radius=0.2),
+                  # narrow inputs (Cin * K <= 64 slots): the lanes-as-neighbors projection
+                  dict(seed=9, batch=2, n=300, dims=3, cin=2, cout=12, k=15, radius=0.2),
+                  dict(seed=10, batch=2, n=300, dims=2, cin=1, cout=8, k=64, radius=0.2),
+                  dict(seed=11, batch=2, n=300, dims=3, cin=5, cout=8, k=8, radius=0.2)]
 
 
 def base_case(clouds, c, normal_feats=False):

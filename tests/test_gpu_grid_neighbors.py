@@ -132,21 +132,29 @@ def test_pdf_and_grads_match_oracle(ref_clouds, batch_size, num_pts, num_dims, b
 
 
 PDS_CASES = [(4, 1000, 2, 0.1), (4, 1000, 3, 0.1), (4, 1000, 6, 0.1), (32, 100, 2, 3.0), (32, 100, 3, 3.0),
-             (21, 100, 6, 3.0), (16, 1000, 3, 0.03), (8, 1000, 3, 0.3)]
+             (21, 100, 6, 3.0), (16, 1000, 3, 0.03), (8, 1000, 3, 0.3),
+             # crowded cells (block per cell), cells beyond the block kernel's 512 points, thinned (one-sided) lists
+             (4, 1000, 3, 0.5), (3, 1000, 2, 0.4), (2, 1000, 3, 1.0), (2, 1000, 4, 0.7),
+             (4, 1000, 3, 0.5, 8), (8, 1000, 3, 0.3, 5), (2, 1000, 3, 1.0, 40)]
 
 
-@pytest.mark.parametrize("batch_size,num_pts,num_dims,radius", PDS_CASES)
-def test_poisson_disk_selection_is_identical(ref_clouds, batch_size, num_pts, num_dims, radius):
+@pytest.mark.parametrize("case", PDS_CASES, ids=lambda c: "-".join(str(v) for v in c))
+def test_poisson_disk_selection_is_identical(ref_clouds, case):
+    batch_size, num_pts, num_dims, radius = case[:4]
+    max_neighs = case[4] if len(case) > 4 else 0
     from pccnn_lib_b200 import ops
     pts, batch_ids = ref_case(ref_clouds, batch_size, num_pts, num_dims)
     cell = np.full((num_dims,), radius, np.float32)
     g = gpu_grid(pts, batch_ids, batch_size, cell)
     o = oracle.build_grid(pts, batch_ids, batch_size, cell)
     gn, gs = ops.find_neighbors(g["sorted_pts"], g["sorted_keys"], g["sorted_pts"], g["sorted_keys"], g["grid_ds"],
-                                g["num_cells"], g["cell"], 0)
-    on, os_ = oracle.find_neighbors(o["sorted_pts"], o["sorted_keys"], o["sorted_pts"], o["sorted_keys"], o["grid_ds"],
-                                    o["num_cells"], cell, 0)
-    assert np.array_equal(gn.cpu().numpy(), on)
+                                g["num_cells"], g["cell"], max_neighs)
+    # the oracle's thinning keeps other rows than the library's: both selections run on the library's lists
+    on, os_ = gn.cpu().numpy(), gs.cpu().numpy()
+    if max_neighs == 0:
+        on0, os0 = oracle.find_neighbors(o["sorted_pts"], o["sorted_keys"], o["sorted_pts"], o["sorted_keys"],
+                                         o["grid_ds"], o["num_cells"], cell, 0)
+        assert np.array_equal(on, on0) and np.array_equal(os_, os0)
     got = ops.poisson_disk_sampling(g["sorted_keys"], gn, gs, g["num_cells"])
     expect = oracle.poisson_disk_sampling(o["sorted_keys"], on, os_, o["num_cells"])
     assert got.dtype == torch.int64 and got.dim() == 2 and got.shape[1] == 1

@@ -121,6 +121,32 @@ __device__ __forceinline__ int resolve_ranges(long long key, const GridDesc<D>& 
     return carry;
 }
 
+// Packed fp32x2 arithmetic (sm_100): both halves are rounded to nearest, as by the scalar
+// __fsub_rn / __fmul_rn / __fmaf_rn.
+__device__ __forceinline__ unsigned long long pack_f32x2(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long sub_f32x2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long mul_f32x2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 enum : int { kCount = 0, kStore = 1, kStoreLimited = 2 };
 
 constexpr unsigned kNoMask = 0xffffffffu;
@@ -330,15 +356,38 @@ neighbors_kernel(int num_pts, const float* __restrict__ pts, const int64_t* __re
                             const float4 v = slots[q * S::kSlots + ci * 32 + lane];
                             w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
                         }
+                        // Two samples per instruction: the packed fp32x2 forms round each half exactly like
+                        // the scalar operation (round to nearest, no flush), so the predicate keeps its bits,
+                        // and they take one issue slot instead of two in a loop that is bound by issue.
+                        float dist2[kGroup];
 #pragma unroll
-                        for (int gi = 0; gi < kGroup; ++gi) {
-                            float acc = 0.f;
+                        for (int gi = 0; gi < kGroup; gi += 2) {
+                            if (MODE != kCount) {  // the rarely used recomputing store keeps its register budget
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    float acc = 0.f;
+#pragma unroll
+                                    for (int d = 0; d < D; ++d) {
+                                        const float v = __fmul_rn(__fsub_rn(s[gi + h][d], w[d]), inv[d]);
+                                        acc = (d == 0) ? __fmul_rn(v, v) : __fmaf_rn(v, v, acc);
+                                    }
+                                    dist2[gi + h] = acc;
+                                }
+                                continue;
+                            }
+                            unsigned long long acc2 = 0ull;
 #pragma unroll
                             for (int d = 0; d < D; ++d) {
-                                const float v = __fmul_rn(__fsub_rn(s[gi][d], w[d]), inv[d]);
-                                acc = (d == 0) ? __fmul_rn(v, v) : __fmaf_rn(v, v, acc);
+                                const unsigned long long v =
+                                    mul_f32x2(sub_f32x2(pack_f32x2(s[gi][d], s[gi + 1][d]), pack_f32x2(w[d], w[d])),
+                                              pack_f32x2(inv[d], inv[d]));
+                                acc2 = (d == 0) ? mul_f32x2(v, v) : fma_f32x2(v, v, acc2);
                             }
-                            const bool hit = acc < 1.0f;
+                            unpack_f32x2(acc2, dist2[gi], dist2[gi + 1]);
+                        }
+#pragma unroll
+                        for (int gi = 0; gi < kGroup; ++gi) {
+                            const bool hit = dist2[gi] < 1.0f;
                             const unsigned bal = __ballot_sync(kFullMask, hit);
                             if (MODE == kCount) {
                                 if (lane == ci) word[gi] = bal;  // lane ci keeps the bits of group ci

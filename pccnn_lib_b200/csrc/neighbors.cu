@@ -121,32 +121,6 @@ __device__ __forceinline__ int resolve_ranges(long long key, const GridDesc<D>& 
     return carry;
 }
 
-// Packed fp32x2 arithmetic (sm_100): both halves are rounded to nearest, as by the scalar
-// __fsub_rn / __fmul_rn / __fmaf_rn.
-__device__ __forceinline__ unsigned long long pack_f32x2(float a, float b) {
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& a, float& b) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ unsigned long long sub_f32x2(unsigned long long a, unsigned long long b) {
-    unsigned long long r;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ unsigned long long mul_f32x2(unsigned long long a, unsigned long long b) {
-    unsigned long long r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
-    unsigned long long r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-
 enum : int { kCount = 0, kStore = 1, kStoreLimited = 2 };
 
 constexpr unsigned kNoMask = 0xffffffffu;

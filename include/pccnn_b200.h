@@ -88,6 +88,21 @@ int pccnn_sort_keys(int64_t n, const int64_t* keys, int key_bits, int64_t* out_s
                     int64_t* out_sorted_ids, int D, const float* pts, float* out_sorted_pts,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* Fused grid front end: bounding boxes, cells per axis, keys, stable sort and the sorted copies
+ * in one call with ONE host synchronisation (the cells per axis are also returned on the host,
+ * because the caller sizes the cell table with them).  Equivalent to pccnn_bounding_box +
+ * pccnn_grid_num_cells + pccnn_compute_keys + pccnn_sort_keys with the key bits derived from the
+ * grid size; replaces the caller-side sequence BoundingBox.__init__ (pccnn_lib/pc/BoundingBox.py:
+ * 10-18), Grid.__init__ and Grid.compute_cell_ids (pc/Grid.py:10-52) and the gathers of
+ * pc/Grid.py:68-70 / pc/Neighborhood.py:27-32 of the reference.  All outputs as in those calls;
+ * out_grid_size_host: D int32 values in host memory. */
+size_t pccnn_grid_front_end_workspace_bytes(int64_t n);
+int pccnn_grid_front_end(int D, int64_t n, const float* pts, const int32_t* batch_ids,
+                         int64_t num_batches, const float* cell_size, float* out_aabb_min,
+                         float* out_aabb_max, int32_t* out_grid_size, int32_t* out_grid_size_host,
+                         int64_t* out_keys, int64_t* out_sorted_keys, int64_t* out_sorted_ids,
+                         float* out_sorted_pts, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Cell-range table over SORTED keys: entry (b, c0, c1) = [first, last+1) positions of
  * the points whose cell starts with (c0, c1); untouched entries stay (0, 0).
  * out_grid_ds: [num_entries, 2] int32, num_entries = B*nc0*nc1; zero-filled here.

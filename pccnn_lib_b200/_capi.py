@@ -23,6 +23,9 @@ SIGNATURES = {
     "pccnn_compute_keys": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "pccnn_sort_keys_workspace_bytes": (_size, [_c_i64]),
     "pccnn_sort_keys": (_c_int, [_c_i64, _ptr, _c_int, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _size, _ptr]),
+    "pccnn_grid_front_end_workspace_bytes": (_size, [_c_i64]),
+    "pccnn_grid_front_end": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_i64, _ptr, _ptr, _ptr, _ptr,
+                                      ctypes.POINTER(_c_i32), _ptr, _ptr, _ptr, _ptr, _ptr, _size, _ptr]),
     "pccnn_build_grid_ds": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_i64, _ptr, _ptr]),
     "pccnn_find_neighbors_workspace_bytes": (_size, [_c_int, _c_i64]),
     "pccnn_find_neighbors_min_workspace_bytes": (_size, [_c_int, _c_i64]),

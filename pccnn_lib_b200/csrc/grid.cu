@@ -319,6 +319,34 @@ int pccnn_sort_keys(int64_t n, const int64_t* keys, int key_bits, int64_t* out_s
     return PCCNN_OK;
 }
 
+size_t pccnn_grid_front_end_workspace_bytes(int64_t n) { return sort_layout(n < 0 ? 0 : n).total; }
+
+int pccnn_grid_front_end(int D, int64_t n, const float* pts, const int32_t* batch_ids, int64_t num_batches,
+                         const float* cell_size, float* out_aabb_min, float* out_aabb_max, int32_t* out_grid_size,
+                         int32_t* out_grid_size_host, int64_t* out_keys, int64_t* out_sorted_keys,
+                         int64_t* out_sorted_ids, float* out_sorted_pts, void* workspace, size_t workspace_bytes,
+                         void* stream) {
+    PCCNN_CHECK_ARG(D >= kMinDims && D <= kMaxDims, "grid_front_end: point dimension %d outside [2, 6]", D);
+    PCCNN_CHECK_ARG(n >= 0 && n < 0x7fffffffLL && num_batches > 0, "grid_front_end: bad sizes");
+    PCCNN_CHECK_ARG(out_grid_size && out_grid_size_host && cell_size, "grid_front_end: null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (int rc = pccnn_bounding_box(D, n, pts, batch_ids, num_batches, out_aabb_min, out_aabb_max, stream)) return rc;
+    if (int rc = pccnn_grid_num_cells(D, num_batches, out_aabb_min, out_aabb_max, cell_size, out_grid_size, stream))
+        return rc;
+    // The one host round trip: the cells per axis size the caller's table and bound the key bits.  The
+    // key kernel does not need it and is queued first.
+    if (int rc = pccnn_compute_keys(D, n, pts, batch_ids, out_aabb_min, out_grid_size, cell_size, out_keys, stream))
+        return rc;
+    PCCNN_CUDA(cudaMemcpyAsync(out_grid_size_host, out_grid_size, (size_t)D * 4, cudaMemcpyDeviceToHost, s));
+    PCCNN_CUDA(cudaStreamSynchronize(s));
+    double span = (double)num_batches;
+    for (int d = 0; d < D; ++d) span *= (double)out_grid_size_host[d];
+    int key_bits = 1;
+    while (key_bits < 64 && (double)(1ull << key_bits) < span + 1.0) ++key_bits;
+    return pccnn_sort_keys(n, out_keys, key_bits, out_sorted_keys, out_sorted_ids, D, pts, out_sorted_pts, workspace,
+                           workspace_bytes, stream);
+}
+
 int pccnn_build_grid_ds(int D, int64_t n, const int64_t* sorted_keys, const int32_t* grid_size,
                         int64_t num_entries, int32_t* out_grid_ds, void* stream) {
     PCCNN_CHECK_ARG(n >= 0 && num_entries >= 0, "build_grid_ds: negative size");

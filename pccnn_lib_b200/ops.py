@@ -119,6 +119,41 @@ def sort_keys(keys, key_bits=64, pts=None):
     return sorted_keys, sorted_ids, sorted_pts
 
 
+def grid_front_end(pts, batch_ids, num_batches, cell_size):
+    """Bounding boxes, cells per axis, keys, stable sort, sorted copies and the cell table of one
+    point set in two library calls and one host synchronisation.
+
+    The caller-side sequence BoundingBox / Grid.__init__ / compute_cell_ids / build_ds of the
+    reference (pccnn_lib/pc/BoundingBox.py:10-18, pc/Grid.py:10-72) as one operator.  Returns a dict
+    with aabb_min, aabb_max, num_cells (device int32), num_cells_host (list), keys, sorted_keys,
+    sorted_ids, sorted_pts, grid_ds.
+    """
+    pts = _need(pts, "pts", torch.float32, 2)
+    batch_ids = _need(batch_ids, "batch_ids", torch.int32, 1)
+    cell_size = _need(cell_size, "cell_size", torch.float32, 1)
+    d, n, b, dev = _dims(pts), pts.shape[0], int(num_batches), pts.device
+    if cell_size.numel() != d or batch_ids.shape[0] != n:
+        raise RuntimeError("cell_size / batch_ids do not match pts")
+    mn = torch.empty((b, d), dtype=torch.float32, device=dev)
+    mx = torch.empty((b, d), dtype=torch.float32, device=dev)
+    cells = torch.empty((d,), dtype=torch.int32, device=dev)
+    keys = torch.empty((n,), dtype=torch.int64, device=dev)
+    sorted_keys, sorted_ids, sorted_pts = torch.empty_like(keys), torch.empty_like(keys), torch.empty_like(pts)
+    host_cells = (ctypes.c_int32 * d)()
+    with torch.cuda.device(dev):
+        stream = _stream()
+        ws = _workspace(_lib.pccnn_grid_front_end_workspace_bytes(n), dev)
+        _capi.check(_lib.pccnn_grid_front_end(d, n, _p(pts), _p(batch_ids), b, _p(cell_size), _p(mn), _p(mx), _p(cells),
+                                              host_cells, _p(keys), _p(sorted_keys), _p(sorted_ids), _p(sorted_pts),
+                                              ws.data_ptr(), ws.numel(), stream), "grid_front_end")
+        num_cells_host = [int(v) for v in host_cells]
+        grid_ds = torch.empty((b, num_cells_host[0], num_cells_host[1], 2), dtype=torch.int32, device=dev)
+        _capi.check(_lib.pccnn_build_grid_ds(d, n, _p(sorted_keys), _p(cells), grid_ds.numel() // 2, _p(grid_ds),
+                                             stream), "build_grid_ds")
+    return dict(aabb_min=mn, aabb_max=mx, num_cells=cells, num_cells_host=num_cells_host, keys=keys,
+                sorted_keys=sorted_keys, sorted_ids=sorted_ids, sorted_pts=sorted_pts, grid_ds=grid_ds)
+
+
 def build_grid_ds(keys, grid_size, out_shape):
     """[B, nc0, nc1, 2] int32 cell-range table; build_grid_ds() of build_grid/build_grid_ds.cu:72-114."""
     keys = _need(keys, "keys", torch.int64, 1)

@@ -13,10 +13,17 @@ class Pointcloud(object):
         self.pts_ = torch.as_tensor(p_pts, **kwargs)
         self.batch_ids_ = torch.as_tensor(p_batch_ids, **kwargs)
         self.batch_size_ = torch.max(self.batch_ids_) + 1
+        self._batch_size_host = None
         if self.pts_with_grads_:
             self.pts_.requires_grad = True
         self.pts_pdf_ = None
         self.pts_unnorm_pdf_ = None
+
+    def batch_size_host(self):
+        """Number of clouds as a Python int; read from the device once and remembered."""
+        if self._batch_size_host is None:
+            self._batch_size_host = int(self.batch_size_)
+        return self._batch_size_host
 
     def to_device(self, p_device):
         self.pts_ = self.pts_.to(p_device)
@@ -28,7 +35,7 @@ class Pointcloud(object):
 
     def get_num_points_per_batch(self):
         with torch.no_grad():
-            return torch.bincount(self.batch_ids_.to(torch.int64), minlength=int(self.batch_size_)).to(torch.int32)
+            return torch.bincount(self.batch_ids_.to(torch.int64), minlength=self.batch_size_host()).to(torch.int32)
 
     def compute_pdf(self, p_badnwidth):
         """KDE of every point with the given per-axis bandwidth; neighbors are searched within
@@ -51,7 +58,7 @@ class Pointcloud(object):
     def _pool(self, p_in_tensor, reduce):
         ids = self.batch_ids_.to(torch.int64)
         index = ids.reshape(-1, *([1] * (p_in_tensor.dim() - 1))).expand_as(p_in_tensor)
-        out = torch.zeros((int(self.batch_size_),) + tuple(p_in_tensor.shape[1:]), dtype=p_in_tensor.dtype,
+        out = torch.zeros((self.batch_size_host(),) + tuple(p_in_tensor.shape[1:]), dtype=p_in_tensor.dtype,
                           device=p_in_tensor.device)
         return out.scatter_reduce(0, index, p_in_tensor, reduce=reduce, include_self=False)
 

@@ -78,3 +78,40 @@ def test_reference_module_names_resolve_to_this_package():
         assert callable(getattr(pccnn_lib_ops, name))
     for m in ("pccnn_lib_ops", "pccnn_lib", "pccnn_lib.pc", "pccnn_lib.op_wrappers"):
         sys.modules.pop(m, None)
+
+
+@pytest.mark.parametrize("dims,cell", [(3, 0.1), (2, 0.25), (5, 0.6)])
+def test_fused_grid_front_end_equals_the_separate_operators_and_the_oracle(ref_clouds, dims, cell):
+    # One fused call (one host synchronisation) against the operator-by-operator sequence and the CPU oracle.
+    from pccnn_lib_b200 import ops
+    from oracle import oracle
+    _t = lambda a: torch.as_tensor(a, device="cuda:0")
+    pts, batch_ids = ref_case(ref_clouds, 6, 700, dims)
+    cell_size = np.full((dims,), cell, np.float32)
+    r = ops.grid_front_end(_t(pts), _t(batch_ids), 6, _t(cell_size))
+    o = oracle.build_grid(pts, batch_ids, 6, cell_size)
+    assert r["num_cells_host"] == list(o["num_cells"])
+    for mine, ref in (("aabb_min", "aabb_min"), ("aabb_max", "aabb_max"), ("num_cells", "num_cells"), ("keys", "keys"),
+                      ("sorted_keys", "sorted_keys"), ("sorted_ids", "sorted_ids"), ("sorted_pts", "sorted_pts"),
+                      ("grid_ds", "grid_ds")):
+        assert np.array_equal(r[mine].cpu().numpy(), np.asarray(o[ref])), mine
+
+
+def test_grid_on_an_unevaluated_box_takes_the_fused_path_with_equal_results(ref_clouds):
+    import pccnn_lib_b200 as lib
+    _t = lambda a: torch.as_tensor(a, device="cuda:0")
+    pts, batch_ids = ref_case(ref_clouds, 5, 600, 3)
+    cell_size = np.full((3,), 0.15, np.float32)
+    pc = lib.pc.Pointcloud(_t(pts), _t(batch_ids))
+    fused = lib.pc.Grid(pc, lib.pc.BoundingBox(pc), cell_size)           # box not touched before: fused call
+    assert fused._fused is not None
+    box = lib.pc.BoundingBox(pc)
+    box.min_                                                             # evaluated: operator-by-operator path
+    plain = lib.pc.Grid(pc, box, cell_size)
+    assert plain._fused is None
+    for g in (fused, plain):
+        g.compute_cell_ids()
+        g.build_ds()
+    for name in ("num_cells_", "cell_ids_", "sorted_ids_", "sorted_cell_ids_", "sorted_pts_", "grid_ds_"):
+        assert torch.equal(getattr(fused, name), getattr(plain, name)), name
+    assert torch.equal(fused.bounding_box_.min_, box.min_) and torch.equal(fused.bounding_box_.max_, box.max_)

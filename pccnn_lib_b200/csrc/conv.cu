@@ -488,6 +488,13 @@ backward_pairs_kernel(ARGS args, int K, const float* __restrict__ pts, const flo
                         for (int k = 0; k < KP; ++k) g[i][k] = (c < cin && k < K) ? __ldg(grow + (size_t)c * K + k) : 0.f;
                     }
                 }
+                // The dP row as fp32x2 pairs (k, k + 1): both contractions below run as packed FMAs, one
+                // issue slot for two products, each half rounded like the scalar FMA.
+                unsigned long long g2[CPL][KP / 2];
+#pragma unroll
+                for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                    for (int k = 0; k < KP; k += 2) g2[i][k / 2] = pack_f32x2(g[i][k], g[i][k + 1]);
                 for (int j0 = 0; j0 < cnt; j0 += 2) {
                     float f[2][CPL];
                     int nj[2];
@@ -504,22 +511,32 @@ backward_pairs_kernel(ARGS args, int K, const float* __restrict__ pts, const flo
                         if (j0 + u >= cnt) break;
                         const int j = j0 + u;
                         float df[CPL], pb[KP];
+                        unsigned long long df2[CPL], f2[CPL];  // df2: partial sums over even / odd k
 #pragma unroll
-                        for (int i = 0; i < CPL; ++i) df[i] = 0.f;
+                        for (int i = 0; i < CPL; ++i) {
+                            df2[i] = 0ull;
+                            f2[i] = pack_f32x2(f[u][i], f[u][i]);
+                        }
 #pragma unroll
                         for (int k = 0; k < KP; k += 4) {
                             const float4 b4 = *reinterpret_cast<const float4*>(&s_basis[warp][j][k]);
-                            const float bk[4] = {b4.x, b4.y, b4.z, b4.w};
+                            const unsigned long long bb[2] = {pack_f32x2(b4.x, b4.y), pack_f32x2(b4.z, b4.w)};
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                float acc = 0.f;
+                            for (int q = 0; q < 2; ++q) {
+                                unsigned long long acc2 = 0ull;
 #pragma unroll
                                 for (int i = 0; i < CPL; ++i) {
-                                    df[i] = fmaf(g[i][k + q], bk[q], df[i]);
-                                    acc = fmaf(g[i][k + q], f[u][i], acc);
+                                    df2[i] = fma_f32x2(g2[i][k / 2 + q], bb[q], df2[i]);
+                                    acc2 = fma_f32x2(g2[i][k / 2 + q], f2[i], acc2);
                                 }
-                                pb[k + q] = acc;
+                                unpack_f32x2(acc2, pb[k + 2 * q], pb[k + 2 * q + 1]);
                             }
+                        }
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i) {
+                            float even, odd;
+                            unpack_f32x2(df2[i], even, odd);
+                            df[i] = even + odd;
                         }
 #pragma unroll
                         for (int i = 0; i < CPL; ++i) {

@@ -191,6 +191,21 @@ int pccnn_poisson_disk_sampling(int D, int64_t n, const int64_t* sorted_keys, co
                                 int64_t* out_count_host, void* workspace, size_t workspace_bytes,
                                 void* stream);
 
+/* Poisson-disk sampling straight from the grid: the same selection as
+ * pccnn_poisson_disk_sampling on the full radius-neighborhood of the points (radius = cell
+ * size, max_neighbors = 0), without that neighbor list ever being built.  Replaces the pair
+ * find_neighbors + poisson_disk_sampling of pccnn_lib/pc/PointPooling.py:39-69 of the
+ * reference (kernel poisson_disk_sampling.cu:36-106: pass order, in-cell order and rejection
+ * rule unchanged; the radius test is the one of count_neighbors.cu:87).
+ * sorted_pts [n, D] and sorted_keys [n] in cell order, grid_ds / grid_size as for the search,
+ * radii [D] = the cell size.  out_selected: room for n int64 positions (ascending). */
+size_t pccnn_poisson_disk_sampling_grid_workspace_bytes(int64_t n);
+int pccnn_poisson_disk_sampling_grid(int D, int64_t n, const float* sorted_pts,
+                                     const int64_t* sorted_keys, const int32_t* grid_ds,
+                                     const int32_t* grid_size, const float* radii,
+                                     int64_t* out_selected, int64_t* out_count_host,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+
 /* Poisson-disk sampling for callers that cannot allocate device memory.  No counterpart in the
  * reference (every op there allocates its own temporaries through torch).
  *

@@ -38,6 +38,9 @@ SIGNATURES = {
     "pccnn_poisson_disk_sampling_workspace_bytes": (_size, [_c_i64]),
     "pccnn_poisson_disk_sampling": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
                                              ctypes.POINTER(_c_i64), _ptr, _size, _ptr]),
+    "pccnn_poisson_disk_sampling_grid_workspace_bytes": (_size, [_c_i64]),
+    "pccnn_poisson_disk_sampling_grid": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+                                                  ctypes.POINTER(_c_i64), _ptr, _size, _ptr]),
     "pccnn_poisson_disk_sampling_static_max_points": (_c_i64, []),
     "pccnn_poisson_disk_sampling_static": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
                                                     ctypes.POINTER(_c_i64), _ptr]),

@@ -18,7 +18,10 @@
 
 #include <mutex>
 
+#include <cub/device/device_scan.cuh>
+
 #include "common.cuh"
+#include "stencil.cuh"
 
 namespace pccnn {
 
@@ -269,6 +272,231 @@ static PdsLayout pds_layout(int64_t n) {
     return L;
 }
 
+// ---- Poisson-disk sampling straight from the grid (no neighbor list) -------------------------------
+// The list-based operator above needs the full self-neighborhood of the points, although a point is
+// only ever compared with SELECTED points, of which a cell holds a handful.  Here the selected
+// points of every cell are kept as a short list (stored in the cell's own slice of a point-sized
+// array), and a cell being decided gathers the selected points of its 3^D stencil once, into shared
+// memory, and tests its own points against them with the neighbor search's exact predicate
+// (sample = the point being decided).  Same passes, same order inside a cell, hence the same
+// selection as the list-based operator on the full radius-neighborhood.
+constexpr int kGridPdsWarps = 4;
+template <int D>
+struct GridPds {
+    // staged stencil candidates + room for the cell's own selections (at most 2^D points pairwise a
+    // cell size apart fit in one cell)
+    static constexpr int kOwn = 1 << D;
+    static constexpr int kCap = (D >= 5) ? 96 : 320;
+};
+
+template <int D>
+__device__ __forceinline__ bool within_radius(const float (&s)[D], const float (&q)[D], const float (&inv)[D]) {
+    float acc = 0.f;
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+        const float v = __fmul_rn(__fsub_rn(s[d], q[d]), inv[d]);
+        acc = (d == 0) ? __fmul_rn(v, v) : __fmaf_rn(v, v, acc);
+    }
+    return acc < 1.0f;
+}
+
+template <int D>
+__global__ void cell_parity_kernel(int n, const int64_t* __restrict__ keys, const int32_t* __restrict__ cell_starts,
+                                   const int32_t* __restrict__ grid_size, const int32_t* __restrict__ counters,
+                                   unsigned char* __restrict__ code) {
+    const GridDesc<D> g = load_grid<D>(grid_size);
+    const int num_cells = counters[0];
+    const int stride = gridDim.x * blockDim.x;
+    for (int cell = blockIdx.x * blockDim.x + threadIdx.x; cell < num_cells; cell += stride) {
+        int c[D];
+        key_to_cell<D>(keys[cell_starts[cell]], g, c);
+        unsigned v = 0;
+#pragma unroll
+        for (int d = 0; d < D; ++d) v |= (unsigned)(c[d] & 1) << d;
+        code[cell] = (unsigned char)v;
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kGridPdsWarps * 32)
+pds_grid_pass_kernel(int pass, int n, const float* __restrict__ pts, const int64_t* __restrict__ keys,
+                     const int32_t* __restrict__ cell_starts, const int32_t* __restrict__ counters,
+                     const unsigned char* __restrict__ code, const int32_t* __restrict__ cell_of_point,
+                     const int2* __restrict__ grid_ds, const int32_t* __restrict__ grid_size,
+                     const float* __restrict__ radii, int32_t* sel_list, int32_t* sel_cnt, int32_t* __restrict__ used) {
+    using S = Stencil<D>;
+    constexpr int kCap = GridPds<D>::kCap, kOwn = GridPds<D>::kOwn;
+    __shared__ int s_lo[kGridPdsWarps][S::kRanges];
+    __shared__ int s_pref[kGridPdsWarps][S::kRanges + 1];
+    __shared__ float s_cand[kGridPdsWarps][D][kCap];
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    const unsigned lt_mask = (1u << lane) - 1u;
+    int* lo = s_lo[warp];
+    int* pref = s_pref[warp];
+    float (*cand)[kCap] = s_cand[warp];
+    volatile int32_t* vsel_list = sel_list;
+    const GridDesc<D> g = load_grid<D>(grid_size);
+    float inv[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) inv[d] = __frcp_rn(__ldg(radii + d));
+    const int num_cells = counters[0];
+    const int warps_total = gridDim.x * kGridPdsWarps;
+
+    for (int base = (blockIdx.x * kGridPdsWarps + warp) * 32; base < num_cells; base += warps_total * 32) {
+        const bool want = base + lane < num_cells && __ldg(code + base + lane) == (unsigned)pass;
+        unsigned todo = __ballot_sync(kFullMask, want);
+        while (todo) {
+            const int ci = base + __ffs(todo) - 1;
+            todo &= todo - 1;
+            const int first = __ldg(cell_starts + ci);
+            const int last = (ci + 1 < num_cells) ? __ldg(cell_starts + ci + 1) : n;
+            resolve_ranges<D>(__ldg(keys + first), g, grid_ds, keys, n, lo, pref);
+
+            // Selected points of the stencil cells -> shared memory.  A range holds at most three cells
+            // (one in 2-D); every lane fetches the short lists of its own range, all loads in flight at once.
+            int staged = 0;
+            bool staged_all = true;
+            for (int o0 = 0; o0 < S::kRanges && staged_all; o0 += 32) {
+                const int o = o0 + lane;
+                int cf[3] = {0, 0, 0}, cn[3] = {0, 0, 0};
+                if (o < S::kRanges) {
+                    const int len = pref[o + 1] - pref[o];
+                    if (len > 0) {
+                        const int ca = __ldg(cell_of_point + lo[o]) - 1, cb = __ldg(cell_of_point + lo[o] + len - 1) - 1;
+#pragma unroll
+                        for (int j = 0; j < 3; ++j) {
+                            if (ca + j <= cb) {
+                                cn[j] = sel_cnt[ca + j];
+                                cf[j] = __ldg(cell_starts + ca + j);
+                            }
+                        }
+                    }
+                }
+                const int mine = cn[0] + cn[1] + cn[2];
+                int incl = mine;
+#pragma unroll
+                for (int sft = 1; sft < 32; sft <<= 1) {
+                    const int v = __shfl_up_sync(kFullMask, incl, sft);
+                    if (lane >= sft) incl += v;
+                }
+                const int batch = __shfl_sync(kFullMask, incl, 31);
+                if (staged + batch > kCap - kOwn) {
+                    staged_all = false;  // too many for the buffer: this cell reads the lists from memory instead
+                    break;
+                }
+                int pos = staged + incl - mine;
+#pragma unroll
+                for (int j = 0; j < 3; ++j) {
+                    for (int k = 0; k < cn[j]; ++k) {
+                        const int q = sel_list[cf[j] + k];
+#pragma unroll
+                        for (int d = 0; d < D; ++d) cand[d][pos] = __ldg(pts + (int64_t)q * D + d);
+                        ++pos;
+                    }
+                }
+                staged += batch;
+            }
+            __syncwarp();
+
+            int own = 0;  // points of this cell selected so far
+            for (int p0 = first; p0 < last; p0 += 32) {
+                const int p = p0 + lane, count = min(32, last - p0);
+                const bool has = p < last;
+                float x[D];
+#pragma unroll
+                for (int d = 0; d < D; ++d) x[d] = has ? __ldg(pts + (int64_t)p * D + d) : 0.f;
+                bool blocked = !has;
+                if (staged_all) {
+                    // staged stencil selections followed by this cell's own earlier selections
+                    for (int i = 0; i < staged; ++i) {
+                        float q[D];
+#pragma unroll
+                        for (int d = 0; d < D; ++d) q[d] = cand[d][i];
+                        blocked = blocked | within_radius<D>(x, q, inv);
+                    }
+                } else {
+                    for (int o = 0; o < S::kRanges; ++o) {
+                        const int len = pref[o + 1] - pref[o];
+                        if (len <= 0) continue;
+                        const int ca = __ldg(cell_of_point + lo[o]) - 1, cb = __ldg(cell_of_point + lo[o] + len - 1) - 1;
+                        for (int c = ca; c <= cb; ++c) {
+                            if (c == ci) continue;  // own selections are taken from the list below
+                            const int cnt = sel_cnt[c], cfirst = __ldg(cell_starts + c);
+                            for (int k = 0; k < cnt; ++k) {
+                                const int qi = sel_list[cfirst + k];
+                                float q[D];
+#pragma unroll
+                                for (int d = 0; d < D; ++d) q[d] = __ldg(pts + (int64_t)qi * D + d);
+                                blocked = blocked | within_radius<D>(x, q, inv);
+                            }
+                        }
+                    }
+                    for (int k = 0; k < own; ++k) {
+                        const int qi = vsel_list[first + k];
+                        float q[D];
+#pragma unroll
+                        for (int d = 0; d < D; ++d) q[d] = __ldg(pts + (int64_t)qi * D + d);
+                        blocked = blocked | within_radius<D>(x, q, inv);
+                    }
+                }
+                // earlier points of the same group that are this point's neighbors
+                unsigned in_group = 0u;
+                for (int qi = 0; qi < count; ++qi) {
+                    float q[D];
+#pragma unroll
+                    for (int d = 0; d < D; ++d) q[d] = __shfl_sync(kFullMask, x[d], qi);
+                    if (qi != lane && within_radius<D>(x, q, inv)) in_group |= 1u << qi;
+                }
+                const unsigned selected = decide_group(count, blocked, in_group);
+                const int rank = __popc(selected & lt_mask);
+                if (has && ((selected >> lane) & 1u)) {
+                    used[p] = 1;
+                    vsel_list[first + own + rank] = p;
+                    if (staged_all && staged + rank < kCap) {
+#pragma unroll
+                        for (int d = 0; d < D; ++d) cand[d][staged + rank] = x[d];
+                    }
+                }
+                const int fresh = __popc(selected);
+                own += fresh;
+                if (staged_all) staged = min(staged + fresh, kCap);
+                __syncwarp();
+            }
+            if (lane == 0) sel_cnt[ci] = own;
+            __syncwarp();
+        }
+    }
+}
+
+struct GridPdsLayout {
+    size_t flags_off, cells_off, used_off, cell_of_point_off, sel_list_off, sel_cnt_off, counters_off, cub_off, cub_bytes,
+        total;
+};
+
+static GridPdsLayout grid_pds_layout(int64_t n) {
+    GridPdsLayout L;
+    const int nn = (int)(n > 0 ? n : 1);
+    size_t a = 0, b = 0, c = 0;
+    cub::DeviceSelect::Flagged(nullptr, a, thrust::counting_iterator<int32_t>(0), (const int32_t*)nullptr,
+                               (int32_t*)nullptr, (int32_t*)nullptr, nn);
+    cub::DeviceSelect::Flagged(nullptr, b, thrust::counting_iterator<int64_t>(0), (const int32_t*)nullptr,
+                               (int64_t*)nullptr, (int32_t*)nullptr, nn);
+    cub::DeviceScan::InclusiveSum(nullptr, c, (const int32_t*)nullptr, (int32_t*)nullptr, nn);
+    L.cub_bytes = a > b ? a : b;
+    if (c > L.cub_bytes) L.cub_bytes = c;
+    const size_t slice = align_up((size_t)n * 4);
+    L.flags_off = 0;
+    L.cells_off = slice;
+    L.used_off = 2 * slice;
+    L.cell_of_point_off = 3 * slice;
+    L.sel_list_off = 4 * slice;
+    L.sel_cnt_off = 5 * slice;
+    L.counters_off = 6 * slice;
+    L.cub_off = L.counters_off + 256;
+    L.total = L.cub_off + align_up(L.cub_bytes) + 256;
+    return L;
+}
+
 }  // namespace pccnn
 
 using namespace pccnn;
@@ -323,6 +551,66 @@ int pccnn_poisson_disk_sampling(int D, int64_t n, const int64_t* sorted_keys, co
         pds_pass_kernel<<<crowded_blocks + sparse_blocks, kPdsThreads, 0, s>>>(
             pass, nn, crowded_blocks, cells, counters, code, crowded, crowded_capacity, (const int2*)neighbors, start_ids,
             used);
+        PCCNN_LAUNCH_CHECK();
+    }
+    cub_bytes = L.cub_bytes;
+    PCCNN_CUDA(cub::DeviceSelect::Flagged(ws + L.cub_off, cub_bytes, thrust::counting_iterator<int64_t>(0), used,
+                                          out_selected, counters + 1, nn, s));
+    int32_t count = 0;
+    PCCNN_CUDA(cudaMemcpyAsync(&count, counters + 1, 4, cudaMemcpyDeviceToHost, s));
+    PCCNN_CUDA(cudaStreamSynchronize(s));
+    *out_count_host = count;
+    return PCCNN_OK;
+}
+
+size_t pccnn_poisson_disk_sampling_grid_workspace_bytes(int64_t n) { return grid_pds_layout(n < 0 ? 0 : n).total; }
+
+int pccnn_poisson_disk_sampling_grid(int D, int64_t n, const float* sorted_pts, const int64_t* sorted_keys,
+                                     const int32_t* grid_ds, const int32_t* grid_size, const float* radii,
+                                     int64_t* out_selected, int64_t* out_count_host, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+    PCCNN_CHECK_ARG(D >= kMinDims && D <= kMaxDims, "poisson_disk_sampling_grid: point dimension %d outside [2, 6]", D);
+    PCCNN_CHECK_ARG(n >= 0 && n < 0x7fffffffLL, "poisson_disk_sampling_grid: %lld points outside [0, 2^31)", (long long)n);
+    PCCNN_CHECK_ARG(out_count_host, "poisson_disk_sampling_grid: null out_count_host");
+    *out_count_host = 0;
+    if (n == 0) return PCCNN_OK;
+    PCCNN_CHECK_ARG(sorted_pts && sorted_keys && grid_ds && grid_size && radii && out_selected,
+                    "poisson_disk_sampling_grid: null pointer");
+    const GridPdsLayout L = grid_pds_layout(n);
+    if (!workspace || workspace_bytes < L.total) {
+        set_error("poisson_disk_sampling_grid: workspace of %zu bytes, need %zu", workspace_bytes, L.total);
+        return PCCNN_ERR_WORKSPACE;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    char* ws = (char*)workspace;
+    int32_t* flags = (int32_t*)(ws + L.flags_off);
+    int32_t* cells = (int32_t*)(ws + L.cells_off);
+    int32_t* used = (int32_t*)(ws + L.used_off);
+    int32_t* cell_of_point = (int32_t*)(ws + L.cell_of_point_off);  // 1-based index of the point's cell
+    int32_t* sel_list = (int32_t*)(ws + L.sel_list_off);
+    int32_t* sel_cnt = (int32_t*)(ws + L.sel_cnt_off);
+    int32_t* counters = (int32_t*)(ws + L.counters_off);  // [0] = occupied cells, [1] = selected points
+    const int nn = (int)n;
+
+    cell_flags_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>(nn, sorted_keys, flags);
+    PCCNN_LAUNCH_CHECK();
+    size_t cub_bytes = L.cub_bytes;
+    PCCNN_CUDA(cub::DeviceSelect::Flagged(ws + L.cub_off, cub_bytes, thrust::counting_iterator<int32_t>(0), flags,
+                                          cells, counters, nn, s));
+    cub_bytes = L.cub_bytes;
+    PCCNN_CUDA(cub::DeviceScan::InclusiveSum(ws + L.cub_off, cub_bytes, flags, cell_of_point, nn, s));
+    // used and the per-cell counts start at zero; the flags are dead now and their space takes the routing bytes
+    PCCNN_CUDA(cudaMemsetAsync(used, 0, (size_t)n * 4, s));
+    PCCNN_CUDA(cudaMemsetAsync(sel_cnt, 0, (size_t)n * 4, s));
+    unsigned char* code = (unsigned char*)flags;
+    PCCNN_DISPATCH_DIM(D, (cell_parity_kernel<DIM><<<grid_for(n, 256, 8), 256, 0, s>>>(nn, sorted_keys, cells, grid_size,
+                                                                                  counters, code)));
+    PCCNN_LAUNCH_CHECK();
+    const unsigned grid = grid_for(n, kGridPdsWarps * 32, 16);
+    for (int pass = 0; pass < (1 << D); ++pass) {
+        PCCNN_DISPATCH_DIM(D, (pds_grid_pass_kernel<DIM><<<grid, kGridPdsWarps * 32, 0, s>>>(
+                                  pass, nn, sorted_pts, sorted_keys, cells, counters, code, cell_of_point,
+                                  (const int2*)grid_ds, grid_size, radii, sel_list, sel_cnt, used)));
         PCCNN_LAUNCH_CHECK();
     }
     cub_bytes = L.cub_bytes;

@@ -299,6 +299,29 @@ def poisson_disk_sampling(sorted_keys, neighbors, start_ids, grid_size):
     return selected[:count.value].reshape(-1, 1)
 
 
+def poisson_disk_sampling_grid(sorted_pts, sorted_keys, grid_ds, grid_size, radii):
+    """The selection of poisson_disk_sampling on the full self-neighborhood (radius = cell size)
+    without building that neighborhood: [k, 1] int64 ascending sorted positions.  Stands for the
+    pair find_neighbors + poisson_disk_sampling of pccnn_lib/pc/PointPooling.py:39-69."""
+    sorted_pts = _need(sorted_pts, "sorted_pts", torch.float32, 2)
+    sorted_keys = _need(sorted_keys, "sorted_keys", torch.int64, 1)
+    grid_ds = _need(grid_ds, "grid_ds", torch.int32, 4)
+    grid_size = _need(grid_size, "grid_size", torch.int32, 1)
+    radii = _need(radii, "radii", torch.float32, 1)
+    d, n = _dims(sorted_pts), sorted_pts.shape[0]
+    if sorted_keys.shape[0] != n or grid_size.numel() != d or radii.numel() != d:
+        raise RuntimeError("poisson_disk_sampling_grid: sizes of keys / grid_size / radii do not match the points")
+    selected = torch.empty((n,), dtype=torch.int64, device=sorted_pts.device)
+    count = ctypes.c_int64(0)
+    with torch.cuda.device(sorted_pts.device):
+        ws = _workspace(_lib.pccnn_poisson_disk_sampling_grid_workspace_bytes(n), sorted_pts.device)
+        _capi.check(_lib.pccnn_poisson_disk_sampling_grid(d, n, _p(sorted_pts), _p(sorted_keys), _p(grid_ds),
+                                                          _p(grid_size), _p(radii), _p(selected), ctypes.byref(count),
+                                                          ws.data_ptr(), ws.numel(), _stream()),
+                    "poisson_disk_sampling_grid")
+    return selected[:count.value].reshape(-1, 1)
+
+
 # ---- dense contraction -----------------------------------------------------------------------
 def gemm_f32(a, b, split=True):
     """a [M, K] @ b[N, K]^T -> [M, N] float32 on the tcgen05 tensor cores (bf16 hi/lo split when

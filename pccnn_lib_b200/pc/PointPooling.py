@@ -2,7 +2,7 @@ import torch
 
 from .BoundingBox import BoundingBox
 from .Grid import Grid
-from ..op_wrappers import FindNeighbors, PoissonDiskSamlping
+from .. import ops
 
 
 class PointPooling(object):
@@ -23,10 +23,10 @@ class PointPooling(object):
             grid.compute_cell_ids()
             grid.build_ds()
             if p_method == "poisson_disk":
-                neighbors, start_ids = FindNeighbors.apply(
-                    grid.sorted_pts_, grid.sorted_cell_ids_, grid.sorted_pts_, grid.sorted_cell_ids_,
-                    grid.grid_ds_, grid.num_cells_, grid.cell_size_, 0)
-                sampled = PoissonDiskSamlping.apply(grid.sorted_cell_ids_, neighbors, start_ids, grid.num_cells_)
+                # the reference searches the full self-neighborhood and hands it to the sampling operator;
+                # the grid-based operator makes the same selection without that list
+                sampled = ops.poisson_disk_sampling_grid(grid.sorted_pts_, grid.sorted_cell_ids_, grid.grid_ds_,
+                                                         grid.num_cells_, grid.cell_size_)
                 self.pooling_ids_ = torch.index_select(grid.sorted_ids_, 0, sampled.reshape(-1))
             elif p_method == "cell_average":
                 unique_ids, inverse_ids = torch.unique(grid.cell_ids_, return_inverse=True)

@@ -177,3 +177,37 @@ def test_neighbor_lists_do_not_depend_on_the_scratch_size(ref_clouds, scratch, m
     nbytes = lo if scratch == "minimum" else lo + 40000
     n, s = ops.find_neighbors(*args, workspace_bytes=nbytes)
     assert torch.equal(s, full_s) and torch.equal(n, full_n)
+
+
+@pytest.mark.parametrize("case", PDS_CASES[:12], ids=lambda c: "-".join(str(v) for v in c))
+def test_grid_based_poisson_disk_sampling_makes_the_same_selection(ref_clouds, case):
+    # No neighbor list: same passes and order, selected points kept per cell.  Must equal the list-based
+    # operator (and the oracle) on the full radius-neighborhood.
+    from pccnn_lib_b200 import ops
+    batch_size, num_pts, num_dims, radius = case[:4]
+    pts, batch_ids = ref_case(ref_clouds, batch_size, num_pts, num_dims)
+    cell = np.full((num_dims,), radius, np.float32)
+    g = gpu_grid(pts, batch_ids, batch_size, cell)
+    o = oracle.build_grid(pts, batch_ids, batch_size, cell)
+    on, os_ = oracle.find_neighbors(o["sorted_pts"], o["sorted_keys"], o["sorted_pts"], o["sorted_keys"], o["grid_ds"],
+                                    o["num_cells"], cell, 0)
+    expect = oracle.poisson_disk_sampling(o["sorted_keys"], on, os_, o["num_cells"])
+    got = ops.poisson_disk_sampling_grid(g["sorted_pts"], g["sorted_keys"], g["grid_ds"], g["num_cells"], g["cell"])
+    assert got.dtype == torch.int64 and got.dim() == 2 and got.shape[1] == 1
+    assert np.array_equal(got.cpu().numpy(), expect)
+
+
+@pytest.mark.parametrize("seed,batch,num_pts,dims,radius", [(41, 6, 30000, 3, 0.05), (42, 3, 20000, 2, 0.02),
+                                                            (43, 4, 40000, 3, 0.3), (44, 2, 3000, 5, 0.5)])
+def test_grid_based_and_list_based_sampling_agree_on_larger_ragged_batches(seed, batch, num_pts, dims, radius):
+    # thousands of cells per pass, sparse and crowded cells side by side; both operators on the GPU
+    from conftest import synthetic_case
+    from pccnn_lib_b200 import ops
+    pts, batch_ids = synthetic_case(seed, batch, num_pts, dims)
+    cell = np.full((dims,), radius, np.float32)
+    g = gpu_grid(pts, batch_ids, batch, cell)
+    nb, st = ops.find_neighbors(g["sorted_pts"], g["sorted_keys"], g["sorted_pts"], g["sorted_keys"], g["grid_ds"],
+                                g["num_cells"], g["cell"], 0)
+    by_list = ops.poisson_disk_sampling(g["sorted_keys"], nb, st, g["num_cells"])
+    by_grid = ops.poisson_disk_sampling_grid(g["sorted_pts"], g["sorted_keys"], g["grid_ds"], g["num_cells"], g["cell"])
+    assert by_list.shape[0] > 0 and torch.equal(by_list, by_grid)

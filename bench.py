@@ -314,6 +314,21 @@ def run_b200(args):
     else:
         peak, peak_src = 6650.0, "fallback"
 
+    # Secondary number: the class-level route to the same density, Pointcloud.compute_pdf, which searches
+    # within 4 bandwidths with at most 300 neighbors per point (pccnn_lib/pc/Pointcloud.py:81-109).
+    import pccnn_lib_b200 as lib
+    pc = lib.pc.Pointcloud(d_pts, d_ids)
+    bw3 = np.full((3,), BANDWIDTH, np.float32)
+    for _ in range(2):
+        pc.compute_pdf(bw3)
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for _ in range(3):
+        pc.compute_pdf(bw3)
+    c1.record()
+    torch.cuda.synchronize()
+    class_pdf_ms = c0.elapsed_time(c1) / 3
+
     n_pts = CLOUDS_PER_RANK * POINTS_PER_CLOUD
     t_rank = float(local_pairs)  # pairs of one step on this rank
     # Algorithmic bytes per launch: 8 B per pair written (store) / read (KDE) plus the per-point streams.
@@ -346,7 +361,7 @@ def run_b200(args):
                                "int32 CSR, fp32 KDE bandwidth 0.01" % CLOUDS_PER_RANK,
                    "clouds_per_gpu": CLOUDS_PER_RANK, "points_per_cloud": POINTS_PER_CLOUD,
                    "pairs_per_step_per_gpu": t_rank, "neighbors_per_point": t_rank / n_pts,
-                   "sub_batches_for_int32_offsets": n_sub, "l2": "inputs larger than L2 (neighbor list)",
+                   "pointcloud_compute_pdf_ms": round(class_pdf_ms, 3), "sub_batches_for_int32_offsets": n_sub, "l2": "inputs larger than L2 (neighbor list)",
                    "library_kernels": "cub radix sort and scan",
                    "sharding": "every rank processes its own batch of 16 clouds (same seeds on every rank); no collective on the data path"},
         "clocks": clocks,

@@ -317,13 +317,68 @@ __global__ void cell_parity_kernel(int n, const int64_t* __restrict__ keys, cons
     }
 }
 
+// D <= 3: the stencil of a cell as cell indices, resolved once for all passes by one thread per
+// (cell, range) - the binary searches of thousands of cells overlap here, whereas a pass kernel
+// that resolves them itself pays their latency cell after cell.  Entry = first cell index * 4 +
+// number of cells (0 ... 3) of the range.
+template <int D>
+__global__ void stencil_cells_kernel(int n, const int64_t* __restrict__ keys, const int32_t* __restrict__ cell_starts,
+                                     const int32_t* __restrict__ counters, const int32_t* __restrict__ cell_of_point,
+                                     const int2* __restrict__ grid_ds, const int32_t* __restrict__ grid_size,
+                                     int32_t* __restrict__ table) {
+    using S = Stencil<D>;
+    const GridDesc<D> g = load_grid<D>(grid_size);
+    const int num_cells = counters[0];
+    const long long total = (long long)num_cells * S::kRanges;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int cell = (int)(i / S::kRanges), o = (int)(i - (long long)cell * S::kRanges);
+        int c[D], cc[D];
+        const int b = key_to_cell<D>(__ldg(keys + __ldg(cell_starts + cell)), g, c);
+#pragma unroll
+        for (int d = 0; d < D; ++d) cc[d] = c[d];
+        int rem = o;
+        bool inside = true;
+#pragma unroll
+        for (int d = S::kOffsetDims - 1; d >= 0; --d) {
+            const int q = rem / 3;
+            cc[d] += rem - q * 3 - 1;
+            rem = q;
+            inside = inside && cc[d] >= 0 && cc[d] < g.nc[d];
+        }
+        int2 r = make_int2(0, 0);
+        if (inside) {
+            const long long ds = ((long long)b * g.nc[0] + cc[0]) * g.nc[1] + cc[1];
+            int2 tube = __ldg(grid_ds + ds);
+            tube.x = max(tube.x, 0);
+            tube.y = min(tube.y, n);
+            if (D == 2) {
+                r = tube;
+            } else if (tube.y > tube.x) {
+                const long long k = cell_key<D>(cc, g, b);
+                const long long klo = k - (c[D - 1] > 0 ? 1 : 0);
+                const long long khi = k + (c[D - 1] < g.nc[D - 1] - 1 ? 1 : 0);
+                r.x = lower_bound_key(keys, tube.x, tube.y, klo);
+                r.y = upper_bound_key(keys, r.x, tube.y, khi);
+            }
+        }
+        int entry = 0;
+        if (r.y > r.x) {
+            const int ca = __ldg(cell_of_point + r.x) - 1, cb = __ldg(cell_of_point + r.y - 1) - 1;
+            entry = ca * 4 + min(cb - ca + 1, 3);
+        }
+        table[i] = entry;
+    }
+}
+
 template <int D>
 __global__ void __launch_bounds__(kGridPdsWarps * 32)
 pds_grid_pass_kernel(int pass, int n, const float* __restrict__ pts, const int64_t* __restrict__ keys,
                      const int32_t* __restrict__ cell_starts, const int32_t* __restrict__ counters,
                      const unsigned char* __restrict__ code, const int32_t* __restrict__ cell_of_point,
                      const int2* __restrict__ grid_ds, const int32_t* __restrict__ grid_size,
-                     const float* __restrict__ radii, int32_t* sel_list, int32_t* sel_cnt, int32_t* __restrict__ used) {
+                     const float* __restrict__ radii, const int32_t* __restrict__ table, int32_t* sel_list,
+                     int32_t* sel_cnt, int32_t* __restrict__ used) {
     using S = Stencil<D>;
     constexpr int kCap = GridPds<D>::kCap, kOwn = GridPds<D>::kOwn;
     __shared__ int s_lo[kGridPdsWarps][S::kRanges];
@@ -350,7 +405,7 @@ pds_grid_pass_kernel(int pass, int n, const float* __restrict__ pts, const int64
             todo &= todo - 1;
             const int first = __ldg(cell_starts + ci);
             const int last = (ci + 1 < num_cells) ? __ldg(cell_starts + ci + 1) : n;
-            resolve_ranges<D>(__ldg(keys + first), g, grid_ds, keys, n, lo, pref);
+            if (!table) resolve_ranges<D>(__ldg(keys + first), g, grid_ds, keys, n, lo, pref);
 
             // Selected points of the stencil cells -> shared memory.  A range holds at most three cells
             // (one in 2-D); every lane fetches the short lists of its own range, all loads in flight at once.
@@ -360,15 +415,23 @@ pds_grid_pass_kernel(int pass, int n, const float* __restrict__ pts, const int64
                 const int o = o0 + lane;
                 int cf[3] = {0, 0, 0}, cn[3] = {0, 0, 0};
                 if (o < S::kRanges) {
-                    const int len = pref[o + 1] - pref[o];
-                    if (len > 0) {
-                        const int ca = __ldg(cell_of_point + lo[o]) - 1, cb = __ldg(cell_of_point + lo[o] + len - 1) - 1;
+                    int ca = 0, cells_here = 0;
+                    if (table) {
+                        const int entry = __ldg(table + (int64_t)ci * S::kRanges + o);
+                        ca = entry >> 2;
+                        cells_here = entry & 3;
+                    } else {
+                        const int len = pref[o + 1] - pref[o];
+                        if (len > 0) {
+                            ca = __ldg(cell_of_point + lo[o]) - 1;
+                            cells_here = __ldg(cell_of_point + lo[o] + len - 1) - ca;
+                        }
+                    }
 #pragma unroll
-                        for (int j = 0; j < 3; ++j) {
-                            if (ca + j <= cb) {
-                                cn[j] = sel_cnt[ca + j];
-                                cf[j] = __ldg(cell_starts + ca + j);
-                            }
+                    for (int j = 0; j < 3; ++j) {
+                        if (j < cells_here) {
+                            cn[j] = sel_cnt[ca + j];
+                            cf[j] = __ldg(cell_starts + ca + j);
                         }
                     }
                 }
@@ -416,9 +479,17 @@ pds_grid_pass_kernel(int pass, int n, const float* __restrict__ pts, const int64
                     }
                 } else {
                     for (int o = 0; o < S::kRanges; ++o) {
-                        const int len = pref[o + 1] - pref[o];
-                        if (len <= 0) continue;
-                        const int ca = __ldg(cell_of_point + lo[o]) - 1, cb = __ldg(cell_of_point + lo[o] + len - 1) - 1;
+                        int ca, cb;
+                        if (table) {
+                            const int entry = __ldg(table + (int64_t)ci * S::kRanges + o);
+                            ca = entry >> 2;
+                            cb = ca + (entry & 3) - 1;
+                        } else {
+                            const int len = pref[o + 1] - pref[o];
+                            if (len <= 0) continue;
+                            ca = __ldg(cell_of_point + lo[o]) - 1;
+                            cb = __ldg(cell_of_point + lo[o] + len - 1) - 1;
+                        }
                         for (int c = ca; c <= cb; ++c) {
                             if (c == ci) continue;  // own selections are taken from the list below
                             const int cnt = sel_cnt[c], cfirst = __ldg(cell_starts + c);
@@ -470,7 +541,7 @@ pds_grid_pass_kernel(int pass, int n, const float* __restrict__ pts, const int64
 
 struct GridPdsLayout {
     size_t flags_off, cells_off, used_off, cell_of_point_off, sel_list_off, sel_cnt_off, counters_off, cub_off, cub_bytes,
-        total;
+        table_off, total;
 };
 
 static GridPdsLayout grid_pds_layout(int64_t n) {
@@ -493,7 +564,9 @@ static GridPdsLayout grid_pds_layout(int64_t n) {
     L.sel_cnt_off = 5 * slice;
     L.counters_off = 6 * slice;
     L.cub_off = L.counters_off + 256;
-    L.total = L.cub_off + align_up(L.cub_bytes) + 256;
+    // stencil table of the D <= 3 path: 9 entries per cell (higher dimensions resolve the ranges in the pass kernel)
+    L.table_off = L.cub_off + align_up(L.cub_bytes) + 256;
+    L.total = L.table_off + align_up((size_t)n * 9 * 4);
     return L;
 }
 
@@ -606,11 +679,23 @@ int pccnn_poisson_disk_sampling_grid(int D, int64_t n, const float* sorted_pts, 
     PCCNN_DISPATCH_DIM(D, (cell_parity_kernel<DIM><<<grid_for(n, 256, 8), 256, 0, s>>>(nn, sorted_keys, cells, grid_size,
                                                                                   counters, code)));
     PCCNN_LAUNCH_CHECK();
+    int32_t* table = nullptr;
+    if (D <= 3) {
+        table = (int32_t*)(ws + L.table_off);
+        if (D == 2) {
+            stencil_cells_kernel<2><<<grid_for(n * 9, 256, 8), 256, 0, s>>>(nn, sorted_keys, cells, counters, cell_of_point,
+                                                                           (const int2*)grid_ds, grid_size, table);
+        } else {
+            stencil_cells_kernel<3><<<grid_for(n * 9, 256, 8), 256, 0, s>>>(nn, sorted_keys, cells, counters, cell_of_point,
+                                                                           (const int2*)grid_ds, grid_size, table);
+        }
+        PCCNN_LAUNCH_CHECK();
+    }
     const unsigned grid = grid_for(n, kGridPdsWarps * 32, 16);
     for (int pass = 0; pass < (1 << D); ++pass) {
         PCCNN_DISPATCH_DIM(D, (pds_grid_pass_kernel<DIM><<<grid, kGridPdsWarps * 32, 0, s>>>(
                                   pass, nn, sorted_pts, sorted_keys, cells, counters, code, cell_of_point,
-                                  (const int2*)grid_ds, grid_size, radii, sel_list, sel_cnt, used)));
+                                  (const int2*)grid_ds, grid_size, radii, table, sel_list, sel_cnt, used)));
         PCCNN_LAUNCH_CHECK();
     }
     cub_bytes = L.cub_bytes;

@@ -83,7 +83,7 @@ neighbors_kernel(int num_pts, const float* __restrict__ pts, const int64_t* __re
     __shared__ int s_lo[kWarpsPerBlock][S::kRanges];
     __shared__ int s_pref[kWarpsPerBlock][S::kRanges + 1];
     const int warp = threadIdx.x >> 5, lane = lane_id();
-    const unsigned lt_mask = (1u << lane) - 1u;
+    const unsigned lane_bit = 1u << lane, lt_mask = lane_bit - 1u;
     float4* slots = s_slots[warp];
     int* slot_ids = reinterpret_cast<int*>(s_slots[warp]);  // masked store pass: positions only
     int* lo = s_lo[warp];
@@ -165,7 +165,8 @@ neighbors_kernel(int num_pts, const float* __restrict__ pts, const int64_t* __re
                     }
                 }
                 if (replay) {
-                    slot_ids[sl] = j;
+                    // final ids, mapped once per staged candidate instead of once per hit
+                    slot_ids[sl] = (pt_index_map && sl < n_slots) ? (int)__ldg(pt_index_map + j) : j;
                 } else {
 #pragma unroll
                     for (int q = 0; q < S::kPlanes; ++q)
@@ -205,10 +206,14 @@ neighbors_kernel(int num_pts, const float* __restrict__ pts, const int64_t* __re
 #pragma unroll
                         for (int ci = 0; ci < kChunks; ++ci) {
                             const unsigned bal = __shfl_sync(kFullMask, cur, gi * kChunks + ci);
-                            if ((bal >> lane) & 1u) {
-                                const int j = slot_ids[ci * 32 + lane];
-                                const int id = pt_index_map ? (int)__ldg(pt_index_map + j) : j;
-                                emit_row<MODE>(out, base, found + __popc(bal & lt_mask), id, m, total, max_neighbors);
+                            // The id is read and the slot computed by every lane, so that the hit itself is
+                            // a single predicated store instead of a divergent block.
+                            const int id = slot_ids[ci * 32 + lane];
+                            const int rank = found + __popc(bal & lt_mask);
+                            if (MODE == kStore) {
+                                if (bal & lane_bit) out[base + rank] = make_int2(id, m);
+                            } else if (bal & lane_bit) {
+                                emit_row<MODE>(out, base, rank, id, m, total, max_neighbors);
                             }
                             found += __popc(bal);
                         }

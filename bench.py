@@ -34,7 +34,7 @@ BANDWIDTH = 0.01
 MAX_PAIRS_PER_CALL = (1 << 31) - 1  # int32 CSR offsets of the reference format
 # DRAM bytes per neighbor pair of the three heavy kernels, from one ncu capture of a 6-cloud case
 # (profiles/neighbors_kernel_pdf_kernel_6clouds_ncu.md); traffic grows in proportion to the pairs.
-NCU_DRAM_BYTES_PER_PAIR = {"neighbors_store": 10.30, "neighbors_count": 0.33, "kde": 8.10}
+NCU_DRAM_BYTES_PER_PAIR = {"neighbors_store": 10.04, "neighbors_count": 0.11, "kde": 8.10}
 
 
 # ---- synthetic clouds --------------------------------------------------------------------------

@@ -17,7 +17,8 @@ import sysconfig
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PCCNN_REFERENCE", "/root/reference")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+        "PCCNN_REFERENCE", os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference")))
     src_dir = os.path.join(ref, "pccnn_lib_ops")
     if not os.path.isdir(src_dir):
         print("reference sources not found at", src_dir)

@@ -15,7 +15,8 @@ import numpy as np
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PCCNN_REFERENCE", "/root/reference")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+        "PCCNN_REFERENCE", os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference")))
     src = os.path.join(ref, "unit_test", "point_clouds")
     out = np.zeros((32, 1000, 3), dtype=np.float32)
     for i in range(32):

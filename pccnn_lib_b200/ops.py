@@ -134,6 +134,8 @@ def grid_front_end(pts, batch_ids, num_batches, cell_size):
     d, n, b, dev = _dims(pts), pts.shape[0], int(num_batches), pts.device
     if cell_size.numel() != d or batch_ids.shape[0] != n:
         raise RuntimeError("cell_size / batch_ids do not match pts")
+    if n == 0 or b <= 0:
+        raise RuntimeError("grid_front_end: needs at least one point and one cloud (an empty set has no bounding box)")
     mn = torch.empty((b, d), dtype=torch.float32, device=dev)
     mx = torch.empty((b, d), dtype=torch.float32, device=dev)
     cells = torch.empty((d,), dtype=torch.int32, device=dev)

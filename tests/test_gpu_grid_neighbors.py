@@ -102,6 +102,16 @@ def test_empty_inputs():
     assert n.shape[0] == 0 and s.cpu().tolist() == [0] * 5
     assert ops.compute_keys(empty_s, torch.zeros((0,), dtype=torch.int32, device="cuda"), g["aabb_min"],
                             g["num_cells"], g["cell"]).shape[0] == 0
+    # the list-free sampling of an empty set selects nothing; the fused front end refuses it (no bounding box)
+    sel = ops.poisson_disk_sampling_grid(empty_s, empty_k, g["grid_ds"], g["num_cells"], g["cell"])
+    assert tuple(sel.shape) == (0, 1)
+    with pytest.raises(RuntimeError):
+        ops.grid_front_end(empty_s, torch.zeros((0,), dtype=torch.int32, device="cuda"), 2, g["cell"])
+    # a cloud of the batch without any point: same tables as the operator-by-operator path
+    one_cloud = batch_ids == 0
+    r = ops.grid_front_end(dev(pts[one_cloud]), dev(np.zeros(int(one_cloud.sum()), np.int32)), 1, g["cell"])
+    o1 = oracle.build_grid(pts[one_cloud], np.zeros(int(one_cloud.sum()), np.int32), 1, cell)
+    assert np.array_equal(r["sorted_ids"].cpu().numpy(), o1["sorted_ids"]) and np.array_equal(r["grid_ds"].cpu().numpy(), o1["grid_ds"])
 
 
 PDF_CASES = [(4, 1000, 2, 0.02), (4, 1000, 3, 0.01), (4, 1000, 6, 0.01), (4, 1000, 2, 0.025), (4, 1000, 3, 0.025),

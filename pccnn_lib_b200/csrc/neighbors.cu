@@ -60,10 +60,18 @@ __device__ __forceinline__ void emit_row(int2* __restrict__ out, int base, int r
         out[base + rank] = make_int2(id, m);
     } else {
         // Even-stride thinning: hit `rank` of `total` is kept iff it starts a new one of the
-        // max_neighbors equal slices of the list.
-        const long long a = (long long)rank * max_neighbors / total;
-        const long long bnext = (long long)(rank + 1) * max_neighbors / total;
-        if (bnext > a) out[base + (int)a] = make_int2(id, m);
+        // max_neighbors equal slices of the list, i.e. iff floor((rank + 1) * max / total) exceeds
+        // a = floor(rank * max / total), which is the case iff (rank * max) mod total + max >= total.
+        // One 32-bit division when the product fits, the 64-bit form otherwise.
+        if ((unsigned long long)rank * (unsigned)max_neighbors < 0x80000000ull) {
+            const unsigned prod = (unsigned)rank * (unsigned)max_neighbors;
+            const unsigned a = prod / (unsigned)total, rem = prod - a * (unsigned)total;
+            if (rem + (unsigned)max_neighbors >= (unsigned)total) out[base + (int)a] = make_int2(id, m);
+        } else {
+            const long long a = (long long)rank * max_neighbors / total;
+            const long long bnext = (long long)(rank + 1) * max_neighbors / total;
+            if (bnext > a) out[base + (int)a] = make_int2(id, m);
+        }
     }
 }
 

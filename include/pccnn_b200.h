@@ -162,9 +162,13 @@ int pccnn_find_neighbors_store(int D, int64_t num_pts, const float* pts, const i
 /* pdf_i = sum_{j in seg(i)} prod_d(1/bw_d) * (2*3.1415)^(-manifold_dims/2)
  *                           * expf(-0.5 * |(p_j - p_i) * (1/bw)|^2).
  * Replaces compute_pdf()  pccnn_lib_ops/compute_pdf/compute_pdf.cu:153-203 (kernel :24-77).
- * float32, summation order differs from the reference: tolerance-matched. */
+ * float32, summation order differs from the reference: tolerance-matched.
+ * The workspace is optional (null / 0 allowed): with pccnn_compute_pdf_workspace_bytes(D, n) bytes,
+ * 3-D points are gathered from a 16-byte padded copy (one load per neighbor instead of three). */
+size_t pccnn_compute_pdf_workspace_bytes(int D, int64_t n);
 int pccnn_compute_pdf(int D, int manifold_dims, const float* bandwidth, int64_t n, const float* pts,
-                      const int32_t* neighbors, const int32_t* start_ids, float* out_pdf, void* stream);
+                      const int32_t* neighbors, const int32_t* start_ids, float* out_pdf,
+                      void* workspace, size_t workspace_bytes, void* stream);
 
 /* Gradient of sum_i in_grads[i] * pdf_i with respect to the points.
  * Replaces compute_pdf_grads()  compute_pdf.cu:206-257 (kernel :80-149).

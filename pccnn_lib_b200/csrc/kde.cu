@@ -73,6 +73,53 @@ pdf_kernel(int manifold_dims, const float* __restrict__ bandwidth, int n, const 
     }
 }
 
+// 3-D points padded to 16 bytes: a neighbor then costs one 128-bit gather instead of three 32-bit ones
+// (the gathers, not the 8 B/pair list stream, are what the density kernel waits on).
+__global__ void pad_points_kernel(int n, const float* __restrict__ pts, float4* __restrict__ out) {
+    const int stride = gridDim.x * blockDim.x;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = make_float4(pts[3 * (int64_t)i], pts[3 * (int64_t)i + 1], pts[3 * (int64_t)i + 2], 0.f);
+}
+
+// pdf_kernel<3> on the padded copy: same terms, same order of the sum.
+__global__ void __launch_bounds__(kPdfWarps * 32)
+pdf_kernel_padded(int manifold_dims, const float* __restrict__ bandwidth, int n, const float4* __restrict__ pts4,
+                  const int2* __restrict__ neighbors, const int32_t* __restrict__ start_ids,
+                  float* __restrict__ out_pdf) {
+    float ibw[3];
+#pragma unroll
+    for (int d = 0; d < 3; ++d) ibw[d] = __frcp_rn(__ldg(bandwidth + d));
+    const float scale = pdf_scale<3>(ibw, manifold_dims);
+    const int lane = lane_id();
+    const int warps_total = gridDim.x * kPdfWarps;
+    for (int i = blockIdx.x * kPdfWarps + (threadIdx.x >> 5); i < n; i += warps_total) {
+        const float4 p = __ldg(pts4 + i);
+        const int lo = (i > 0) ? __ldg(start_ids + i - 1) : 0;
+        const int hi = __ldg(start_ids + i);
+        float acc = 0.f;
+        auto term = [&](int j) {
+            const float4 q = __ldg(pts4 + j);
+            const float vx = (q.x - p.x) * ibw[0], vy = (q.y - p.y) * ibw[1], vz = (q.z - p.z) * ibw[2];
+            return expf(fmaf(vz, vz, fmaf(vy, vy, fmaf(vx, vx, 0.f))) * -0.5f);
+        };
+        int t = lo + lane;
+        for (; t + 96 < hi; t += 128) {
+            const int j0 = __ldcs(&neighbors[t]).x;
+            const int j1 = __ldcs(&neighbors[t + 32]).x;
+            const int j2 = __ldcs(&neighbors[t + 64]).x;
+            const int j3 = __ldcs(&neighbors[t + 96]).x;
+            const float e0 = term(j0), e1 = term(j1), e2 = term(j2), e3 = term(j3);
+            acc += e0;
+            acc += e1;
+            acc += e2;
+            acc += e3;
+        }
+        for (; t < hi; t += 32) acc += term(__ldcs(&neighbors[t]).x);
+        acc = warp_sum(acc);
+        if (lane == 0) out_pdf[i] = acc * scale;
+    }
+}
+
 template <int D>
 __global__ void __launch_bounds__(kPdfWarps * 32)
 pdf_grads_kernel(int manifold_dims, const float* __restrict__ bandwidth, int n, const float* __restrict__ pts,
@@ -124,13 +171,26 @@ using namespace pccnn;
 
 extern "C" {
 
+size_t pccnn_compute_pdf_workspace_bytes(int D, int64_t n) { return (D == 3 && n > 0) ? (size_t)n * 16 : 0; }
+
 int pccnn_compute_pdf(int D, int manifold_dims, const float* bandwidth, int64_t n, const float* pts,
-                      const int32_t* neighbors, const int32_t* start_ids, float* out_pdf, void* stream) {
+                      const int32_t* neighbors, const int32_t* start_ids, float* out_pdf, void* workspace,
+                      size_t workspace_bytes, void* stream) {
     PCCNN_CHECK_ARG(n >= 0 && n < 0x7fffffffLL, "compute_pdf: %lld points outside [0, 2^31)", (long long)n);
     if (n == 0) return PCCNN_OK;
     PCCNN_CHECK_ARG(bandwidth && pts && start_ids && out_pdf, "compute_pdf: null pointer");
     cudaStream_t s = (cudaStream_t)stream;
     const unsigned grid = grid_for(n * 32, kPdfWarps * 32, 8);
+    if (D == 3 && workspace && workspace_bytes >= (size_t)n * 16 && reinterpret_cast<uintptr_t>(workspace) % 16 == 0) {
+        // optional scratch given: gather from a 16-byte padded copy of the points
+        float4* padded = (float4*)workspace;
+        pad_points_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>((int)n, pts, padded);
+        PCCNN_LAUNCH_CHECK();
+        pdf_kernel_padded<<<grid, kPdfWarps * 32, 0, s>>>(manifold_dims, bandwidth, (int)n, padded, (const int2*)neighbors,
+                                                         start_ids, out_pdf);
+        PCCNN_LAUNCH_CHECK();
+        return PCCNN_OK;
+    }
     PCCNN_DISPATCH_DIM(D, (pdf_kernel<DIM><<<grid, kPdfWarps * 32, 0, s>>>(
                               manifold_dims, bandwidth, (int)n, pts, (const int2*)neighbors, start_ids, out_pdf)));
     PCCNN_LAUNCH_CHECK();

@@ -263,8 +263,10 @@ def compute_pdf(manifold_dims, bandwidth, pts, neighbors, start_ids):
     bandwidth, pts, neighbors, start_ids, d = _pdf_args(bandwidth, pts, neighbors, start_ids)
     out = torch.empty((pts.shape[0],), dtype=torch.float32, device=pts.device)
     with torch.cuda.device(pts.device):
+        ws = _workspace(_lib.pccnn_compute_pdf_workspace_bytes(d, pts.shape[0]), pts.device)
         _capi.check(_lib.pccnn_compute_pdf(d, int(manifold_dims), _p(bandwidth), pts.shape[0], _p(pts),
-                                           _p(neighbors), _p(start_ids), _p(out), _stream()), "compute_pdf")
+                                           _p(neighbors), _p(start_ids), _p(out), ws.data_ptr(), ws.numel(), _stream()),
+                    "compute_pdf")
     return out
 
 

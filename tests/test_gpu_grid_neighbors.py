@@ -221,3 +221,20 @@ def test_grid_based_and_list_based_sampling_agree_on_larger_ragged_batches(seed,
     by_list = ops.poisson_disk_sampling(g["sorted_keys"], nb, st, g["num_cells"])
     by_grid = ops.poisson_disk_sampling_grid(g["sorted_pts"], g["sorted_keys"], g["grid_ds"], g["num_cells"], g["cell"])
     assert by_list.shape[0] > 0 and torch.equal(by_list, by_grid)
+
+
+def test_pdf_with_and_without_the_optional_scratch_is_bitwise_the_same(ref_clouds):
+    # 3-D: with scratch the neighbors are gathered from a padded copy of the points; same terms, same order
+    import ctypes
+    from pccnn_lib_b200 import _capi, ops
+    pts, batch_ids = ref_case(ref_clouds, 4, 1000, 3)
+    gn, gs, on, os_, g, o = both_neighborhoods(pts, batch_ids, 4, 0.1, 0)
+    spts = dev(o["sorted_pts"])
+    bw = dev(np.full((3,), 0.025, np.float32))
+    with_scratch = ops.compute_pdf(3, bw, spts, gn, gs)
+    plain = torch.empty_like(with_scratch)
+    rc = _capi.lib.pccnn_compute_pdf(3, 3, bw.data_ptr(), spts.shape[0], spts.data_ptr(), gn.data_ptr(), gs.data_ptr(),
+                                     plain.data_ptr(), None, 0, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(with_scratch, plain)

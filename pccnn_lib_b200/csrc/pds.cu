@@ -283,8 +283,8 @@ static PdsLayout pds_layout(int64_t n) {
 constexpr int kGridPdsWarps = 4;
 template <int D>
 struct GridPds {
-    // staged stencil candidates + room for the cell's own selections (at most 2^D points pairwise a
-    // cell size apart fit in one cell)
+    // staged stencil candidates + room for the cell's own selections (2^D points pairwise a cell size
+    // apart fit in one cell up to D = 3; the kernel falls back to the lists in memory beyond the buffer)
     static constexpr int kOwn = 1 << D;
     static constexpr int kCap = (D >= 5) ? 96 : 320;
 };
@@ -530,7 +530,13 @@ pds_grid_pass_kernel(int pass, int n, const float* __restrict__ pts, const int64
                 }
                 const int fresh = __popc(selected);
                 own += fresh;
-                if (staged_all) staged = min(staged + fresh, kCap);
+                if (staged_all) {
+                    // more selections than the buffer holds (possible in five or more dimensions, where a
+                    // cell can host more than 2^D points a cell size apart): the remaining groups of this
+                    // cell read the lists from memory, which are complete
+                    if (staged + fresh > kCap) staged_all = false;
+                    else staged += fresh;
+                }
                 __syncwarp();
             }
             if (lane == 0) sel_cnt[ci] = own;

@@ -19,6 +19,8 @@
 //                      releases the stage and finally signals the epilogue
 //   all four warps   : epilogue      -- tcgen05.ld 32 lanes x 32 columns per warp and step, plain
 //                      global stores of whole 128-byte row segments
+// With more output tiles than SMs the persistent form runs instead (gemm_bf16_persistent_kernel below:
+// one CTA per SM, accumulator double-buffered in tensor memory, four dedicated epilogue warps).
 // Every wait is bounded: on expiry the kernel records a status word,
 // leaves its loops, releases tensor memory and returns.
 #include <cuda.h>
@@ -100,6 +102,48 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
     d |= (uint64_t)1 << 46;                            // version
     d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
     return d;
+}
+
+// One accumulator segment of 32 columns (starting at column col0) of output row `row`: fp32 or bf16 stores,
+// 128-bit wide where the destination allows.
+__device__ __forceinline__ void store_acc_segment(const uint32_t (&r)[32], int row, int M, int N, int col0, float* C,
+                                                  int ldc, int c_is_bf16) {
+    if (row < M && c_is_bf16) {
+        // bf16 output (inference configuration): C is a __nv_bfloat16 matrix, ldc in elements
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (size_t)row * ldc + col0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            const int col = col0 + j;
+            if (col + 7 < N && ((((uintptr_t)(dst + j)) & 15) == 0)) {
+                uint32_t wv[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * q]),
+                                                                    __uint_as_float(r[j + 2 * q + 1]));
+                    wv[q] = *reinterpret_cast<const uint32_t*>(&h2);
+                }
+                *reinterpret_cast<uint4*>(dst + j) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    if (col + e < N) dst[j + e] = __float2bfloat16_rn(__uint_as_float(r[j + e]));
+            }
+        }
+    } else if (row < M) {
+        float* dst = C + (size_t)row * ldc + col0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const int col = col0 + j;
+            if (col + 3 < N && ((((uintptr_t)dst) & 15) == 0)) {
+                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (col + e < N) dst[j + e] = __uint_as_float(r[j + e]);
+            }
+        }
+    }
 }
 
 constexpr int kGemmStages = 3;
@@ -221,42 +265,143 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         for (int c0 = 0; c0 < BN; c0 += 32) {
             uint32_t r[32];
             tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
-            if (row < M && c_is_bf16) {
-                // bf16 output (inference configuration): C is a __nv_bfloat16 matrix, ldc in elements
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (size_t)row * ldc + n0 + c0;
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    const int col = n0 + c0 + j;
-                    if (col + 7 < N && ((((uintptr_t)(dst + j)) & 15) == 0)) {
-                        uint32_t wv[4];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * q]),
-                                                                            __uint_as_float(r[j + 2 * q + 1]));
-                            wv[q] = *reinterpret_cast<const uint32_t*>(&h2);
-                        }
-                        *reinterpret_cast<uint4*>(dst + j) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e)
-                            if (col + e < N) dst[j + e] = __float2bfloat16_rn(__uint_as_float(r[j + e]));
-                    }
-                }
-            } else if (row < M) {
-                float* dst = C + (size_t)row * ldc + n0 + c0;
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    const int col = n0 + c0 + j;
-                    if (col + 3 < N && ((((uintptr_t)dst) & 15) == 0)) {
-                        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                          __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (col + e < N) dst[j + e] = __uint_as_float(r[j + e]);
-                    }
+            store_acc_segment(r, row, M, N, n0 + c0, C, ldc, c_is_bf16);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent form of the kernel above: one CTA per SM walks the output tiles, the accumulator is
+// double-buffered in tensor memory (2 x BN columns), and the roles never meet inside a tile:
+//   warp 0, one lane : TMA producer, runs ahead across tile boundaries (the stage ring never drains)
+//   warp 1, one lane : MMA issuer, starts the next tile in the other accumulator as soon as that one is free
+//   warps 2-5        : epilogue of the finished accumulator (warp w reads tensor-memory lanes
+//                      [32 (w % 4), 32 (w % 4) + 32)), then hands the accumulator back
+// so the pipeline fill and the epilogue of one tile overlap the main loop of its neighbors.
+template <int BN, bool SPLIT>
+__global__ void __launch_bounds__(192)
+gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                            const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                            float* __restrict__ C, int M, int N, int ldc, int k_blocks, int c_is_bf16, int n_tiles,
+                            int num_tiles, int* status) {
+    using SM = NtSmem<BN, SPLIT>;
+    constexpr int kStages = SM::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + kStages * SM::kStage);
+    uint64_t* full = bars;                       // [stages] TMA -> MMA
+    uint64_t* empty = bars + kStages;            // [stages] MMA -> TMA
+    uint64_t* acc_full = bars + 2 * kStages;     // [2] MMA -> epilogue
+    uint64_t* acc_empty = bars + 2 * kStages + 2;  // [2] epilogue (4 warps) -> MMA
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kStages + 4);
+    constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;
+    constexpr uint32_t kTmemCols = 2 * kAccCols;  // a power of two in [64, 512]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full + a, 1);
+            mbar_init(acc_empty + a, 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool ok = true;
+    if (warp == 0 && lane == 0) {
+        int it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile / n_tiles) * kGemmBM, n0 = (tile % n_tiles) * BN;
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % kStages, round = it / kStages;
+                if (round > 0) ok = mbar_wait(empty + s, (round - 1) & 1);
+                if (!ok) break;
+                uint8_t* st = smem + s * SM::kStage;
+                mbar_expect_tx(full + s, SM::kStage);
+                tma_load_2d(st, &map_a_hi, full + s, kb * kGemmBK, m0);
+                tma_load_2d(st + SM::kA, &map_b_hi, full + s, kb * kGemmBK, n0);
+                if (SPLIT) {
+                    tma_load_2d(st + SM::kA + SM::kB, &map_a_lo, full + s, kb * kGemmBK, m0);
+                    tma_load_2d(st + 2 * SM::kA + SM::kB, &map_b_lo, full + s, kb * kGemmBK, n0);
                 }
             }
+        }
+        if (!ok) atomicExch(status, 1);
+    } else if (warp == 1 && lane == 0) {
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                   ((uint32_t)(kGemmBM >> 4) << 24);
+        int it = 0, local = 0;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            const int a = local & 1, use = local >> 1;
+            // the first use of an accumulator finds its barrier in the initial phase and passes at once
+            ok = mbar_wait(acc_empty + a, (uint32_t)((use & 1) ^ 1));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + (uint32_t)a * kAccCols;
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % kStages, round = it / kStages;
+                ok = mbar_wait(full + s, round & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t st = smem_u32(smem + s * SM::kStage);
+                const uint64_t da_hi = umma_desc_k_sw128(st), db_hi = umma_desc_k_sw128(st + SM::kA);
+                const uint64_t da_lo = umma_desc_k_sw128(st + SM::kA + SM::kB);
+                const uint64_t db_lo = umma_desc_k_sw128(st + 2 * SM::kA + SM::kB);
+#pragma unroll
+                for (int k = 0; k < kGemmBK / 16; ++k) {
+                    tc_mma_bf16(acc, da_hi + 2 * k, db_hi + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    if (SPLIT) {
+                        tc_mma_bf16(acc, da_lo + 2 * k, db_hi + 2 * k, idesc, 1u);
+                        tc_mma_bf16(acc, da_hi + 2 * k, db_lo + 2 * k, idesc, 1u);
+                    }
+                }
+                tc_commit(empty + s);
+            }
+            if (ok) tc_commit(acc_full + a);
+        }
+        if (!ok) atomicExch(status, 1);
+    } else if (warp >= 2) {
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+            const int a = local & 1, use = local >> 1;
+            const int m0 = (tile / n_tiles) * kGemmBM, n0 = (tile % n_tiles) * BN;
+            if (!mbar_wait(acc_full + a, (uint32_t)(use & 1))) {
+                if (lane == 0) atomicExch(status, 2);
+                break;
+            }
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tc_ld_32x32(tmem_base + (uint32_t)a * kAccCols + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+                store_acc_segment(r, row, M, N, n0 + c0, C, ldc, c_is_bf16);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + a);
         }
     }
     tc_fence_before();
@@ -491,11 +636,22 @@ static int launch_gemm_impl(const CUtensorMap& ma_hi, const CUtensorMap& ma_lo, 
     std::call_once(once, [] {
         attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<BN, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         NtSmem<BN, SPLIT>::kBytes);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(gemm_bf16_persistent_kernel<BN, SPLIT>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, NtSmem<BN, SPLIT>::kBytes);
     });
     PCCNN_CUDA(attr_err);
-    dim3 grid((unsigned)((M + kGemmBM - 1) / kGemmBM), (unsigned)((N + BN - 1) / BN));
-    gemm_bf16_kernel<BN, SPLIT><<<grid, 128, NtSmem<BN, SPLIT>::kBytes, s>>>(ma_hi, ma_lo, mb_hi, mb_lo, C, (int)M, N, ldc,
-                                                                          K_padded / kGemmBK, c_is_bf16, status);
+    const int m_tiles = (int)((M + kGemmBM - 1) / kGemmBM), n_tiles = (N + BN - 1) / BN;
+    const long long num_tiles = (long long)m_tiles * n_tiles;
+    if (num_tiles > sm_count() && num_tiles < 0x7fffffffLL) {
+        // more tiles than SMs: one persistent CTA per SM, fill and epilogue hidden behind neighboring tiles
+        gemm_bf16_persistent_kernel<BN, SPLIT><<<sm_count(), 192, NtSmem<BN, SPLIT>::kBytes, s>>>(
+            ma_hi, ma_lo, mb_hi, mb_lo, C, (int)M, N, ldc, K_padded / kGemmBK, c_is_bf16, n_tiles, (int)num_tiles, status);
+    } else {
+        dim3 grid((unsigned)m_tiles, (unsigned)n_tiles);
+        gemm_bf16_kernel<BN, SPLIT><<<grid, 128, NtSmem<BN, SPLIT>::kBytes, s>>>(ma_hi, ma_lo, mb_hi, mb_lo, C, (int)M, N, ldc,
+                                                                              K_padded / kGemmBK, c_is_bf16, status);
+    }
     PCCNN_LAUNCH_CHECK();
     return PCCNN_OK;
 }

@@ -6,7 +6,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(128, 128, 64), (300, 64, 256), (1000, 4, 512), (257, 200, 2048), (500, 600, 128), (64, 32, 48),
-          (4096, 128, 2048), (1, 16, 64), (129, 17, 100)]
+          (4096, 128, 2048), (1, 16, 64), (129, 17, 100),
+          # more output tiles than SMs: the persistent kernel with the double-buffered accumulator
+          (40000, 128, 192), (30000, 300, 128), (25000, 40, 320), (20001, 16, 64)]
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES)
@@ -23,7 +25,7 @@ def test_split_gemm_has_fp32_accuracy(m, n, k):
     assert np.allclose(got, expect, rtol=1e-4, atol=1e-4 * np.sqrt(k))
 
 
-@pytest.mark.parametrize("m,n,k", SHAPES[:5])
+@pytest.mark.parametrize("m,n,k", SHAPES[:5] + SHAPES[-4:-2])
 def test_single_pass_gemm_matches_bf16_rounded_inputs(m, n, k):
     from pccnn_lib_b200 import ops
     rs = np.random.RandomState(7 * m + n + k)

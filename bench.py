@@ -616,6 +616,20 @@ def run_conv_workload(args):
                      "rows": int(rows), "inner": int(kpad), "cols": int(cout), "ms": gemm_ms,
                      "useful_fp32_equivalent_tflops": round(flops / 3 / (gemm_ms * 1e-3) / 1e12, 2)},
     }
+    # CPU baseline for the layer-sized forward workload: the torch composition that mirrors the reference's
+    # ATen host code (index_select, broadcast ops, index_add_, matmul) on all host cores, float32.
+    if w["kind"] == "kp" and not w["backward"] and t * k * cin <= (1 << 28) and not args.no_cpu:
+        from oracle import conv_oracle
+        host = [x.cpu() for x in (pc.pts_, feats, pc_out.pts_, nb.neighbors_, nb.start_ids_, rad, kpts, weights)]
+        conv_oracle.kp_conv(host[0], host[1], host[2], host[3], host[4], host[5], host[6], sigma, host[7], dtype=torch.float32)
+        reps, c0 = 5, time.perf_counter()
+        for _ in range(reps):
+            conv_oracle.kp_conv(host[0], host[1], host[2], host[3], host[4], host[5], host[6], sigma, host[7],
+                                dtype=torch.float32)
+        cpu_s = (time.perf_counter() - c0) / reps
+        line["cpu_baseline"] = {"value": m / cpu_s, "unit": "points/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": "the whole layer, %d forward passes of the torch-CPU restatement, %.2f ms each"
+                                          % (reps, cpu_s * 1e3)}
     print(json.dumps(line))
 
 

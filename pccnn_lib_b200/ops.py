@@ -6,6 +6,7 @@ libpccnn_b200.so with raw device pointers on the current CUDA stream.  Outputs a
 with torch so they live in the caller's caching allocator.  Tensors must be CUDA tensors:
 there is no CPU path.
 """
+import contextlib
 import ctypes
 
 import torch
@@ -36,6 +37,16 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+_SAME_DEVICE = contextlib.nullcontext()
+
+
+def _on(device):
+    """Makes `device` current for the call; free when it already is (the usual case)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _SAME_DEVICE
+    return torch.cuda.device(device)
+
+
 def _workspace(nbytes, device):
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
 
@@ -56,7 +67,7 @@ def bounding_box(pts, batch_ids, num_batches):
     b = int(num_batches)
     mn = torch.empty((b, d), dtype=torch.float32, device=pts.device)
     mx = torch.empty((b, d), dtype=torch.float32, device=pts.device)
-    with torch.cuda.device(pts.device):
+    with _on(pts.device):
         _capi.check(_lib.pccnn_bounding_box(d, pts.shape[0], _p(pts), _p(batch_ids), b, _p(mn), _p(mx),
                                             _stream()), "bounding_box")
     return mn, mx
@@ -69,7 +80,7 @@ def grid_num_cells(aabb_min, aabb_max, cell_size):
     cell_size = _need(cell_size, "cell_size", torch.float32, 1)
     d = aabb_min.shape[1]
     out = torch.empty((d,), dtype=torch.int32, device=aabb_min.device)
-    with torch.cuda.device(aabb_min.device):
+    with _on(aabb_min.device):
         _capi.check(_lib.pccnn_grid_num_cells(d, aabb_min.shape[0], _p(aabb_min), _p(aabb_max), _p(cell_size),
                                               _p(out), _stream()), "grid_num_cells")
     return out
@@ -88,7 +99,7 @@ def compute_keys(pts, batch_ids, aabb_min, grid_size, cell_size):
     if batch_ids.shape[0] != pts.shape[0]:
         raise RuntimeError("batch_ids and pts disagree on the number of points")
     out = torch.empty((pts.shape[0],), dtype=torch.int64, device=pts.device)
-    with torch.cuda.device(pts.device):
+    with _on(pts.device):
         _capi.check(_lib.pccnn_compute_keys(d, pts.shape[0], _p(pts), _p(batch_ids), _p(aabb_min),
                                             _p(grid_size), _p(cell_size), _p(out), _stream()), "compute_keys")
     return out
@@ -109,7 +120,7 @@ def sort_keys(keys, key_bits=64, pts=None):
         pts = _need(pts, "pts", torch.float32, 2)
         d = _dims(pts)
         sorted_pts = torch.empty_like(pts)
-    with torch.cuda.device(keys.device):
+    with _on(keys.device):
         nbytes = _lib.pccnn_sort_keys_workspace_bytes(n)
         ws = _workspace(nbytes, keys.device)
         _capi.check(_lib.pccnn_sort_keys(n, _p(keys), int(key_bits), _p(sorted_keys), _p(sorted_ids), d, _p(pts),
@@ -142,7 +153,7 @@ def grid_front_end(pts, batch_ids, num_batches, cell_size):
     keys = torch.empty((n,), dtype=torch.int64, device=dev)
     sorted_keys, sorted_ids, sorted_pts = torch.empty_like(keys), torch.empty_like(keys), torch.empty_like(pts)
     host_cells = (ctypes.c_int32 * d)()
-    with torch.cuda.device(dev):
+    with _on(dev):
         stream = _stream()
         ws = _workspace(_lib.pccnn_grid_front_end_workspace_bytes(n), dev)
         _capi.check(_lib.pccnn_grid_front_end(d, n, _p(pts), _p(batch_ids), b, _p(cell_size), _p(mn), _p(mx), _p(cells),
@@ -166,7 +177,7 @@ def build_grid_ds(keys, grid_size, out_shape):
     d = grid_size.numel()
     out = torch.empty(shape, dtype=torch.int32, device=keys.device)
     entries = shape[0] * shape[1] * shape[2]
-    with torch.cuda.device(keys.device):
+    with _on(keys.device):
         _capi.check(_lib.pccnn_build_grid_ds(d, keys.shape[0], _p(keys), _p(grid_size), entries, _p(out),
                                              _stream()), "build_grid_ds")
     return out
@@ -205,7 +216,7 @@ def find_neighbors_count(pts, pt_keys, samples, sample_keys, grid_ds, grid_size,
     st.keep = (pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii)  # keep the inputs alive
     st.start_ids = torch.empty((m,), dtype=torch.int32, device=pts.device)
     total = ctypes.c_int64(0)
-    with torch.cuda.device(pts.device):
+    with _on(pts.device):
         nbytes = _lib.pccnn_find_neighbors_workspace_bytes(d, m)
         if workspace_bytes is not None:
             nbytes = max(int(workspace_bytes), _lib.pccnn_find_neighbors_min_workspace_bytes(d, m))
@@ -222,7 +233,7 @@ def find_neighbors_count(pts, pt_keys, samples, sample_keys, grid_ds, grid_size,
 def find_neighbors_store(st):
     """Second half of find_neighbors: allocates the [T, 2] list and fills it."""
     neighbors = torch.empty((st.total, 2), dtype=torch.int32, device=st.device)
-    with torch.cuda.device(st.device):
+    with _on(st.device):
         _capi.check(_lib.pccnn_find_neighbors_store(*st.common, _p(st.start_ids), _p(st.pt_index_map), _p(neighbors),
                                                     st.workspace.data_ptr(), st.workspace.numel(), _stream()),
                     "find_neighbors (store)")
@@ -262,7 +273,7 @@ def compute_pdf(manifold_dims, bandwidth, pts, neighbors, start_ids):
     """Unnormalised KDE per point; compute_pdf() of compute_pdf/compute_pdf.cu:153-203."""
     bandwidth, pts, neighbors, start_ids, d = _pdf_args(bandwidth, pts, neighbors, start_ids)
     out = torch.empty((pts.shape[0],), dtype=torch.float32, device=pts.device)
-    with torch.cuda.device(pts.device):
+    with _on(pts.device):
         ws = _workspace(_lib.pccnn_compute_pdf_workspace_bytes(d, pts.shape[0]), pts.device)
         _capi.check(_lib.pccnn_compute_pdf(d, int(manifold_dims), _p(bandwidth), pts.shape[0], _p(pts),
                                            _p(neighbors), _p(start_ids), _p(out), ws.data_ptr(), ws.numel(), _stream()),
@@ -275,7 +286,7 @@ def compute_pdf_grads(manifold_dims, bandwidth, pts, neighbors, start_ids, in_gr
     bandwidth, pts, neighbors, start_ids, d = _pdf_args(bandwidth, pts, neighbors, start_ids)
     in_grads = _need(in_grads, "in_grads", torch.float32, 1)
     out = torch.empty_like(pts)
-    with torch.cuda.device(pts.device):
+    with _on(pts.device):
         _capi.check(_lib.pccnn_compute_pdf_grads(d, int(manifold_dims), _p(bandwidth), pts.shape[0], _p(pts),
                                                  _p(neighbors), _p(start_ids), _p(in_grads), _p(out), _stream()),
                     "compute_pdf_grads")
@@ -294,7 +305,7 @@ def poisson_disk_sampling(sorted_keys, neighbors, start_ids, grid_size):
     d = grid_size.numel()
     selected = torch.empty((n,), dtype=torch.int64, device=sorted_keys.device)
     count = ctypes.c_int64(0)
-    with torch.cuda.device(sorted_keys.device):
+    with _on(sorted_keys.device):
         ws = _workspace(_lib.pccnn_poisson_disk_sampling_workspace_bytes(n), sorted_keys.device)
         _capi.check(_lib.pccnn_poisson_disk_sampling(d, n, _p(sorted_keys), _p(neighbors), _p(start_ids),
                                                      _p(grid_size), _p(selected), ctypes.byref(count),
@@ -317,7 +328,7 @@ def poisson_disk_sampling_grid(sorted_pts, sorted_keys, grid_ds, grid_size, radi
         raise RuntimeError("poisson_disk_sampling_grid: sizes of keys / grid_size / radii do not match the points")
     selected = torch.empty((n,), dtype=torch.int64, device=sorted_pts.device)
     count = ctypes.c_int64(0)
-    with torch.cuda.device(sorted_pts.device):
+    with _on(sorted_pts.device):
         ws = _workspace(_lib.pccnn_poisson_disk_sampling_grid_workspace_bytes(n), sorted_pts.device)
         _capi.check(_lib.pccnn_poisson_disk_sampling_grid(d, n, _p(sorted_pts), _p(sorted_keys), _p(grid_ds),
                                                           _p(grid_size), _p(radii), _p(selected), ctypes.byref(count),
@@ -340,7 +351,7 @@ def gemm_f32(a, b, split=True):
     out = torch.empty((m, n), dtype=torch.float32, device=a.device)
     if n == 0 or k == 0:
         return out.zero_()
-    with torch.cuda.device(a.device):
+    with _on(a.device):
         ws = _workspace(_lib.pccnn_gemm_workspace_bytes(m, n, k), a.device)
         _capi.check(_lib.pccnn_gemm_f32(m, n, k, _p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0),
                                         1 if split else 0, ws.data_ptr(), ws.numel(), _stream()), "gemm_f32")
@@ -378,7 +389,7 @@ def kp_conv(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma,
         raise RuntimeError("kernel_pts must be [K, %d] and weights [K * Cin, Cout]" % d)
     m = samples.shape[0]
     out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
-    with torch.cuda.device(pts.device):
+    with _on(pts.device):
         ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
         _capi.check(_lib.pccnn_kp_conv(d, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
                                        _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
@@ -396,7 +407,7 @@ def _kp_conv_bf16(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, 
         raise RuntimeError("bfloat16 KPConv needs 3-D points, kernel_pts [K, 3] and weights [K * Cin, Cout]")
     m = samples.shape[0]
     out = torch.empty((m, cout), dtype=torch.bfloat16, device=pts.device)
-    with torch.cuda.device(pts.device):
+    with _on(pts.device):
         ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
         _capi.check(_lib.pccnn_kp_conv_bf16(d, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
                                             _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights),
@@ -418,7 +429,7 @@ def mc_conv(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_proj, ax
         raise RuntimeError("axis_proj must be [%d, H], axis_bias [1, H] and weights [mlps, H * Cin / mlps, Cout / mlps]" % d)
     m = samples.shape[0]
     out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
-    with torch.cuda.device(pts.device):
+    with _on(pts.device):
         ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, hidden, cout), pts.device)
         _capi.check(_lib.pccnn_mc_conv(d, pts.shape[0], _p(pts), _p(pdf), _p(feats), cin, m, _p(samples), _p(neighbors),
                                        _p(start_ids), _p(radii), _p(axis_proj), _p(axis_bias), hidden, n_mlps,
@@ -445,7 +456,7 @@ def gemm_bf16(a_hi, b_hi, a_lo=None, b_lo=None, out=None, status=None):
         out = torch.empty((m, n), dtype=torch.float32, device=a_hi.device)
     if status is None:
         status = torch.zeros((1,), dtype=torch.int32, device=a_hi.device)
-    with torch.cuda.device(a_hi.device):
+    with _on(a_hi.device):
         _capi.check(_lib.pccnn_gemm_bf16(m, n, k, _p(a_hi), _p(a_lo), a_hi.stride(0), _p(b_hi), _p(b_lo), b_hi.stride(0),
                                          _p(out), out.stride(0), _p(status), _stream()), "gemm_bf16")
     return out
@@ -463,7 +474,7 @@ def gemm_tn_f32(a, b, split=True):
     out = torch.zeros((i, n), dtype=torch.float32, device=a.device)
     if r == 0 or i == 0 or n == 0:
         return out
-    with torch.cuda.device(a.device):
+    with _on(a.device):
         ws = _workspace(_lib.pccnn_gemm_tn_workspace_bytes(r, i, n), a.device)
         _capi.check(_lib.pccnn_gemm_tn_f32(r, i, n, _p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0),
                                            1 if split else 0, ws.data_ptr(), ws.numel(), _stream()), "gemm_tn_f32")
@@ -483,7 +494,7 @@ def kp_conv_grads(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, 
     dev = pts.device
     d_w, d_f = torch.empty_like(weights), torch.empty_like(feats)
     d_k, d_p, d_s = torch.empty_like(kernel_pts), torch.empty_like(pts), torch.empty_like(samples)
-    with torch.cuda.device(dev):
+    with _on(dev):
         ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, k, cout), dev)
         _capi.check(_lib.pccnn_kp_conv_grads(d, n, _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
                                              _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights),
@@ -510,7 +521,7 @@ def mc_conv_grads(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_pr
     d_w, d_f = torch.empty_like(weights), torch.empty_like(feats)
     d_a, d_b, d_pdf = torch.empty_like(axis_proj), torch.empty_like(axis_bias), torch.empty_like(pdf)
     d_p, d_s = torch.empty_like(pts), torch.empty_like(samples)
-    with torch.cuda.device(dev):
+    with _on(dev):
         ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, hidden, cout), dev)
         _capi.check(_lib.pccnn_mc_conv_grads(d, n, _p(pts), _p(pdf), _p(feats), cin, m, _p(samples), _p(neighbors),
                                              _p(start_ids), _p(radii), _p(axis_proj), _p(axis_bias), hidden, n_mlps,

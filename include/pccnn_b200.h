@@ -138,14 +138,17 @@ int pccnn_build_grid_ds(int D, int64_t n, const int64_t* sorted_keys, const int3
  * Workspace: pccnn_find_neighbors_workspace_bytes is the recommended size.  Beyond the fixed
  * part (pccnn_find_neighbors_min_workspace_bytes) it holds a pool in which the count pass keeps
  * one bit per tested candidate so that the store pass need not test again; samples whose bits
- * no longer fit are simply tested twice.  Any size >= the minimum gives the same result. */
+ * no longer fit are simply tested twice.  Any size >= the minimum gives the same result.
+ * sample_key_bits: number of low key bits that can be set (0 = unknown, all 64); samples that are not
+ * the sorted points themselves are ordered by key with that many radix passes' worth of bits. */
 size_t pccnn_find_neighbors_workspace_bytes(int D, int64_t num_samples);
 size_t pccnn_find_neighbors_min_workspace_bytes(int D, int64_t num_samples);
 int pccnn_find_neighbors_count(int D, int64_t num_pts, const float* pts, const int64_t* pt_keys,
                                int64_t num_samples, const float* samples, const int64_t* sample_keys,
                                const int32_t* grid_ds, const int32_t* grid_size, const float* radii,
-                               int32_t max_neighbors, int32_t* out_start_ids, int64_t* out_total_host,
-                               void* workspace, size_t workspace_bytes, void* stream);
+                               int32_t max_neighbors, int32_t sample_key_bits, int32_t* out_start_ids,
+                               int64_t* out_total_host, void* workspace, size_t workspace_bytes,
+                               void* stream);
 /* pt_index_map may be NULL; otherwise row.x = (int32)pt_index_map[point index], which
  * replaces the mapping through sorted_ids in pccnn_lib/pc/Neighborhood.py:47-53. */
 int pccnn_find_neighbors_store(int D, int64_t num_pts, const float* pts, const int64_t* pt_keys,

@@ -30,7 +30,7 @@ SIGNATURES = {
     "pccnn_find_neighbors_workspace_bytes": (_size, [_c_int, _c_i64]),
     "pccnn_find_neighbors_min_workspace_bytes": (_size, [_c_int, _c_i64]),
     "pccnn_find_neighbors_count": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
-                                            _c_i32, _ptr, ctypes.POINTER(_c_i64), _ptr, _size, _ptr]),
+                                            _c_i32, _c_i32, _ptr, ctypes.POINTER(_c_i64), _ptr, _size, _ptr]),
     "pccnn_find_neighbors_store": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
                                             _c_i32, _ptr, _ptr, _ptr, _ptr, _size, _ptr]),
     "pccnn_compute_pdf_workspace_bytes": (_size, [_c_int, _c_i64]),

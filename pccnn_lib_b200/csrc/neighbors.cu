@@ -423,9 +423,10 @@ size_t pccnn_find_neighbors_min_workspace_bytes(int D, int64_t num_samples) {
 int pccnn_find_neighbors_count(int D, int64_t num_pts, const float* pts, const int64_t* pt_keys,
                                int64_t num_samples, const float* samples, const int64_t* sample_keys,
                                const int32_t* grid_ds, const int32_t* grid_size, const float* radii,
-                               int32_t max_neighbors, int32_t* out_start_ids, int64_t* out_total_host,
-                               void* workspace, size_t workspace_bytes, void* stream) {
+                               int32_t max_neighbors, int32_t sample_key_bits, int32_t* out_start_ids,
+                               int64_t* out_total_host, void* workspace, size_t workspace_bytes, void* stream) {
     if (int rc = check_common("find_neighbors_count", D, num_pts, num_samples)) return rc;
+    PCCNN_CHECK_ARG(sample_key_bits >= 0 && sample_key_bits <= 64, "find_neighbors_count: sample_key_bits outside [0, 64]");
     PCCNN_CHECK_ARG(out_total_host, "find_neighbors_count: null out_total_host");
     PCCNN_CHECK_ARG(max_neighbors >= 0, "find_neighbors_count: negative max_neighbors");
     *out_total_host = 0;
@@ -454,7 +455,8 @@ int pccnn_find_neighbors_count(int D, int64_t num_pts, const float* pts, const i
         PCCNN_LAUNCH_CHECK();
         size_t cub_bytes = L.cub_bytes;
         PCCNN_CUDA(cub::DeviceRadixSort::SortPairs(ws + L.cub_off, cub_bytes, sample_keys, (int64_t*)(ws + L.keys_off),
-                                                   (const int32_t*)iota, (int32_t*)(ws + L.order_off), m, 0, 64, s));
+                                                   (const int32_t*)iota, (int32_t*)(ws + L.order_off), m, 0,
+                                                   sample_key_bits > 0 ? sample_key_bits : 64, s));
         order = (const int32_t*)(ws + L.order_off);
     }
     PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kCount><<<neighbor_grid(m), kWarpsPerBlock * 32, 0, s>>>(

@@ -190,11 +190,12 @@ class _NeighborSearch(object):
 
 
 def find_neighbors_count(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii, max_neighbors,
-                         pt_index_map=None, workspace_bytes=None):
+                         pt_index_map=None, workspace_bytes=None, key_bits=0):
     """First half of find_neighbors: counts, scans and learns T (one host synchronisation).
     Returns the state object to hand to find_neighbors_store.  `workspace_bytes` overrides the
     recommended scratch size (never below the library's minimum); a smaller scratch only makes
-    the store pass repeat more distance tests."""
+    the store pass repeat more distance tests.  `key_bits` (0 = unknown): how many low bits of the keys
+    can be set, which shortens the ordering of samples that are not the sorted points themselves."""
     pts = _need(pts, "pts", torch.float32, 2)
     pt_keys = _need(pt_keys, "pt_keys", torch.int64, 1)
     samples = _need(samples, "samples", torch.float32, 2)
@@ -223,7 +224,7 @@ def find_neighbors_count(pts, pt_keys, samples, sample_keys, grid_ds, grid_size,
         st.workspace = _workspace(nbytes, pts.device)
         st.common = (d, n, _p(pts), _p(pt_keys), m, _p(samples), _p(sample_keys), _p(grid_ds), _p(grid_size),
                      _p(radii), int(max_neighbors))
-        _capi.check(_lib.pccnn_find_neighbors_count(*st.common, _p(st.start_ids), ctypes.byref(total),
+        _capi.check(_lib.pccnn_find_neighbors_count(*st.common, int(key_bits), _p(st.start_ids), ctypes.byref(total),
                                                     st.workspace.data_ptr(), st.workspace.numel(), _stream()),
                     "find_neighbors (count)")
     st.total = total.value
@@ -241,7 +242,7 @@ def find_neighbors_store(st):
 
 
 def find_neighbors(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii, max_neighbors,
-                   pt_index_map=None, workspace_bytes=None):
+                   pt_index_map=None, workspace_bytes=None, key_bits=0):
     """Radius search -> [neighbors [T, 2] int32, start_ids [M] int32 (inclusive ends)].
 
     find_neighbors() of find_neighbors/find_neighbors.cu:27-66 of the reference.  `pts` and
@@ -250,7 +251,7 @@ def find_neighbors(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii
     as pccnn_lib/pc/Neighborhood.py:47-53 does afterwards.
     """
     return find_neighbors_store(find_neighbors_count(pts, pt_keys, samples, sample_keys, grid_ds, grid_size, radii,
-                                                     max_neighbors, pt_index_map, workspace_bytes))
+                                                     max_neighbors, pt_index_map, workspace_bytes, key_bits))
 
 
 # ---- kernel density estimation ---------------------------------------------------------------

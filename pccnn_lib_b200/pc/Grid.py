@@ -66,6 +66,16 @@ class Grid(object):
                 key_bits = min(64, max(1, int(math.ceil(math.log2(span + 1)))))
                 self.sorted_cell_ids_, self.sorted_ids_, self.sorted_pts_ = ops.sort_keys(self.cell_ids_, key_bits, pts)
 
+    def key_bits(self):
+        """Number of low bits a key of this grid can have set (0 when the cells per axis are not known on
+        the host yet)."""
+        if self._num_cells_host is None:
+            return 0
+        span = float(self.pointcloud_.batch_size_host())
+        for c in self._num_cells_host:
+            span *= c
+        return min(64, max(1, int(math.ceil(math.log2(span + 1)))))
+
     def build_ds(self):
         if self.cell_ids_ is None or self.sorted_ids_ is None:
             raise RuntimeError('In order to build the data structure first the'

@@ -1,7 +1,6 @@
 import torch
 
 from .. import ops
-from ..op_wrappers import ComputeKeys
 
 
 class Neighborhood(object):
@@ -22,11 +21,13 @@ class Neighborhood(object):
             if grid.grid_ds_ is None:
                 grid.compute_cell_ids()
                 grid.build_ds()
-            sample_cell_ids = ComputeKeys.apply(self.samples_.pts_.detach(), self.samples_.batch_ids_,
-                                                grid.bounding_box_.min_, grid.num_cells_, grid.cell_size_)
+            # keys carry no gradient: the operator is called directly, without the autograd wrapper
+            sample_cell_ids = ops.compute_keys(self.samples_.pts_.detach(), self.samples_.batch_ids_,
+                                               grid.bounding_box_.min_, grid.num_cells_, grid.cell_size_)
             self.neighbors_, self.start_ids_ = ops.find_neighbors(
                 grid.sorted_pts_, grid.sorted_cell_ids_, self.samples_.pts_.detach(), sample_cell_ids,
-                grid.grid_ds_, grid.num_cells_, grid.cell_size_, p_max_neighbors, pt_index_map=grid.sorted_ids_)
+                grid.grid_ds_, grid.num_cells_, grid.cell_size_, p_max_neighbors, pt_index_map=grid.sorted_ids_,
+                key_bits=grid.key_bits())
 
     def __repr__(self):
         return "### Neighbors:\n{}\n### Start indices:\n{}".format(self.neighbors_, self.start_ids_)

@@ -733,8 +733,9 @@ def cpu_step(pts, batch_ids, num_clouds):
 
 
 def cpu_baseline_sample(num_clouds=None):
+    from oracle import oracle
     num_clouds = num_clouds or CLOUDS_PER_RANK
-    cores = len(os.sched_getaffinity(0))
+    cores = oracle.set_threads(len(os.sched_getaffinity(0)))  # a launcher may have capped OMP_NUM_THREADS
     pts, ids = make_batch(0, num_clouds)
     t0 = time.perf_counter()
     pairs = cpu_step(pts, ids, num_clouds)
@@ -749,7 +750,8 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    cores = len(os.sched_getaffinity(0))
+    from oracle import oracle
+    cores = oracle.set_threads(len(os.sched_getaffinity(0)))  # a launcher may have capped OMP_NUM_THREADS
     num_clouds = 8  # half of the batch per step keeps the default run within a couple of minutes
     pts, ids = make_batch(0, num_clouds)
     for _ in range(max(args.warmup, 1)):

@@ -34,6 +34,11 @@ def lib():
     return _lib
 
 
+def set_threads(n):
+    """Asks the OpenMP runtime of the oracle for n threads; returns how many it will use."""
+    return int(lib().orc_set_threads(int(n)))
+
+
 def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 

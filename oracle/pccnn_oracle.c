@@ -19,6 +19,9 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #define MAXD 6
 
@@ -326,4 +329,16 @@ int64_t orc_poisson_disk_sampling(int D, int64_t n, const int64_t* sorted_keys, 
     for (int64_t i = 0; i < n; ++i) if (used[i]) out_selected[k++] = i;
     free(used);
     return k;
+}
+
+/* Thread control for the timed CPU baseline: a launcher may have capped OMP_NUM_THREADS (torchrun sets it
+ * to 1 per rank); the bench asks for all the cores it is allowed to use and reports what it got. */
+int orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
 }

@@ -29,7 +29,7 @@
 
 namespace pccnn {
 
-constexpr int kWarpsPerBlock = 8;
+constexpr int kWarpsPerBlock = 4;
 
 enum : int { kCount = 0, kStore = 1, kStoreLimited = 2 };
 

@@ -633,6 +633,51 @@ def run_conv_workload(args):
     print(json.dumps(line))
 
 
+def run_pooling_workload(args):
+    """Poisson-disk pooling of the encoder's first level (64 clouds x 50k surface points, radius 0.02), both routes:
+    the reference's pair of operators (full self-neighborhood, then the list-based sampling) and the list-free
+    sampling on the grid.  One step = grid front end + sampling; the two selections are compared."""
+    import torch
+    from pccnn_lib_b200 import ops
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    clouds = args.clouds if args.clouds != CLOUDS_PER_RANK else 64
+    pts, ids = make_batch(0, clouds, args.points or 50000)
+    d_pts, d_ids = torch.as_tensor(pts, device=device), torch.as_tensor(ids, device=device)
+    cell = torch.full((3,), 0.02, dtype=torch.float32, device=device)
+
+    def event():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    rows = []
+    for i in range(max(args.warmup, 3) + args.steps):
+        m = [event()]
+        g = ops.grid_front_end(d_pts, d_ids, clouds, cell)
+        m.append(event())
+        nb, st = ops.find_neighbors(g["sorted_pts"], g["sorted_keys"], g["sorted_pts"], g["sorted_keys"], g["grid_ds"],
+                                    g["num_cells"], cell, 0)
+        m.append(event())
+        by_list = ops.poisson_disk_sampling(g["sorted_keys"], nb, st, g["num_cells"])
+        m.append(event())
+        by_grid = ops.poisson_disk_sampling_grid(g["sorted_pts"], g["sorted_keys"], g["grid_ds"], g["num_cells"], cell)
+        m.append(event())
+        torch.cuda.synchronize()
+        if i >= max(args.warmup, 3):
+            rows.append([m[j].elapsed_time(m[j + 1]) for j in range(4)])
+    same = bool(torch.equal(by_list, by_grid))
+    front, search, listed, gridded = [float(np.mean([r[j] for r in rows])) for j in range(4)]
+    print(json.dumps({
+        "metric": "pooled points/s (Poisson-disk pooling, list-free route)", "value": pts.shape[0] / ((front + gridded) * 1e-3),
+        "unit": "points/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": front + gridded,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32+i32/i64", "data": "synthetic",
+        "config": {"workload": run_pooling_workload.__doc__.split("\n")[0], "points": int(pts.shape[0]),
+                   "pairs_of_the_self_neighborhood": int(nb.shape[0]), "selected": int(by_grid.shape[0]),
+                   "grid_front_end_ms": front, "search_ms": search, "list_based_sampling_ms": listed,
+                   "list_free_sampling_ms": gridded, "selections_identical": same}}))
+
+
 def run_encoder_workload(args):
     """KPConv 5-level encoder, inference, bf16 features and weights with fp32 accumulation: 64 clouds x 50k
     surface points, Poisson-disk radii 0.02 ... 0.32, convolution radius 2.5 x the sampling radius, channels
@@ -844,7 +889,7 @@ def main():
                     help="convolution workloads: points per cloud (default: the workload's own size)")
     ap.add_argument("--presort", action="store_true",
                     help="convolution workloads: store the points in grid-cell order instead of random order")
-    ap.add_argument("--workload", default="neighbors_kde", choices=["neighbors_kde", "kpconv_encoder_cfg3"] + sorted(CONV_WORKLOADS),
+    ap.add_argument("--workload", default="neighbors_kde", choices=["neighbors_kde", "kpconv_encoder_cfg3", "pooling_cfg3_level1"] + sorted(CONV_WORKLOADS),
                     help="neighbors_kde is the headline workload; the others time one convolution layer")
     args = ap.parse_args()
     globals()["CLOUDS_PER_RANK"] = args.clouds
@@ -854,6 +899,8 @@ def main():
         run_conv_workload(args)
     elif args.impl == "reference_gpu":
         run_reference_gpu(args)
+    elif args.workload == "pooling_cfg3_level1":
+        run_pooling_workload(args)
     elif args.workload == "kpconv_encoder_cfg3":
         run_encoder_workload(args)
     elif args.workload != "neighbors_kde":

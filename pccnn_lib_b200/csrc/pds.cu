@@ -111,8 +111,11 @@ __device__ void pds_sparse_cells(int pass, int n, int warp_index, int warps_tota
                                  int32_t* used) {
     const int lane = lane_id();
     volatile int32_t* vused = used;
-    for (int base = warp_index * 32; base < num_cells; base += warps_total * 32) {
-        const int cell = base + lane;
+    // the 32 cells of a batch are taken num_batches apart: cells with long neighbor lists sit next to each
+    // other in cell order (dense clouds) and spread like this they land in different warps
+    const int num_batches = (num_cells + 31) / 32;
+    for (int batch = warp_index; batch < num_batches; batch += warps_total) {
+        const int cell = lane * num_batches + batch;
         const bool want = cell < num_cells && __ldg(code + cell) == (unsigned)pass;
         int my_first = 0, my_count = 0;
         if (want) {
@@ -397,11 +400,16 @@ pds_grid_pass_kernel(int pass, int n, const float* __restrict__ pts, const int64
     const int num_cells = counters[0];
     const int warps_total = gridDim.x * kGridPdsWarps;
 
-    for (int base = (blockIdx.x * kGridPdsWarps + warp) * 32; base < num_cells; base += warps_total * 32) {
-        const bool want = base + lane < num_cells && __ldg(code + base + lane) == (unsigned)pass;
+    // A warp looks at 32 cells at a time.  The 32 are taken num_batches apart rather than next to each other:
+    // crowded cells sit next to each other in cell order (dense clouds), and spread like this they land in
+    // different warps instead of queueing up in one.
+    const int num_batches = (num_cells + 31) / 32;
+    for (int batch = blockIdx.x * kGridPdsWarps + warp; batch < num_batches; batch += warps_total) {
+        const int my_cell = lane * num_batches + batch;
+        const bool want = my_cell < num_cells && __ldg(code + my_cell) == (unsigned)pass;
         unsigned todo = __ballot_sync(kFullMask, want);
         while (todo) {
-            const int ci = base + __ffs(todo) - 1;
+            const int ci = (__ffs(todo) - 1) * num_batches + batch;
             todo &= todo - 1;
             const int first = __ldg(cell_starts + ci);
             const int last = (ci + 1 < num_cells) ? __ldg(cell_starts + ci + 1) : n;

@@ -1,5 +1,8 @@
-"""``kernel_pts_dict['<dims>_<points>']``: kernel-point dispositions (float64 [points, dims], row 0 the
-centre), loaded from kernel_points.npz next to this file (see make_kernel_points.py)."""
+"""``kernel_pts_dict['<dims>_<points>']``: the KPConv kernel-point dispositions of the reference
+(pccnn_lib/pc/layers/kernel_points/kernel_points.py of phermosilla/pccnn_lib: float64 [points, dims], row 0
+the centre; 2, 3 and 4 dimensions with 8, 16, 32 and 64 points), loaded from kernel_points.npz next to this
+file.  The .npz is written by oracle/make_kernel_points.py, which imports the reference's module, so a new
+KPConv layer starts from the reference's kernel points and sigma."""
 import os
 
 import numpy as np

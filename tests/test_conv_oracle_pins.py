@@ -87,7 +87,7 @@ def test_kpconv_backward_formulas(ref_clouds, c):
     # the reference gradchecks weights, features and kernel points (unit_test/test_kpconv_grads.py:111-121)
     # and points (test_kpconv_pt_grads.py:98-100) numerically in float32; here the hand-written
     # backward is compared with autograd of the float64 forward.
-    case = kp_case(ref_clouds, c, normal_feats=True)
+    case = kp_case(ref_clouds, c, normal_feats=True, shrink=True)
     g = np.random.RandomState(3).normal(size=(case["samples"].shape[0], c["cout"]))
     args = dict(pts=case["pts"], feats=case["feats"], samples=case["samples"], neighbors=case["neighbors"],
                 start_ids=case["start_ids"], radii=case["radii"], kernel_pts=case["kernel_pts"],
@@ -119,3 +119,17 @@ def test_mcconv_oracle_with_two_mlps_is_block_diagonal(ref_clouds):
     got = conv_oracle.mc_conv(case["pts"], case["pdf"], case["feats"], case["samples"], case["neighbors"],
                               case["start_ids"], case["radii"], case["axis"], case["bias"], case["weights"])
     assert tuple(got.shape) == (case["samples"].shape[0], 64) and torch.isfinite(got).all()
+
+
+@pytest.mark.parametrize("dims", [2, 3, 4])
+@pytest.mark.parametrize("num_pts", [8, 16, 32, 64])
+def test_prepared_kernel_points_are_the_reference_layers(dims, num_pts):
+    # kernel_pts_ / sigma_ of a fresh KPConv layer against what the reference's constructor registers
+    # (pccnn_lib/pc/layers/KPConv.py:45-57), stored by oracle/make_kernel_points.py from the reference install
+    import os
+    from conftest import GOLDEN
+    from pccnn_lib_b200.pc.layers import prepare_kernel_points
+    golden = np.load(os.path.join(GOLDEN, "ref_kernel_points_prepared.npz"))
+    pts, sigma = prepare_kernel_points(dims, num_pts)
+    assert pts.dtype == np.float32 and np.array_equal(pts, golden["%d_%d_pts" % (dims, num_pts)])
+    assert sigma == float(golden["%d_%d_sigma" % (dims, num_pts)])

@@ -50,6 +50,31 @@ const char* pccnn_last_error(void);
 const char* pccnn_version(void);
 
 /* ------------------------------------------------------------------------- */
+/* Failure reporting and input validation                                     */
+/* ------------------------------------------------------------------------- */
+
+/* The reference checks nothing (no TORCH_CHECK, no cudaGetLastError in pccnn_lib_ops); these two entry points
+ * have no counterpart there.
+ *
+ * Kernels of this library never wait without a limit.  When a wait inside a tensor-core kernel of a convolution
+ * runs out, the kernel records it, releases what it holds and returns; the operator ends with a one-thread
+ * kernel that copies the record into one int of pinned host memory.  That int is sticky: the next convolution
+ * entry point of the process finds it, clears it and returns PCCNN_ERR_DEVICE before doing anything, and
+ * pccnn_check_status does the same on request -- with synchronize != 0 it first waits for `stream`, so that a
+ * failure of the calls enqueued so far cannot be missed; with synchronize == 0 it only reports what has already
+ * reached the host. */
+int pccnn_check_status(int synchronize, void* stream);
+
+/* Checks a caller-built neighbor list before it is handed to pccnn_compute_pdf*, pccnn_poisson_disk_sampling or the
+ * convolutions, which index points, features and samples with its entries unchecked: every row.x in
+ * [0, num_pts), every row.y equal to the sample whose segment holds the row, end offsets non-negative and
+ * non-decreasing, last end offset == total.  Synchronises the stream; returns PCCNN_ERR_INVALID with the first
+ * offending row or sample in the message.  Workspace: pccnn_validate_neighbors_workspace_bytes(). */
+size_t pccnn_validate_neighbors_workspace_bytes(void);
+int pccnn_validate_neighbors(int64_t num_pts, int64_t num_samples, const int32_t* neighbors, const int32_t* start_ids,
+                             int64_t total, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- */
 /* Bounding box and grid sizing (caller-side code of the reference)           */
 /* ------------------------------------------------------------------------- */
 
@@ -316,6 +341,12 @@ int pccnn_mc_conv_grads(int D, int64_t num_pts, const float* pts, const float* p
  * tcgen05 passes give fp32-level accuracy (relative error of a product below 2^-16);
  * split == 0: one bf16 pass.  Synchronises the stream to read the kernel's status word. */
 size_t pccnn_gemm_workspace_bytes(int64_t M, int N, int K);
+
+/* Test hooks of the tensor-core kernels on the current device (no counterpart in the reference): the poll limit of
+ * their bounded waits (<= 0 restores the default of 2^21 polls) and a producer that issues no load from K block
+ * `withhold_from` on (< 0: off), so that a test can let the consumers' waits run out with no copy in flight and
+ * check that the kernel returns, the status is reported and the next call works.  Not for production use. */
+int pccnn_gemm_set_test_hooks(int poll_limit, int withhold_from);
 int pccnn_gemm_f32(int64_t M, int N, int K, const float* A, int64_t lda, const float* B, int64_t ldb,
                    float* C, int64_t ldc, int split, void* workspace, size_t workspace_bytes, void* stream);
 

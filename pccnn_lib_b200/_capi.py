@@ -18,6 +18,10 @@ _size = ctypes.c_size_t
 SIGNATURES = {
     "pccnn_last_error": (ctypes.c_char_p, []),
     "pccnn_version": (ctypes.c_char_p, []),
+    "pccnn_check_status": (_c_int, [_c_int, _ptr]),
+    "pccnn_validate_neighbors_workspace_bytes": (_size, []),
+    "pccnn_validate_neighbors": (_c_int, [_c_i64, _c_i64, _ptr, _ptr, _c_i64, _ptr, _size, _ptr]),
+    "pccnn_gemm_set_test_hooks": (_c_int, [_c_int, _c_int]),
     "pccnn_bounding_box": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_i64, _ptr, _ptr, _ptr]),
     "pccnn_grid_num_cells": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "pccnn_compute_keys": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),

@@ -22,6 +22,7 @@
 
 #include "common.cuh"
 #include "gemm.cuh"
+#include "status.cuh"
 
 namespace pccnn {
 
@@ -682,12 +683,17 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
     const float* feats = (const float*)feats_any;
     const float* weights = (const float*)weights_any;
     float* out = (float*)out_any;
+    if (int rc = take_sticky_status(who)) return rc;  // an earlier call's tensor-core kernel gave up
     PCCNN_CHECK_ARG(!io_bf16 || D == 3, "%s: bf16 features are supported for 3-D points only", who);
     PCCNN_CHECK_ARG(D >= kMinDims && D <= kMaxDims, "%s: point dimension %d outside [2, 6]", who, D);
     PCCNN_CHECK_ARG(K >= 1 && K <= 64, "%s: basis size %d outside [1, 64]", who, K);
     PCCNN_CHECK_ARG(cin >= 1 && cout >= 1 && num_mlps >= 1 && cout % num_mlps == 0 && (cin * K) % num_mlps == 0,
                     "%s: bad channel counts (cin %d, cout %d, mlps %d)", who, cin, cout, num_mlps);
     PCCNN_CHECK_ARG(num_samples >= 0 && num_samples < 0x7fffffffLL && num_pts >= 0, "%s: bad sizes", who);
+    // Several MLPs: MLP j reads the j-th slice of the P rows and writes the j-th slice of the outputs; the
+    // slices are TMA operands of their own, so they must start on 16-byte boundaries (8 bf16 values).
+    PCCNN_CHECK_ARG(num_mlps == 1 || ((cin * K / num_mlps) % 8 == 0 && (cout / num_mlps) % 8 == 0),
+                    "%s: with several MLPs, Cin*K per MLP and Cout per MLP must be multiples of 8", who);
     if (num_samples == 0) return PCCNN_OK;
     PCCNN_CHECK_ARG(pts && feats && samples && start_ids && radii && weights && out, "%s: null pointer", who);
     const ConvLayout L = conv_layout(num_samples, cin, K, cout);
@@ -729,12 +735,12 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
         }
         if (rc) return rc;
         for (int j = 0; j < num_mlps; ++j) {
-            // Slice j of the P rows (offset j * inner_j, 16-byte aligned because inner_j % 8 == 0 is checked
-            // below) times W_j^T.  Columns read past the slice meet zero weights.
+            // Slice j of the P rows (offset j * inner_j, 16-byte aligned: inner_j % 8 == 0 was checked above)
+            // times W_j^T.  The reduction runs over the slice rounded up to 64 columns: what is read past the
+            // slice (the next MLP's columns, or the zero fill past the row end) meets the zero padding of W_j^T.
             const size_t a_off = (size_t)j * inner_j * 2;
             const size_t b_off = (size_t)j * cout_j * L.ld_p * 2;
-            PCCNN_CHECK_ARG(num_mlps == 1 || inner_j % 64 == 0, "%s: Cin*K per MLP must be a multiple of 64", who);
-            const int kp = num_mlps == 1 ? L.ld_p : inner_j;
+            const int kp = num_mlps == 1 ? L.ld_p : (inner_j + 63) / 64 * 64;
             GemmOperand a{ws + L.p_hi_off + a_off, io_bf16 ? nullptr : ws + L.p_lo_off + a_off, L.ld_p};
             GemmOperand b{ws + L.w_hi_off + b_off, io_bf16 ? nullptr : ws + L.w_lo_off + b_off, L.ld_p};
             float* c_ptr = io_bf16 ? (float*)((__nv_bfloat16*)out_any + (size_t)m0 * cout + (size_t)j * cout_j)
@@ -742,7 +748,7 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
             if (int rc2 = gemm_bf16_nt(a, b, c_ptr, m1 - m0, cout_j, kp, cout, status, s, io_bf16 ? 1 : 0)) return rc2;
         }
     }
-    return PCCNN_OK;
+    return publish_status(status, kOriginConvForward, s);
 }
 
 struct ConvBackwardLayout {
@@ -782,6 +788,7 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
                          const float* weights, int cout, const float* in_grads, float* d_weights, float* d_feat,
                          float* d_param0, size_t param0_floats, float* d_param1, size_t param1_floats, float* d_pdf,
                          float* d_pts, float* d_samples, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+    if (int rc = take_sticky_status(who)) return rc;  // an earlier call's tensor-core kernel gave up
     PCCNN_CHECK_ARG(D >= kMinDims && D <= kMaxDims, "%s: point dimension %d outside [2, 6]", who, D);
     PCCNN_CHECK_ARG(K >= 1 && K <= 64, "%s: basis size %d outside [1, 64]", who, K);
     PCCNN_CHECK_ARG(cin >= 1 && cout >= 1 && num_mlps >= 1 && cout % num_mlps == 0 && (cin * K) % num_mlps == 0,
@@ -789,8 +796,8 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
     PCCNN_CHECK_ARG(num_samples >= 0 && num_samples < 0x7fffffffLL && num_pts >= 0, "%s: bad sizes", who);
     PCCNN_CHECK_ARG(d_weights && d_feat && d_param0 && d_pts && d_samples, "%s: null output", who);
     const int inner = cin * K, inner_j = inner / num_mlps, cout_j = cout / num_mlps;
-    PCCNN_CHECK_ARG(num_mlps == 1 || (inner_j % 64 == 0 && cout_j % 64 == 0),
-                    "%s: with several MLPs, Cin*K and Cout per MLP must be multiples of 64", who);
+    PCCNN_CHECK_ARG(num_mlps == 1 || (inner_j % 8 == 0 && cout_j % 8 == 0),
+                    "%s: with several MLPs, Cin*K per MLP and Cout per MLP must be multiples of 8", who);
     PCCNN_CUDA(cudaMemsetAsync(d_weights, 0, (size_t)inner * cout_j * 4, s));
     PCCNN_CUDA(cudaMemsetAsync(d_feat, 0, (size_t)num_pts * cin * 4, s));
     PCCNN_CUDA(cudaMemsetAsync(d_param0, 0, param0_floats * 4, s));
@@ -836,7 +843,8 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
                                               cout_j, status, s)))
                 return rc;
             // dP_j = g_j W_j^T  ->  columns [j * inner_j, (j + 1) * inner_j) of the dP rows
-            const int kp = num_mlps == 1 ? L.ld_g : cout_j;
+            // (reduction over the MLP's outputs rounded up to 64: the surplus columns of g meet zero weights)
+            const int kp = num_mlps == 1 ? L.ld_g : (cout_j + 63) / 64 * 64;
             if ((rc = gemm_bf16_nt(g, w, d_proj + (size_t)j * inner_j, rows, inner_j, kp, inner, status, s))) return rc;
         }
         PCCNN_DISPATCH_DIM(D, (rc = launch_backward_pairs<DIM, ARGS, BASIS>(
@@ -844,7 +852,7 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
                                    d_proj, d_feat, d_pts, d_samples, d_param0, d_param1, d_pdf, s)));
         if (rc) return rc;
     }
-    return PCCNN_OK;
+    return publish_status(status, kOriginConvBackward, s);
 }
 
 }  // namespace pccnn

@@ -42,10 +42,16 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait: false when the barrier did not flip within the iteration limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Poll limit of every wait (about 2^21 polls are tens of milliseconds) and a test hook: a producer that stops
+// issuing loads from a given K block on, so that a test can watch the consumers' waits run out with no copy in
+// flight.  Both are read once per kernel; pccnn_gemm_set_test_hooks changes them.
+__device__ uint32_t d_poll_limit = 1u << 21;
+__device__ int d_withhold_from = -1;
+
+// Bounded wait: false when the barrier did not flip within `limit` polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < (1u << 21); ++it) {
+    for (uint32_t it = 0; it < limit; ++it) {
         uint32_t ok;
         asm volatile(
             "{\n.reg .pred p;\n"
@@ -146,6 +152,21 @@ __device__ __forceinline__ void store_acc_segment(const uint32_t (&r)[32], int r
     }
 }
 
+// Progress of the two single-thread roles, kept in shared memory so that a CTA that gives up can tell which
+// stages still have bulk copies in flight.
+struct RoleProgress {
+    int issued;    // stages the producer has armed and issued loads for
+    int consumed;  // stages whose full barrier the MMA issuer has seen flip
+    int failed;    // some wait of this CTA ran out
+};
+
+// Teardown after a wait ran out (called by one thread, after the block-wide barrier that follows the role
+// loops): every stage that was armed but never consumed may still be the target of a bulk copy, and the CTA
+// must not retire while one can land in its shared memory, so wait (bounded again) for those barriers.
+__device__ __forceinline__ void drain_stages(const RoleProgress* pr, uint64_t* full, int stages, uint32_t limit) {
+    for (int it = pr->consumed; it < pr->issued; ++it) mbar_wait(full + it % stages, (uint32_t)((it / stages) & 1), limit);
+}
+
 constexpr int kGemmStages = 3;
 constexpr int kGemmBM = 128;
 constexpr int kGemmBK = 64;  // bf16 elements: one 128-byte swizzle row
@@ -184,12 +205,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     uint64_t* full = bars;                   // [stages] TMA -> MMA
     uint64_t* empty = bars + kStages;        // [stages] MMA -> TMA
     uint64_t* acc_ready = bars + 2 * kStages;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kStages + 1);
+    uint64_t* drained = bars + 2 * kStages + 1;  // teardown only: the MMAs issued before giving up have finished
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kStages + 2);
+    RoleProgress* progress = (RoleProgress*)(tmem_slot + 1);
     constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;  // power of two >= 32
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * kGemmBM, n0 = blockIdx.y * BN;
     const int total = k_blocks;
+    const uint32_t limit = d_poll_limit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -197,6 +221,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             mbar_init(empty + s, 1);
         }
         mbar_init(acc_ready, 1);
+        mbar_init(drained, 1);
+        progress->issued = progress->consumed = progress->failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -213,9 +239,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     bool ok = true;
     if (warp == 0 && lane == 0) {
         // ---- TMA producer: one K block per stage, all operand planes of it
-        for (int it = 0; it < total && ok; ++it) {
+        const int stop = d_withhold_from >= 0 ? min(total, d_withhold_from) : total;
+        int it = 0;
+        for (; it < stop && ok; ++it) {
             const int s = it % kStages, round = it / kStages;
-            if (round > 0) ok = mbar_wait(empty + s, (round - 1) & 1);
+            if (round > 0) ok = mbar_wait(empty + s, (round - 1) & 1, limit);
             if (!ok) break;
             uint8_t* st = smem + s * SM::kStage;
             mbar_expect_tx(full + s, SM::kStage);
@@ -226,13 +254,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                 tma_load_2d(st + 2 * SM::kA + SM::kB, &map_b_lo, full + s, it * kGemmBK, n0);
             }
         }
+        progress->issued = it;
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer.  Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major.
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                    ((uint32_t)(kGemmBM >> 4) << 24);
-        for (int it = 0; it < total && ok; ++it) {
+        int it = 0;
+        for (; it < total && ok; ++it) {
             const int s = it % kStages, round = it / kStages;
-            ok = mbar_wait(full + s, round & 1);
+            ok = mbar_wait(full + s, round & 1, limit);
             if (!ok) break;
             tc_fence_after();
             const uint32_t st = smem_u32(smem + s * SM::kStage);
@@ -250,14 +280,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             }
             tc_commit(empty + s);  // arrives once the MMAs above have finished reading the stage
         }
-        if (ok) tc_commit(acc_ready);
+        progress->consumed = it;
+        if (ok) {
+            tc_commit(acc_ready);
+        } else {
+            // giving up: tensor memory may only be released once the MMAs already issued have finished
+            tc_commit(drained);
+            mbar_wait(drained, 0, limit);
+        }
     }
-    if (!ok) atomicExch(status, 1);
+    if (!ok) {
+        atomicExch(status, 1);
+        progress->failed = 1;
+    }
 
     // ---- epilogue: all four warps; warp w owns accumulator lanes [32w, 32w + 32).
     __syncwarp();
-    bool ready = mbar_wait(acc_ready, 0);
-    if (!ready && lane == 0) atomicExch(status, 2);
+    // one decision per warp: the tcgen05.ld below is a warp-wide (.sync.aligned) instruction
+    const bool ready = __all_sync(kFullMask, mbar_wait(acc_ready, 0, limit));
+    if (!ready && lane == 0) {
+        atomicExch(status, 2);
+        progress->failed = 1;
+    }
     tc_fence_after();
     if (ready) {
         const int row = m0 + warp * 32 + lane;
@@ -269,6 +313,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         }
     }
     tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && progress->failed) drain_stages(progress, full, kStages, limit);
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -301,11 +347,14 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
     uint64_t* empty = bars + kStages;            // [stages] MMA -> TMA
     uint64_t* acc_full = bars + 2 * kStages;     // [2] MMA -> epilogue
     uint64_t* acc_empty = bars + 2 * kStages + 2;  // [2] epilogue (4 warps) -> MMA
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kStages + 4);
+    uint64_t* drained = bars + 2 * kStages + 4;  // teardown only: the MMAs issued before giving up have finished
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kStages + 5);
+    RoleProgress* progress = (RoleProgress*)(tmem_slot + 1);
     constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;
     constexpr uint32_t kTmemCols = 2 * kAccCols;  // a power of two in [64, 512]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t limit = d_poll_limit;
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full + s, 1);
@@ -315,6 +364,8 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
             mbar_init(acc_full + a, 1);
             mbar_init(acc_empty + a, 4);
         }
+        mbar_init(drained, 1);
+        progress->issued = progress->consumed = progress->failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -331,11 +382,16 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
     bool ok = true;
     if (warp == 0 && lane == 0) {
         int it = 0;
+        const int withhold = d_withhold_from;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             const int m0 = (tile / n_tiles) * kGemmBM, n0 = (tile % n_tiles) * BN;
             for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                if (withhold >= 0 && it >= withhold) {  // test hook: nothing more is issued
+                    ok = false;
+                    break;
+                }
                 const int s = it % kStages, round = it / kStages;
-                if (round > 0) ok = mbar_wait(empty + s, (round - 1) & 1);
+                if (round > 0) ok = mbar_wait(empty + s, (round - 1) & 1, limit);
                 if (!ok) break;
                 uint8_t* st = smem + s * SM::kStage;
                 mbar_expect_tx(full + s, SM::kStage);
@@ -347,7 +403,11 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                 }
             }
         }
-        if (!ok) atomicExch(status, 1);
+        progress->issued = it;
+        if (!ok) {
+            atomicExch(status, 1);
+            progress->failed = 1;
+        }
     } else if (warp == 1 && lane == 0) {
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                    ((uint32_t)(kGemmBM >> 4) << 24);
@@ -355,13 +415,13 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
             const int a = local & 1, use = local >> 1;
             // the first use of an accumulator finds its barrier in the initial phase and passes at once
-            ok = mbar_wait(acc_empty + a, (uint32_t)((use & 1) ^ 1));
+            ok = mbar_wait(acc_empty + a, (uint32_t)((use & 1) ^ 1), limit);
             if (!ok) break;
             tc_fence_after();
             const uint32_t acc = tmem_base + (uint32_t)a * kAccCols;
             for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                 const int s = it % kStages, round = it / kStages;
-                ok = mbar_wait(full + s, round & 1);
+                ok = mbar_wait(full + s, round & 1, limit);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t st = smem_u32(smem + s * SM::kStage);
@@ -380,15 +440,26 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
             }
             if (ok) tc_commit(acc_full + a);
         }
-        if (!ok) atomicExch(status, 1);
+        progress->consumed = it;
+        if (!ok) {
+            atomicExch(status, 1);
+            progress->failed = 1;
+            // tensor memory may only be released once the MMAs already issued have finished
+            tc_commit(drained);
+            mbar_wait(drained, 0, limit);
+        }
     } else if (warp >= 2) {
         const int quarter = warp & 3;
         int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
             const int a = local & 1, use = local >> 1;
             const int m0 = (tile / n_tiles) * kGemmBM, n0 = (tile % n_tiles) * BN;
-            if (!mbar_wait(acc_full + a, (uint32_t)(use & 1))) {
-                if (lane == 0) atomicExch(status, 2);
+            // one decision per warp: the tcgen05.ld below is a warp-wide (.sync.aligned) instruction
+            if (!__all_sync(kFullMask, mbar_wait(acc_full + a, (uint32_t)(use & 1), limit))) {
+                if (lane == 0) {
+                    atomicExch(status, 2);
+                    progress->failed = 1;
+                }
                 break;
             }
             tc_fence_after();
@@ -405,6 +476,8 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
         }
     }
     tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && progress->failed) drain_stages(progress, full, kStages, limit);
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -441,7 +514,9 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
     uint64_t* full = bars;
     uint64_t* empty = bars + kGemmStages;
     uint64_t* acc_ready = bars + 2 * kGemmStages;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kGemmStages + 1);
+    uint64_t* drained = bars + 2 * kGemmStages + 1;  // teardown only: the MMAs issued before giving up have finished
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kGemmStages + 2);
+    RoleProgress* progress = (RoleProgress*)(tmem_slot + 1);
     constexpr uint32_t kTmemCols = BN;
     constexpr int kHalf = 64 * kGemmBK * 2;  // one 64-row x 64-column box: 8 KB
 
@@ -454,6 +529,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
     const int k_blocks = kb_end - kb_begin;
     if (k_blocks <= 0) return;
     const int total = k_blocks * passes;
+    const uint32_t limit = d_poll_limit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
@@ -461,6 +537,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             mbar_init(empty + s, 1);
         }
         mbar_init(acc_ready, 1);
+        mbar_init(drained, 1);
+        progress->issued = progress->consumed = progress->failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -476,9 +554,11 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
 
     bool ok = true;
     if (warp == 0 && lane == 0) {
-        for (int it = 0; it < total && ok; ++it) {
+        const int stop = d_withhold_from >= 0 ? min(total, d_withhold_from) : total;
+        int it = 0;
+        for (; it < stop && ok; ++it) {
             const int s = it % kGemmStages, round = it / kGemmStages;
-            if (round > 0) ok = mbar_wait(empty + s, (round - 1) & 1);
+            if (round > 0) ok = mbar_wait(empty + s, (round - 1) & 1, limit);
             if (!ok) break;
             const int pass = it / k_blocks, kb = kb_begin + (it - pass * k_blocks);
             const CUtensorMap* ma = (pass == 1) ? &map_a_lo : &map_a_hi;
@@ -491,13 +571,15 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             for (int h = 0; h < BN / 64; ++h)
                 tma_load_2d(sa + GemmSmem<BN>::kA + h * kHalf, mb, full + s, n0 + h * 64, kb * 64);
         }
+        progress->issued = it;
     } else if (warp == 1 && lane == 0) {
         // fp32 accumulate, bf16 x bf16, both operands MN-major (bits 15 and 16).
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) |
                                    ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kGemmBM >> 4) << 24);
-        for (int it = 0; it < total && ok; ++it) {
+        int it = 0;
+        for (; it < total && ok; ++it) {
             const int s = it % kGemmStages, round = it / kGemmStages;
-            ok = mbar_wait(full + s, round & 1);
+            ok = mbar_wait(full + s, round & 1, limit);
             if (!ok) break;
             tc_fence_after();
             const uint32_t sa = smem_u32(smem + s * GemmSmem<BN>::kStage);
@@ -509,13 +591,27 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             }
             tc_commit(empty + s);
         }
-        if (ok) tc_commit(acc_ready);
+        progress->consumed = it;
+        if (ok) {
+            tc_commit(acc_ready);
+        } else {
+            // giving up: tensor memory may only be released once the MMAs already issued have finished
+            tc_commit(drained);
+            mbar_wait(drained, 0, limit);
+        }
     }
-    if (!ok) atomicExch(status, 3);
+    if (!ok) {
+        atomicExch(status, 3);
+        progress->failed = 1;
+    }
 
     __syncwarp();
-    bool ready = mbar_wait(acc_ready, 0);
-    if (!ready && lane == 0) atomicExch(status, 4);
+    // one decision per warp: the tcgen05.ld below is a warp-wide (.sync.aligned) instruction
+    const bool ready = __all_sync(kFullMask, mbar_wait(acc_ready, 0, limit));
+    if (!ready && lane == 0) {
+        atomicExch(status, 4);
+        progress->failed = 1;
+    }
     tc_fence_after();
     if (ready) {
         const int row = i0 + warp * 32 + lane;
@@ -532,6 +628,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
         }
     }
     tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && progress->failed) drain_stages(progress, full, kGemmStages, limit);
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -752,6 +850,14 @@ int split_bf16_transpose(int rows, int cols, const float* src, int64_t ld_src, i
 using namespace pccnn;
 
 extern "C" {
+
+int pccnn_gemm_set_test_hooks(int poll_limit, int withhold_from) {
+    const uint32_t limit = poll_limit > 0 ? (uint32_t)poll_limit : (1u << 21);
+    const int withhold = withhold_from >= 0 ? withhold_from : -1;
+    PCCNN_CUDA(cudaMemcpyToSymbol(d_poll_limit, &limit, sizeof(limit)));
+    PCCNN_CUDA(cudaMemcpyToSymbol(d_withhold_from, &withhold, sizeof(withhold)));
+    return PCCNN_OK;
+}
 
 size_t pccnn_gemm_workspace_bytes(int64_t M, int N, int K) {
     const int64_t kp = (K + 63) / 64 * 64;

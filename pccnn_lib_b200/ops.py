@@ -8,6 +8,7 @@ there is no CPU path.
 """
 import contextlib
 import ctypes
+import os
 
 import torch
 
@@ -56,6 +57,37 @@ def _dims(pts, name="pts"):
     if d < 2 or d > 6:
         raise RuntimeError("%s has %d dimensions; supported range is [2, 6]" % (name, d))
     return d
+
+
+# ---- failure reporting and input validation -----------------------------------------------------
+def check_status(synchronize=True):
+    """Raises RuntimeError if a tensor-core kernel of an earlier convolution call gave up on one of its bounded
+    waits (its outputs are then incomplete).  With `synchronize` the current stream is waited for first, so
+    nothing enqueued so far can be missed; without it only failures that already reached the host are seen.
+    The convolution operators make the cheap check themselves at every call, so a failure surfaces at the next
+    convolution at the latest.  No counterpart in the reference, which checks nothing."""
+    _capi.check(_lib.pccnn_check_status(1 if synchronize else 0, _stream()), "check_status")
+
+
+def validate_neighbors(neighbors, start_ids, num_pts):
+    """Checks a neighbor list on the device (indices in range, rows grouped by sample, end offsets monotone and
+    ending at T) and raises RuntimeError naming the first bad row instead of letting a later kernel read out of
+    bounds.  Synchronises.  Runs automatically in front of every operator that takes a list when the environment
+    variable PCCNN_VALIDATE_NEIGHBORS is set to 1."""
+    neighbors = _need(neighbors, "neighbors", torch.int32, 2)
+    start_ids = _need(start_ids, "start_ids", torch.int32, 1)
+    if neighbors.shape[1] != 2:
+        raise RuntimeError("neighbors must be [T, 2]")
+    with _on(start_ids.device):
+        ws = _workspace(_lib.pccnn_validate_neighbors_workspace_bytes(), start_ids.device)
+        _capi.check(_lib.pccnn_validate_neighbors(int(num_pts), start_ids.shape[0], _p(neighbors), _p(start_ids),
+                                                  neighbors.shape[0], ws.data_ptr(), ws.numel(), _stream()),
+                    "validate_neighbors")
+
+
+def _maybe_validate(neighbors, start_ids, num_pts):
+    if os.environ.get("PCCNN_VALIDATE_NEIGHBORS", "0") == "1":
+        validate_neighbors(neighbors, start_ids, num_pts)
 
 
 # ---- grid front end --------------------------------------------------------------------------
@@ -267,6 +299,7 @@ def _pdf_args(bandwidth, pts, neighbors, start_ids):
         raise RuntimeError("start_ids must have one entry per point")
     if neighbors.shape[1] != 2:
         raise RuntimeError("neighbors must be [T, 2]")
+    _maybe_validate(neighbors, start_ids, pts.shape[0])
     return bandwidth, pts, neighbors, start_ids, d
 
 
@@ -304,6 +337,9 @@ def poisson_disk_sampling(sorted_keys, neighbors, start_ids, grid_size):
     grid_size = _need(grid_size, "grid_size", torch.int32, 1)
     n = sorted_keys.shape[0]
     d = grid_size.numel()
+    if start_ids.shape[0] != n:
+        raise RuntimeError("start_ids must have one entry per point")
+    _maybe_validate(neighbors, start_ids, n)
     selected = torch.empty((n,), dtype=torch.int64, device=sorted_keys.device)
     count = ctypes.c_int64(0)
     with _on(sorted_keys.device):
@@ -374,6 +410,9 @@ def _conv_common(pts, feats, samples, neighbors, start_ids, radii, feat_dtype=to
         raise RuntimeError("features need one row per point")
     if start_ids.shape[0] != samples.shape[0]:
         raise RuntimeError("start_ids needs one entry per sample")
+    if neighbors.shape[1] != 2:
+        raise RuntimeError("neighbors must be [T, 2]")
+    _maybe_validate(neighbors, start_ids, pts.shape[0])
     return pts, feats, samples, neighbors, start_ids, radii, d
 
 

@@ -10,6 +10,9 @@ if ROOT not in sys.path:
 
 GOLDEN = os.path.join(ROOT, "tests", "golden")
 
+# Every operator that takes a neighbor list checks it first in the tests (pccnn_lib_b200.ops.validate_neighbors).
+os.environ.setdefault("PCCNN_VALIDATE_NEIGHBORS", "1")
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")

@@ -90,6 +90,26 @@ def test_mcconv_grads(ref_clouds, c):
         assert grads_close(a.cpu().numpy(), b.numpy().reshape(a.shape)), name
 
 
+@pytest.mark.parametrize("num_mlps,cout", [(2, 64), (4, 64), (2, 16), (4, 96)])
+def test_mcconv_with_several_mlps_forward_and_grads(ref_clouds, num_mlps, cout):
+    # per-MLP slices of the projected operand, of the weights and of the upstream gradient, including output
+    # slices narrower than one 64-column tensor-core tile (e.g. MCConv(cin=32, cout=64, hidden=16, mlps=4))
+    from pccnn_lib_b200 import ops
+    c = dict(MC_CASES[0], cout=cout)
+    case = mc_case(ref_clouds, c, normal_feats=True, num_mlps=num_mlps)
+    a = [dev(case[k]) for k in ("pts", "pdf", "feats", "samples", "neighbors", "start_ids", "radii", "axis", "bias",
+                                "weights")]
+    h = [case[k] for k in ("pts", "pdf", "feats", "samples", "neighbors", "start_ids", "radii", "axis", "bias", "weights")]
+    got = ops.mc_conv(*a).cpu().numpy()
+    expect = conv_oracle.mc_conv(*h).numpy()
+    scale = max(1.0, float(np.abs(expect).max()))
+    assert close(got / scale, expect / scale)
+    g = np.random.RandomState(11).normal(size=(case["samples"].shape[0], cout)).astype(np.float32)
+    for name, x, y in zip(["weights", "features", "axis", "bias", "pdf", "pts", "samples"],
+                          ops.mc_conv_grads(*a, dev(g)), conv_oracle.mc_conv_grads(*h, g)):
+        assert grads_close(x.cpu().numpy(), y.numpy().reshape(x.shape)), name
+
+
 def test_layers_run_end_to_end_with_autograd(ref_clouds):
     # The mirrored classes: Pointcloud -> compute_pdf -> MCConv / KPConv -> backward through the op wrappers.
     import pccnn_lib_b200 as lib

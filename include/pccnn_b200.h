@@ -316,6 +316,12 @@ int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, co
  * (shared/mlp_basis.cu:50-96); outputs: weights (shape of the weights), features, axis [D, hidden],
  * bias [hidden], pdf [num_pts], points, samples. */
 size_t pccnn_conv_grads_workspace_bytes(int64_t num_samples, int cin, int basis_size, int cout);
+/* Data parallelism (no counterpart in the reference, which is single-process): `event` (a cudaEvent_t) is recorded
+ * on the stream of the NEXT pccnn_kp_conv_grads / pccnn_mc_conv_grads call of this thread at the point where
+ * out_weight_grads is final, i.e. before the last per-pair kernel of the call; a communication stream that waits
+ * for it can sum the weight gradient over the ranks while the feature / point gradients are still computed.
+ * One shot: the call consumes it.  NULL cancels. */
+int pccnn_conv_grads_set_weight_grads_event(void* event);
 int pccnn_kp_conv_grads(int D, int64_t num_pts, const float* pts, const float* feats, int cin,
                         int64_t num_samples, const float* samples, const int32_t* neighbors,
                         const int32_t* start_ids, const float* radii, const float* kernel_pts,

@@ -57,6 +57,7 @@ SIGNATURES = {
     "pccnn_mc_conv": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                                _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
     "pccnn_conv_grads_workspace_bytes": (_size, [_c_i64, _c_int, _c_int, _c_int]),
+    "pccnn_conv_grads_set_weight_grads_event": (_c_int, [_ptr]),
     "pccnn_kp_conv_grads": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
                                      ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _size,
                                      _ptr]),

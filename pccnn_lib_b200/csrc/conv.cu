@@ -690,10 +690,10 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
     PCCNN_CHECK_ARG(cin >= 1 && cout >= 1 && num_mlps >= 1 && cout % num_mlps == 0 && (cin * K) % num_mlps == 0,
                     "%s: bad channel counts (cin %d, cout %d, mlps %d)", who, cin, cout, num_mlps);
     PCCNN_CHECK_ARG(num_samples >= 0 && num_samples < 0x7fffffffLL && num_pts >= 0, "%s: bad sizes", who);
-    // Several MLPs: MLP j reads the j-th slice of the P rows and writes the j-th slice of the outputs; the
+    // Several MLPs: MLP j reads the j-th slice of the P rows and writes the j-th slice of the outputs; the P
     // slices are TMA operands of their own, so they must start on 16-byte boundaries (8 bf16 values).
-    PCCNN_CHECK_ARG(num_mlps == 1 || ((cin * K / num_mlps) % 8 == 0 && (cout / num_mlps) % 8 == 0),
-                    "%s: with several MLPs, Cin*K per MLP and Cout per MLP must be multiples of 8", who);
+    PCCNN_CHECK_ARG(num_mlps == 1 || (cin * K / num_mlps) % 8 == 0,
+                    "%s: with several MLPs, Cin*K per MLP must be a multiple of 8", who);
     if (num_samples == 0) return PCCNN_OK;
     PCCNN_CHECK_ARG(pts && feats && samples && start_ids && radii && weights && out, "%s: null pointer", who);
     const ConvLayout L = conv_layout(num_samples, cin, K, cout);
@@ -741,7 +741,8 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
             const size_t a_off = (size_t)j * inner_j * 2;
             const size_t b_off = (size_t)j * cout_j * L.ld_p * 2;
             const int kp = num_mlps == 1 ? L.ld_p : (inner_j + 63) / 64 * 64;
-            GemmOperand a{ws + L.p_hi_off + a_off, io_bf16 ? nullptr : ws + L.p_lo_off + a_off, L.ld_p};
+            GemmOperand a{ws + L.p_hi_off + a_off, io_bf16 ? nullptr : ws + L.p_lo_off + a_off, L.ld_p,
+                          L.ld_p - (int64_t)j * inner_j};
             GemmOperand b{ws + L.w_hi_off + b_off, io_bf16 ? nullptr : ws + L.w_lo_off + b_off, L.ld_p};
             float* c_ptr = io_bf16 ? (float*)((__nv_bfloat16*)out_any + (size_t)m0 * cout + (size_t)j * cout_j)
                                    : out + (size_t)m0 * cout + (size_t)j * cout_j;
@@ -779,6 +780,11 @@ static ConvBackwardLayout conv_backward_layout(int64_t num_samples, int cin, int
     return L;
 }
 
+// Event that the next conv_backward of this thread records on its stream as soon as the weight gradient is
+// complete (after the last chunk's dW contraction, before that chunk's per-pair kernel), so that a caller can start
+// the allreduce of dW on another stream while the rest of the backward pass still runs.  One shot.
+static thread_local cudaEvent_t g_weight_grads_event = nullptr;
+
 // Backward of conv_forward.  Per chunk of samples: recompute P, dW += P^T g and dP = g W^T on the
 // tensor cores, then the per-pair kernel.  All outputs are zeroed here and accumulated into.
 template <class ARGS, template <int, int> class BASIS>
@@ -797,7 +803,8 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
     PCCNN_CHECK_ARG(d_weights && d_feat && d_param0 && d_pts && d_samples, "%s: null output", who);
     const int inner = cin * K, inner_j = inner / num_mlps, cout_j = cout / num_mlps;
     PCCNN_CHECK_ARG(num_mlps == 1 || (inner_j % 8 == 0 && cout_j % 8 == 0),
-                    "%s: with several MLPs, Cin*K per MLP and Cout per MLP must be multiples of 8", who);
+                    "%s: with several MLPs, Cin*K per MLP and Cout per MLP must be multiples of 8 (the slices of the "
+                    "projected operand and of the upstream gradient are tensor-core operands of their own)", who);
     PCCNN_CUDA(cudaMemsetAsync(d_weights, 0, (size_t)inner * cout_j * 4, s));
     PCCNN_CUDA(cudaMemsetAsync(d_feat, 0, (size_t)num_pts * cin * 4, s));
     PCCNN_CUDA(cudaMemsetAsync(d_param0, 0, param0_floats * 4, s));
@@ -815,6 +822,8 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
     char* ws = (char*)workspace;
     int* status = (int*)(ws + L.status_off);
     PCCNN_CUDA(cudaMemsetAsync(status, 0, 4, s));
+    const cudaEvent_t weight_grads_event = g_weight_grads_event;
+    g_weight_grads_event = nullptr;
     // W_j as bf16 hi/lo rows [inner_j, ld_g] (reduction index of dP = g W^T is the output channel).
     for (int j = 0; j < num_mlps; ++j) {
         const size_t off = (size_t)j * inner_j * L.ld_g * 2;
@@ -834,8 +843,10 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
         if ((rc = split_bf16(rows, cout, in_grads + (size_t)m0 * cout, cout, L.ld_g, ws + L.g_hi_off, ws + L.g_lo_off, s)))
             return rc;
         for (int j = 0; j < num_mlps; ++j) {
-            GemmOperand p{ws + L.p_hi_off + (size_t)j * inner_j * 2, ws + L.p_lo_off + (size_t)j * inner_j * 2, L.ld_p};
-            GemmOperand g{ws + L.g_hi_off + (size_t)j * cout_j * 2, ws + L.g_lo_off + (size_t)j * cout_j * 2, L.ld_g};
+            GemmOperand p{ws + L.p_hi_off + (size_t)j * inner_j * 2, ws + L.p_lo_off + (size_t)j * inner_j * 2, L.ld_p,
+                          L.ld_p - (int64_t)j * inner_j};
+            GemmOperand g{ws + L.g_hi_off + (size_t)j * cout_j * 2, ws + L.g_lo_off + (size_t)j * cout_j * 2, L.ld_g,
+                          L.ld_g - (int64_t)j * cout_j};
             GemmOperand w{ws + L.w_hi_off + (size_t)j * inner_j * L.ld_g * 2,
                           ws + L.w_lo_off + (size_t)j * inner_j * L.ld_g * 2, L.ld_g};
             // dW_j += P_j^T g_j
@@ -845,6 +856,8 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
             // dP_j = g_j W_j^T  ->  columns [j * inner_j, (j + 1) * inner_j) of the dP rows
             // (reduction over the MLP's outputs rounded up to 64: the surplus columns of g meet zero weights)
             const int kp = num_mlps == 1 ? L.ld_g : (cout_j + 63) / 64 * 64;
+            if (j == num_mlps - 1 && m1 == num_samples && weight_grads_event)
+                PCCNN_CUDA(cudaEventRecord(weight_grads_event, s));  // dW is final from here on
             if ((rc = gemm_bf16_nt(g, w, d_proj + (size_t)j * inner_j, rows, inner_j, kp, inner, status, s))) return rc;
         }
         PCCNN_DISPATCH_DIM(D, (rc = launch_backward_pairs<DIM, ARGS, BASIS>(
@@ -897,6 +910,11 @@ int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, co
     return conv_forward<MLPBasisArgs, MLPBasis>("mc_conv", D, hidden, args, num_pts, pts, feats, cin, num_samples,
                                                 samples, neighbors, start_ids, radii, num_mlps, weights, cout, out,
                                                 workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int pccnn_conv_grads_set_weight_grads_event(void* event) {
+    g_weight_grads_event = (cudaEvent_t)event;
+    return PCCNN_OK;
 }
 
 size_t pccnn_conv_grads_workspace_bytes(int64_t num_samples, int cin, int basis_size, int cout) {

@@ -700,7 +700,7 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 // 2-D bf16 tensor [rows, ld] (ld elements per row, K contiguous), box = box_rows x 64, 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t ld, int box_rows) {
+static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t ld, int box_rows, int64_t cols = 0) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) {
         set_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -710,7 +710,7 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t ld
         set_error("gemm operand must be 16-byte aligned with rows padded to 64 elements (ld = %lld)", (long long)ld);
         return PCCNN_ERR_INVALID;
     }
-    cuuint64_t dims[2] = {(cuuint64_t)ld, (cuuint64_t)(rows > 0 ? rows : 1)};
+    cuuint64_t dims[2] = {(cuuint64_t)(cols > 0 && cols < ld ? cols : ld), (cuuint64_t)(rows > 0 ? rows : 1)};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
@@ -759,10 +759,10 @@ static int launch_gemm(const GemmOperand& a, const GemmOperand& b, float* C, int
                        int c_is_bf16, int* status, cudaStream_t s) {
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     const bool split = a.lo && b.lo;
-    if (int rc = make_map(&ma_hi, a.hi, M, a.ld, kGemmBM)) return rc;
-    if (int rc = make_map(&ma_lo, split ? a.lo : a.hi, M, a.ld, kGemmBM)) return rc;
-    if (int rc = make_map(&mb_hi, b.hi, N, b.ld, BN)) return rc;
-    if (int rc = make_map(&mb_lo, split ? b.lo : b.hi, N, b.ld, BN)) return rc;
+    if (int rc = make_map(&ma_hi, a.hi, M, a.ld, kGemmBM, a.cols)) return rc;
+    if (int rc = make_map(&ma_lo, split ? a.lo : a.hi, M, a.ld, kGemmBM, a.cols)) return rc;
+    if (int rc = make_map(&mb_hi, b.hi, N, b.ld, BN, b.cols)) return rc;
+    if (int rc = make_map(&mb_lo, split ? b.lo : b.hi, N, b.ld, BN, b.cols)) return rc;
     if (split) return launch_gemm_impl<BN, true>(ma_hi, ma_lo, mb_hi, mb_lo, C, M, N, K_padded, ldc, c_is_bf16, status, s);
     return launch_gemm_impl<BN, false>(ma_hi, ma_lo, mb_hi, mb_lo, C, M, N, K_padded, ldc, c_is_bf16, status, s);
 }
@@ -785,10 +785,10 @@ static int launch_gemm_tn(const GemmOperand& a, const GemmOperand& b, float* C, 
                           int* status, cudaStream_t s) {
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     const int passes = (a.lo && b.lo) ? 3 : 1;
-    if (int rc = make_map(&ma_hi, a.hi, rows, a.ld, 64)) return rc;
-    if (int rc = make_map(&ma_lo, passes == 3 ? a.lo : a.hi, rows, a.ld, 64)) return rc;
-    if (int rc = make_map(&mb_hi, b.hi, rows, b.ld, 64)) return rc;
-    if (int rc = make_map(&mb_lo, passes == 3 ? b.lo : b.hi, rows, b.ld, 64)) return rc;
+    if (int rc = make_map(&ma_hi, a.hi, rows, a.ld, 64, a.cols)) return rc;
+    if (int rc = make_map(&ma_lo, passes == 3 ? a.lo : a.hi, rows, a.ld, 64, a.cols)) return rc;
+    if (int rc = make_map(&mb_hi, b.hi, rows, b.ld, 64, b.cols)) return rc;
+    if (int rc = make_map(&mb_lo, passes == 3 ? b.lo : b.hi, rows, b.ld, 64, b.cols)) return rc;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {

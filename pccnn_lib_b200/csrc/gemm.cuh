@@ -12,6 +12,10 @@ struct GemmOperand {
     void* hi;
     void* lo;  // null: single bf16 pass
     int64_t ld;
+    // Columns that exist from `hi` / `lo` to the end of the row (0: all `ld` of them).  An operand that is a column
+    // slice of a wider matrix starts inside a row; what a tile reads past the end of that row is filled with zeros
+    // by the TMA unit instead of running into the next row.
+    int64_t cols = 0;
 };
 
 // C[M, N] (fp32, row stride ldc) = A[M, K] * B[N, K]^T.  Three passes when both operands carry a

@@ -521,8 +521,18 @@ def gemm_tn_f32(a, b, split=True):
     return out
 
 
-def kp_conv_grads(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights, in_grads):
-    """[dW, dFeat, dKernelPts, dPts, dSamples]; kpconv_grads() of pccnn_lib_ops/pcconvs/kpconv.cu:63-112."""
+def _arm_weight_grads_event(event):
+    if event is not None:
+        if not event.cuda_event:
+            event.record()  # torch creates the underlying CUDA event at its first record
+        _capi.check(_lib.pccnn_conv_grads_set_weight_grads_event(event.cuda_event), "set_weight_grads_event")
+
+
+def kp_conv_grads(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights, in_grads,
+                  weight_grads_event=None):
+    """[dW, dFeat, dKernelPts, dPts, dSamples]; kpconv_grads() of pccnn_lib_ops/pcconvs/kpconv.cu:63-112.
+    `weight_grads_event` (an extension for data parallelism): a torch.cuda.Event that is recorded on the current
+    stream as soon as dW is final, before the rest of the backward pass has run."""
     pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii)
     kernel_pts = _need(kernel_pts, "kernel_pts", torch.float32, 2)
     weights = _need(weights, "weights", torch.float32, 2)
@@ -536,6 +546,7 @@ def kp_conv_grads(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, 
     d_k, d_p, d_s = torch.empty_like(kernel_pts), torch.empty_like(pts), torch.empty_like(samples)
     with _on(dev):
         ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, k, cout), dev)
+        _arm_weight_grads_event(weight_grads_event)
         _capi.check(_lib.pccnn_kp_conv_grads(d, n, _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
                                              _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights),
                                              cout, _p(in_grads), d_w.data_ptr(), d_f.data_ptr(), d_k.data_ptr(),
@@ -544,8 +555,10 @@ def kp_conv_grads(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, 
     return [d_w, d_f, d_k, d_p, d_s]
 
 
-def mc_conv_grads(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_proj, axis_bias, weights, in_grads):
-    """[dW, dFeat, dAxis, dBias, dPdf, dPts, dSamples]; mcconv_grads() of pccnn_lib_ops/pcconvs/mcconv.cu:73-143."""
+def mc_conv_grads(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_proj, axis_bias, weights, in_grads,
+                  weight_grads_event=None):
+    """[dW, dFeat, dAxis, dBias, dPdf, dPts, dSamples]; mcconv_grads() of pccnn_lib_ops/pcconvs/mcconv.cu:73-143.
+    `weight_grads_event`: as for kp_conv_grads."""
     pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii)
     pdf = _need(pdf, "pdf", torch.float32, 1)
     axis_proj = _need(axis_proj, "axis_proj", torch.float32, 2)
@@ -563,6 +576,7 @@ def mc_conv_grads(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_pr
     d_p, d_s = torch.empty_like(pts), torch.empty_like(samples)
     with _on(dev):
         ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, hidden, cout), dev)
+        _arm_weight_grads_event(weight_grads_event)
         _capi.check(_lib.pccnn_mc_conv_grads(d, n, _p(pts), _p(pdf), _p(feats), cin, m, _p(samples), _p(neighbors),
                                              _p(start_ids), _p(radii), _p(axis_proj), _p(axis_bias), hidden, n_mlps,
                                              _p(weights), cout, _p(in_grads), d_w.data_ptr(), d_f.data_ptr(),

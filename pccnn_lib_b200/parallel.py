@@ -32,6 +32,22 @@ def shard_clouds(points_per_cloud, world_size, rank):
     return bounds[rank], bounds[rank + 1]
 
 
+def assign_clouds(weights, world_size):
+    """Clouds to ranks by estimated work, without the contiguity of shard_clouds: heaviest cloud first, each to
+    the rank with the least work so far (longest-processing-time rule), which keeps one unusually dense cloud
+    from dragging its neighbors in id order onto the same rank.  Returns one ascending list of cloud ids per
+    rank; deterministic (ties go to the lower rank and the lower cloud id), so every rank computes the same plan.
+    """
+    order = sorted(range(len(weights)), key=lambda c: (-float(weights[c]), c))
+    loads = [0.0] * world_size
+    plan = [[] for _ in range(world_size)]
+    for c in order:
+        r = min(range(world_size), key=lambda i: (loads[i], i))
+        plan[r].append(c)
+        loads[r] += float(weights[c])
+    return [sorted(p) for p in plan]
+
+
 def rebase_batch_ids(batch_ids, first_cloud):
     """Batch ids of a shard renumbered from zero (each rank builds its own grid)."""
     return batch_ids - first_cloud

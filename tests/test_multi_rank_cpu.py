@@ -26,6 +26,17 @@ def test_shards_cover_every_cloud_once_and_balance_points():
     assert max(loads) <= 2.0 * sum(ragged) / 3
 
 
+def test_work_balanced_assignment_covers_every_cloud_once():
+    weights = [48.0] * 15 + [420.0] + [30.0] * 16  # one cloud with nine times the work of the others
+    for world in (1, 2, 4, 8):
+        plan = parallel.assign_clouds(weights, world)
+        assert sorted(c for p in plan for c in p) == list(range(len(weights)))
+        loads = [sum(weights[c] for c in p) for p in plan]
+        # no rank exceeds the larger of the mean load (+ one light cloud) and the heaviest single cloud
+        assert max(loads) <= max(sum(weights) / world + 48.0, 420.0)
+    assert parallel.assign_clouds(weights, 4) == parallel.assign_clouds(list(weights), 4)  # deterministic
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -338,6 +338,120 @@ int pccnn_mc_conv_grads(int D, int64_t num_pts, const float* pts, const float* p
                         float* out_sample_grads, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------- */
+/* Weight variance (variance-aware initialisation)                            */
+/* ------------------------------------------------------------------------- */
+
+/* out_variance[0] (device float) = 1 / mean_m( sum_{i, j in seg(m)} (b_i . b_j) (f_i . f_j) ), the quantity the
+ * layers of the reference accumulate during their warm-up passes to scale their weight initialisation
+ * (pccnn_lib/pc/layers/KPConv.py:103-116, MCConv.py:97-110).  The double sum over the neighbors of a sample is
+ * the squared norm of the sample's projected features, so it is computed in O(n) per sample, not O(n^2).
+ * Replace kpconv_compute_weight_variance()  pccnn_lib_ops/pcconvs/kpconv.cu:115-135 and
+ * mcconv_compute_weight_variance()  mcconv.cu:146-171 (kernel shared/compute_variance_weights.cu:24-170).
+ * Scratch: pccnn_conv_weight_var_workspace_bytes(num_samples, cin, basis_size).  num_samples >= 1. */
+size_t pccnn_conv_weight_var_workspace_bytes(int64_t num_samples, int cin, int basis_size);
+int pccnn_kp_conv_weight_var(int D, int64_t num_pts, const float* pts, const float* feats, int cin, int64_t num_samples,
+                             const float* samples, const int32_t* neighbors, const int32_t* start_ids, const float* radii,
+                             const float* kernel_pts, int num_kernel_pts, float sigma, float* out_variance,
+                             void* workspace, size_t workspace_bytes, void* stream);
+int pccnn_mc_conv_weight_var(int D, int64_t num_pts, const float* pts, const float* pdf, const float* feats, int cin,
+                             int64_t num_samples, const float* samples, const int32_t* neighbors, const int32_t* start_ids,
+                             const float* radii, const float* axis, const float* bias, int hidden, float* out_variance,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* The other convolutions of the reference                                    */
+/* ------------------------------------------------------------------------- */
+
+/* Same projection + tensor-core contraction as KPConv with another basis; workspaces from
+ * pccnn_conv_workspace_bytes / pccnn_conv_grads_workspace_bytes / pccnn_conv_weight_var_workspace_bytes with
+ * basis_size = the number of basis functions.  Weights [basis_size * cin, cout], row index c * basis_size + k.
+ *
+ * KPConvN: b[t, k] = clamp(1 - |kp_k - d_t| / sigma, 0, 1) / pdf[n0(t)].  Replaces kpconvn(), kpconvn_grads(),
+ * kpconvn_compute_weight_variance()  pccnn_lib_ops/pcconvs/kpconvn.cu:32-155.  Gradient outputs: weights, features,
+ * kernel points [K, D], points, samples (the reference returns no density gradient). */
+int pccnn_kp_conv_n(int D, int64_t num_pts, const float* pts, const float* pdf, const float* feats, int cin,
+                    int64_t num_samples, const float* samples, const int32_t* neighbors, const int32_t* start_ids,
+                    const float* radii, const float* kernel_pts, int num_kernel_pts, float sigma, const float* weights,
+                    int cout, float* out, void* workspace, size_t workspace_bytes, void* stream);
+int pccnn_kp_conv_n_grads(int D, int64_t num_pts, const float* pts, const float* pdf, const float* feats, int cin,
+                          int64_t num_samples, const float* samples, const int32_t* neighbors, const int32_t* start_ids,
+                          const float* radii, const float* kernel_pts, int num_kernel_pts, float sigma,
+                          const float* weights, int cout, const float* in_grads, float* out_weight_grads,
+                          float* out_feat_grads, float* out_kernel_pt_grads, float* out_pt_grads, float* out_sample_grads,
+                          void* workspace, size_t workspace_bytes, void* stream);
+int pccnn_kp_conv_n_weight_var(int D, int64_t num_pts, const float* pts, const float* pdf, const float* feats, int cin,
+                               int64_t num_samples, const float* samples, const int32_t* neighbors,
+                               const int32_t* start_ids, const float* radii, const float* kernel_pts, int num_kernel_pts,
+                               float sigma, float* out_variance, void* workspace, size_t workspace_bytes, void* stream);
+
+/* PCCNN: b[t, k] = exp(-|kp_k - d_t|^2 / (2 sigma^2)) / pdf[n0(t)].  Replaces pccnn(), pccnn_grads(),
+ * pccnn_compute_weight_variance()  pccnn_lib_ops/pcconvs/pccnn.cu:32-165 (basis shared/kernel_pts_basis.cu:72-111).
+ * Argument order as there (features before the density).  Gradient outputs: weights, features, kernel points,
+ * density [num_pts], points, samples. */
+int pccnn_pccnn_conv(int D, int64_t num_pts, const float* pts, const float* feats, int cin, const float* pdf,
+                     int64_t num_samples, const float* samples, const int32_t* neighbors, const int32_t* start_ids,
+                     const float* radii, const float* kernel_pts, int num_kernel_pts, float sigma, const float* weights,
+                     int cout, float* out, void* workspace, size_t workspace_bytes, void* stream);
+int pccnn_pccnn_conv_grads(int D, int64_t num_pts, const float* pts, const float* feats, int cin, const float* pdf,
+                           int64_t num_samples, const float* samples, const int32_t* neighbors, const int32_t* start_ids,
+                           const float* radii, const float* kernel_pts, int num_kernel_pts, float sigma,
+                           const float* weights, int cout, const float* in_grads, float* out_weight_grads,
+                           float* out_feat_grads, float* out_kernel_pt_grads, float* out_pdf_grads, float* out_pt_grads,
+                           float* out_sample_grads, void* workspace, size_t workspace_bytes, void* stream);
+int pccnn_pccnn_conv_weight_var(int D, int64_t num_pts, const float* pts, const float* feats, int cin, const float* pdf,
+                                int64_t num_samples, const float* samples, const int32_t* neighbors,
+                                const int32_t* start_ids, const float* radii, const float* kernel_pts, int num_kernel_pts,
+                                float sigma, float* out_variance, void* workspace, size_t workspace_bytes, void* stream);
+
+/* SPHConv (3-D points only): one-hot basis over radial x azimuth x polar bins (+ one bin for offsets shorter than
+ * 1e-4), bin edges ascending on the device, at most 64 edges and 64 basis functions; the output of a sample is
+ * divided by its neighbor count + 1e-6.  Replaces sphconv(), sphconv_grads(), sphconv_compute_weight_variance()
+ * pccnn_lib_ops/pcconvs/sphconv.cu:32-146 (basis shared/spherical_basis.cu:24-168).  Gradient outputs: weights and
+ * features only, as in the reference (the bins are not differentiable). */
+int pccnn_sph_conv(int D, int64_t num_pts, const float* pts, const float* feats, int cin, int64_t num_samples,
+                   const float* samples, const int32_t* neighbors, const int32_t* start_ids, const float* radii,
+                   const float* radial_bins, int num_radial, const float* azimuth_bins, int num_azimuth,
+                   const float* polar_bins, int num_polar, const float* weights, int cout, float* out, void* workspace,
+                   size_t workspace_bytes, void* stream);
+int pccnn_sph_conv_grads(int D, int64_t num_pts, const float* pts, const float* feats, int cin, int64_t num_samples,
+                         const float* samples, const int32_t* neighbors, const int32_t* start_ids, const float* radii,
+                         const float* radial_bins, int num_radial, const float* azimuth_bins, int num_azimuth,
+                         const float* polar_bins, int num_polar, const float* weights, int cout, const float* in_grads,
+                         float* out_weight_grads, float* out_feat_grads, void* workspace, size_t workspace_bytes,
+                         void* stream);
+int pccnn_sph_conv_weight_var(int D, int64_t num_pts, const float* pts, const float* feats, int cin, int64_t num_samples,
+                              const float* samples, const int32_t* neighbors, const int32_t* start_ids, const float* radii,
+                              const float* radial_bins, int num_radial, const float* azimuth_bins, int num_azimuth,
+                              const float* polar_bins, int num_polar, float* out_variance, void* workspace,
+                              size_t workspace_bytes, void* stream);
+
+/* PointConv.  pccnn_point_conv_basis: out_basis[t, :] = ((pts[n0(t)] - samples[n1(t)]) / radii) . axis + bias, a
+ * [num_pairs, hidden] tensor that the layer post-processes in Python; its gradients: points [num_pts, D], samples
+ * [num_samples, D], axis [D, hidden], bias [hidden] (all zero-filled here).  Replace pointconv_basis() and
+ * pointconv_basis_grads()  pccnn_lib_ops/pcconvs/pointconv.cu:32-86.
+ * pccnn_point_conv* take the basis [num_pairs, hidden] (hidden <= 64) as an input; gradient outputs: weights,
+ * features, basis [num_pairs, hidden].  Replace pointconv(), pointconv_grads(), pointconv_compute_weight_variance()
+ * pointconv.cu:89-139. */
+int pccnn_point_conv_basis(int D, int64_t num_pairs, const float* pts, const float* radii, const float* samples,
+                           const int32_t* neighbors, const float* axis, const float* bias, int hidden, float* out_basis,
+                           void* stream);
+int pccnn_point_conv_basis_grads(int D, int64_t num_pts, int64_t num_samples, int64_t num_pairs, const float* pts,
+                                 const float* radii, const float* samples, const int32_t* neighbors, const float* axis,
+                                 int hidden, const float* in_grads, float* out_pt_grads, float* out_sample_grads,
+                                 float* out_axis_grads, float* out_bias_grads, void* stream);
+int pccnn_point_conv(int64_t num_pts, const float* basis, int hidden, const float* feats, int cin, int64_t num_samples,
+                     const int32_t* neighbors, const int32_t* start_ids, const float* weights, int cout, float* out,
+                     void* workspace, size_t workspace_bytes, void* stream);
+int pccnn_point_conv_grads(int64_t num_pts, const float* basis, int hidden, const float* feats, int cin,
+                           int64_t num_samples, int64_t num_pairs, const int32_t* neighbors, const int32_t* start_ids,
+                           const float* weights, int cout, const float* in_grads, float* out_weight_grads,
+                           float* out_feat_grads, float* out_basis_grads, void* workspace, size_t workspace_bytes,
+                           void* stream);
+int pccnn_point_conv_weight_var(int64_t num_pts, const float* basis, int hidden, const float* feats, int cin,
+                                int64_t num_samples, const int32_t* neighbors, const int32_t* start_ids,
+                                float* out_variance, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- */
 /* Dense contraction on the tensor cores                                      */
 /* ------------------------------------------------------------------------- */
 

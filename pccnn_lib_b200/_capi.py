@@ -64,6 +64,40 @@ SIGNATURES = {
     "pccnn_mc_conv_grads": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
                                      _ptr, _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                                      _ptr, _size, _ptr]),
+    "pccnn_conv_weight_var_workspace_bytes": (_size, [_c_i64, _c_int, _c_int]),
+    "pccnn_kp_conv_weight_var": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
+                                          ctypes.c_float, _ptr, _ptr, _size, _ptr]),
+    "pccnn_mc_conv_weight_var": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
+                                          _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
+    # density-normalised kernel-point convolutions: (D, n, pts, a, b, cin, m, samples, neighbors, ends, radii, kpts, K, sigma, ...)
+    "pccnn_kp_conv_n": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
+                                 ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
+    "pccnn_kp_conv_n_grads": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
+                                       ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _size, _ptr]),
+    "pccnn_kp_conv_n_weight_var": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
+                                            _c_int, ctypes.c_float, _ptr, _ptr, _size, _ptr]),
+    "pccnn_pccnn_conv": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _ptr, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
+                                  ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
+    "pccnn_pccnn_conv_grads": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _ptr, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
+                                        ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _size,
+                                        _ptr]),
+    "pccnn_pccnn_conv_weight_var": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _ptr, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
+                                             _c_int, ctypes.c_float, _ptr, _ptr, _size, _ptr]),
+    "pccnn_sph_conv": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _c_int,
+                                _ptr, _c_int, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
+    "pccnn_sph_conv_grads": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr,
+                                      _c_int, _ptr, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _size, _ptr]),
+    "pccnn_sph_conv_weight_var": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
+                                           _ptr, _c_int, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
+    "pccnn_point_conv_basis": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr]),
+    "pccnn_point_conv_basis_grads": (_c_int, [_c_int, _c_i64, _c_i64, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr,
+                                              _ptr, _ptr, _ptr, _ptr, _ptr]),
+    "pccnn_point_conv": (_c_int, [_c_i64, _ptr, _c_int, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _size,
+                                  _ptr]),
+    "pccnn_point_conv_grads": (_c_int, [_c_i64, _ptr, _c_int, _ptr, _c_int, _c_i64, _c_i64, _ptr, _ptr, _ptr, _c_int, _ptr,
+                                        _ptr, _ptr, _ptr, _ptr, _size, _ptr]),
+    "pccnn_point_conv_weight_var": (_c_int, [_c_i64, _ptr, _c_int, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _size,
+                                             _ptr]),
     "pccnn_gemm_workspace_bytes": (_size, [_c_i64, _c_int, _c_int]),
     "pccnn_gemm_f32": (_c_int, [_c_i64, _c_int, _c_int, _ptr, _c_i64, _ptr, _c_i64, _ptr, _c_i64, _c_int, _ptr,
                                 _size, _ptr]),

@@ -24,3 +24,17 @@ class ComputeKPConv(torch.autograd.Function):
             pts, features, samples, neighbors, start_ids, radii, kernel_pts, ctx.sigma_, conv_weights,
             p_grads.contiguous())
         return pt_grads, feat_grads, sample_grads, None, None, None, kernel_pts_grads, None, weight_grads
+
+
+class ComputeKPConvWeightVar(torch.autograd.Function):
+    """Weight variance a KPConv layer should be initialised with on this batch
+    (pccnn_lib/op_wrappers/compute_kpconv.py:76-116 of the reference); not differentiable."""
+
+    @staticmethod
+    def forward(ctx, p_pts, p_features, p_samples, p_neighbors, p_start_ids, p_radii, p_kernel_pts, p_sigma):
+        return ops.kp_conv_weight_var(p_pts, p_features, p_samples, p_neighbors, p_start_ids, p_radii, p_kernel_pts,
+                                      p_sigma)
+
+    @staticmethod
+    def backward(ctx, p_grads):
+        return None, None, None, None, None, None, None, None

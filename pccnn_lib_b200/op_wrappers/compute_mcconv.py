@@ -23,3 +23,18 @@ class ComputeMCConv(torch.autograd.Function):
             pts, pt_pdf, features, samples, neighbors, start_ids, radii, axis_proj, axis_bias, conv_weights,
             p_grads.contiguous())
         return pt_grads, pdf_grad, feat_grads, sample_grads, None, None, None, axis_grad, bias_grad, weight_grads
+
+
+class ComputeMCConvWeightVar(torch.autograd.Function):
+    """Weight variance an MCConv layer should be initialised with on this batch
+    (pccnn_lib/op_wrappers/compute_mcconv.py:78-119 of the reference); not differentiable."""
+
+    @staticmethod
+    def forward(ctx, p_pts, p_pt_pdf, p_features, p_samples, p_neighbors, p_start_ids, p_radii, p_axis_proj,
+                p_axis_bias):
+        return ops.mc_conv_weight_var(p_pts, p_pt_pdf, p_features, p_samples, p_neighbors, p_start_ids, p_radii,
+                                      p_axis_proj, p_axis_bias)
+
+    @staticmethod
+    def backward(ctx, p_grads):
+        return None, None, None, None, None, None, None, None, None

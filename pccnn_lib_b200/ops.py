@@ -583,3 +583,319 @@ def mc_conv_grads(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_pr
                                              d_a.data_ptr(), d_b.data_ptr(), d_pdf.data_ptr(), d_p.data_ptr(),
                                              d_s.data_ptr(), ws.data_ptr(), ws.numel(), _stream()), "mc_conv_grads")
     return [d_w, d_f, d_a, d_b, d_pdf, d_p, d_s]
+
+
+# ---- weight variance (variance-aware initialisation) ---------------------------------------------
+def _variance_out(device):
+    return torch.empty((), dtype=torch.float32, device=device)
+
+
+def kp_conv_weight_var(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma):
+    """0-dim tensor 1 / mean_m ||P[m]||^2; kpconv_compute_weight_variance() of pccnn_lib_ops/pcconvs/kpconv.cu:115-135."""
+    pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii)
+    kernel_pts = _need(kernel_pts, "kernel_pts", torch.float32, 2)
+    k, cin, m = kernel_pts.shape[0], feats.shape[1], samples.shape[0]
+    out = _variance_out(pts.device)
+    with _on(pts.device):
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, k), pts.device)
+        _capi.check(_lib.pccnn_kp_conv_weight_var(d, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
+                                                  _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), out.data_ptr(),
+                                                  ws.data_ptr(), ws.numel(), _stream()), "kp_conv_weight_var")
+    return out
+
+
+def mc_conv_weight_var(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_proj, axis_bias):
+    """mcconv_compute_weight_variance() of pccnn_lib_ops/pcconvs/mcconv.cu:146-171."""
+    pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii)
+    pdf = _need(pdf, "pdf", torch.float32, 1)
+    axis_proj = _need(axis_proj, "axis_proj", torch.float32, 2)
+    axis_bias = _need(axis_bias, "axis_bias", torch.float32)
+    hidden, cin, m = axis_proj.shape[1], feats.shape[1], samples.shape[0]
+    out = _variance_out(pts.device)
+    with _on(pts.device):
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, hidden), pts.device)
+        _capi.check(_lib.pccnn_mc_conv_weight_var(d, pts.shape[0], _p(pts), _p(pdf), _p(feats), cin, m, _p(samples),
+                                                  _p(neighbors), _p(start_ids), _p(radii), _p(axis_proj), _p(axis_bias),
+                                                  hidden, out.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+                    "mc_conv_weight_var")
+    return out
+
+
+# ---- KPConvN and PCCNN -------------------------------------------------------------------------------
+def _kp_density_args(pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, weights=None, in_grads=None):
+    pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii)
+    pdf = _need(pdf, "pdf", torch.float32, 1)
+    kernel_pts = _need(kernel_pts, "kernel_pts", torch.float32, 2)
+    k, cin = kernel_pts.shape[0], feats.shape[1]
+    if kernel_pts.shape[1] != d or pdf.shape[0] != pts.shape[0]:
+        raise RuntimeError("kernel_pts must be [K, %d] and pdf must have one entry per point" % d)
+    cout = None
+    if weights is not None:
+        weights = _need(weights, "weights", torch.float32, 2)
+        if weights.shape[0] != k * cin:
+            raise RuntimeError("weights must be [K * Cin, Cout]")
+        cout = weights.shape[1]
+    if in_grads is not None:
+        in_grads = _need(in_grads, "in_grads", torch.float32, 2)
+        if tuple(in_grads.shape) != (samples.shape[0], cout):
+            raise RuntimeError("in_grads must be [M, Cout]")
+    return pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, weights, in_grads, d, k, cin, cout
+
+
+def kp_conv_n(pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights):
+    """KPConvN forward (kernel-point basis divided by the neighbor's density); kpconvn() of
+    pccnn_lib_ops/pcconvs/kpconvn.cu:32-68."""
+    pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, weights, _, d, k, cin, cout = _kp_density_args(
+        pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, weights)
+    m = samples.shape[0]
+    out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
+    with _on(pts.device):
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
+        _capi.check(_lib.pccnn_kp_conv_n(d, pts.shape[0], _p(pts), _p(pdf), _p(feats), cin, m, _p(samples), _p(neighbors),
+                                         _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
+                                         _p(out), ws.data_ptr(), ws.numel(), _stream()), "kp_conv_n")
+    return out
+
+
+def kp_conv_n_grads(pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights, in_grads):
+    """[dW, dFeat, dKernelPts, dPts, dSamples]; kpconvn_grads() of pccnn_lib_ops/pcconvs/kpconvn.cu:71-130."""
+    pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, weights, in_grads, d, k, cin, cout = \
+        _kp_density_args(pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, weights, in_grads)
+    m, n, dev = samples.shape[0], pts.shape[0], pts.device
+    d_w, d_f = torch.empty_like(weights), torch.empty_like(feats)
+    d_k, d_p, d_s = torch.empty_like(kernel_pts), torch.empty_like(pts), torch.empty_like(samples)
+    with _on(dev):
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, k, cout), dev)
+        _capi.check(_lib.pccnn_kp_conv_n_grads(d, n, _p(pts), _p(pdf), _p(feats), cin, m, _p(samples), _p(neighbors),
+                                               _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
+                                               _p(in_grads), d_w.data_ptr(), d_f.data_ptr(), d_k.data_ptr(), d_p.data_ptr(),
+                                               d_s.data_ptr(), ws.data_ptr(), ws.numel(), _stream()), "kp_conv_n_grads")
+    return [d_w, d_f, d_k, d_p, d_s]
+
+
+def kp_conv_n_weight_var(pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma):
+    """kpconvn_compute_weight_variance() of pccnn_lib_ops/pcconvs/kpconvn.cu:133-155."""
+    pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, _, _, d, k, cin, _ = _kp_density_args(
+        pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts)
+    m = samples.shape[0]
+    out = _variance_out(pts.device)
+    with _on(pts.device):
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, k), pts.device)
+        _capi.check(_lib.pccnn_kp_conv_n_weight_var(d, pts.shape[0], _p(pts), _p(pdf), _p(feats), cin, m, _p(samples),
+                                                    _p(neighbors), _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma),
+                                                    out.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+                    "kp_conv_n_weight_var")
+    return out
+
+
+def pccnn(pts, feats, pdf, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights):
+    """PCCNN forward (Gaussian kernel-point basis divided by the density); pccnn() of pccnn_lib_ops/pcconvs/pccnn.cu:32-66.
+    Argument order as there: features before the density."""
+    pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, weights, _, d, k, cin, cout = _kp_density_args(
+        pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, weights)
+    m = samples.shape[0]
+    out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
+    with _on(pts.device):
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
+        _capi.check(_lib.pccnn_pccnn_conv(d, pts.shape[0], _p(pts), _p(feats), cin, _p(pdf), m, _p(samples), _p(neighbors),
+                                          _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
+                                          _p(out), ws.data_ptr(), ws.numel(), _stream()), "pccnn")
+    return out
+
+
+def pccnn_grads(pts, feats, pdf, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights, in_grads):
+    """[dW, dFeat, dKernelPts, dPdf, dPts, dSamples]; pccnn_grads() of pccnn_lib_ops/pcconvs/pccnn.cu:69-139."""
+    pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, weights, in_grads, d, k, cin, cout = \
+        _kp_density_args(pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, weights, in_grads)
+    m, n, dev = samples.shape[0], pts.shape[0], pts.device
+    d_w, d_f, d_k = torch.empty_like(weights), torch.empty_like(feats), torch.empty_like(kernel_pts)
+    d_pdf, d_p, d_s = torch.empty_like(pdf), torch.empty_like(pts), torch.empty_like(samples)
+    with _on(dev):
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, k, cout), dev)
+        _capi.check(_lib.pccnn_pccnn_conv_grads(d, n, _p(pts), _p(feats), cin, _p(pdf), m, _p(samples), _p(neighbors),
+                                                _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
+                                                _p(in_grads), d_w.data_ptr(), d_f.data_ptr(), d_k.data_ptr(),
+                                                d_pdf.data_ptr(), d_p.data_ptr(), d_s.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                _stream()), "pccnn_grads")
+    return [d_w, d_f, d_k, d_pdf, d_p, d_s]
+
+
+def pccnn_weight_variance(pts, feats, pdf, samples, neighbors, start_ids, radii, kernel_pts, sigma):
+    """pccnn_compute_weight_variance() of pccnn_lib_ops/pcconvs/pccnn.cu:142-165."""
+    pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts, _, _, d, k, cin, _ = _kp_density_args(
+        pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts)
+    m = samples.shape[0]
+    out = _variance_out(pts.device)
+    with _on(pts.device):
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, k), pts.device)
+        _capi.check(_lib.pccnn_pccnn_conv_weight_var(d, pts.shape[0], _p(pts), _p(feats), cin, _p(pdf), m, _p(samples),
+                                                     _p(neighbors), _p(start_ids), _p(radii), _p(kernel_pts), k,
+                                                     float(sigma), out.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+                    "pccnn_weight_variance")
+    return out
+
+
+# ---- SPHConv -----------------------------------------------------------------------------------------
+def _sph_args(pts, feats, samples, neighbors, start_ids, radii, radial_bins, azimuz_bins, polar_bins):
+    pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii)
+    if d != 3:
+        raise RuntimeError("SPHConv is defined for 3-D points only")
+    bins = [_need(b, n, torch.float32, 1) for b, n in ((radial_bins, "radial_bins"), (azimuz_bins, "azimuz_bins"),
+                                                        (polar_bins, "polar_bins"))]
+    k = bins[0].numel() * bins[1].numel() * bins[2].numel() + 1
+    return pts, feats, samples, neighbors, start_ids, radii, bins, k
+
+
+def _bins_c(bins):
+    return (_p(bins[0]), bins[0].numel(), _p(bins[1]), bins[1].numel(), _p(bins[2]), bins[2].numel())
+
+
+def sph_conv(pts, feats, samples, neighbors, start_ids, radii, radial_bins, azimuz_bins, polar_bins, weights):
+    """SPHConv forward -> [M, Cout]; sphconv() of pccnn_lib_ops/pcconvs/sphconv.cu:32-72."""
+    pts, feats, samples, neighbors, start_ids, radii, bins, k = _sph_args(pts, feats, samples, neighbors, start_ids, radii,
+                                                                           radial_bins, azimuz_bins, polar_bins)
+    weights = _need(weights, "weights", torch.float32, 2)
+    cin, cout, m = feats.shape[1], weights.shape[1], samples.shape[0]
+    if weights.shape[0] != k * cin:
+        raise RuntimeError("weights must be [(R * A * P + 1) * Cin, Cout]")
+    out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
+    with _on(pts.device):
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
+        _capi.check(_lib.pccnn_sph_conv(3, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors), _p(start_ids),
+                                        _p(radii), *_bins_c(bins), _p(weights), cout, _p(out), ws.data_ptr(), ws.numel(),
+                                        _stream()), "sph_conv")
+    return out
+
+
+def sph_conv_grads(pts, feats, samples, neighbors, start_ids, radii, radial_bins, azimuz_bins, polar_bins, weights,
+                   in_grads):
+    """[dW, dFeat]; sphconv_grads() of pccnn_lib_ops/pcconvs/sphconv.cu:75-120."""
+    pts, feats, samples, neighbors, start_ids, radii, bins, k = _sph_args(pts, feats, samples, neighbors, start_ids, radii,
+                                                                           radial_bins, azimuz_bins, polar_bins)
+    weights = _need(weights, "weights", torch.float32, 2)
+    in_grads = _need(in_grads, "in_grads", torch.float32, 2)
+    cin, cout, m = feats.shape[1], weights.shape[1], samples.shape[0]
+    if weights.shape[0] != k * cin or tuple(in_grads.shape) != (m, cout):
+        raise RuntimeError("weights must be [(R * A * P + 1) * Cin, Cout] and in_grads [M, Cout]")
+    d_w, d_f = torch.empty_like(weights), torch.empty_like(feats)
+    with _on(pts.device):
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, k, cout), pts.device)
+        _capi.check(_lib.pccnn_sph_conv_grads(3, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
+                                              _p(start_ids), _p(radii), *_bins_c(bins), _p(weights), cout, _p(in_grads),
+                                              d_w.data_ptr(), d_f.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+                    "sph_conv_grads")
+    return [d_w, d_f]
+
+
+def sph_conv_weight_var(pts, feats, samples, neighbors, start_ids, radii, radial_bins, azimuz_bins, polar_bins):
+    """sphconv_compute_weight_variance() of pccnn_lib_ops/pcconvs/sphconv.cu:123-146."""
+    pts, feats, samples, neighbors, start_ids, radii, bins, k = _sph_args(pts, feats, samples, neighbors, start_ids, radii,
+                                                                           radial_bins, azimuz_bins, polar_bins)
+    cin, m = feats.shape[1], samples.shape[0]
+    out = _variance_out(pts.device)
+    with _on(pts.device):
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, k), pts.device)
+        _capi.check(_lib.pccnn_sph_conv_weight_var(3, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
+                                                   _p(start_ids), _p(radii), *_bins_c(bins), out.data_ptr(), ws.data_ptr(),
+                                                   ws.numel(), _stream()), "sph_conv_weight_var")
+    return out
+
+
+# ---- PointConv ---------------------------------------------------------------------------------------
+def point_conv_basis(pts, radii, samples, neighbors, axis_proj, axis_bias):
+    """[T, H] affine projection of the normalised offsets; pointconv_basis() of pccnn_lib_ops/pcconvs/pointconv.cu:32-51."""
+    pts = _need(pts, "pts", torch.float32, 2)
+    radii = _need(radii, "radii", torch.float32, 1)
+    samples = _need(samples, "samples", torch.float32, 2)
+    neighbors = _need(neighbors, "neighbors", torch.int32, 2)
+    axis_proj = _need(axis_proj, "axis_proj", torch.float32, 2)
+    axis_bias = _need(axis_bias, "axis_bias", torch.float32)
+    d, hidden, t = _dims(pts), axis_proj.shape[1], neighbors.shape[0]
+    if samples.shape[1] != d or radii.numel() != d or axis_proj.shape[0] != d or axis_bias.numel() != hidden:
+        raise RuntimeError("samples, radii, axis_proj [D, H] and axis_bias [1, H] must match the point dimension %d" % d)
+    out = torch.empty((t, hidden), dtype=torch.float32, device=pts.device)
+    with _on(pts.device):
+        _capi.check(_lib.pccnn_point_conv_basis(d, t, _p(pts), _p(radii), _p(samples), _p(neighbors), _p(axis_proj),
+                                                _p(axis_bias), hidden, _p(out), _stream()), "point_conv_basis")
+    return out
+
+
+def point_conv_basis_grads(pts, radii, samples, neighbors, axis_proj, axis_bias, in_grads):
+    """[dPts, dSamples, dAxis, dBias]; pointconv_basis_grads() of pccnn_lib_ops/pcconvs/pointconv.cu:54-86."""
+    pts = _need(pts, "pts", torch.float32, 2)
+    radii = _need(radii, "radii", torch.float32, 1)
+    samples = _need(samples, "samples", torch.float32, 2)
+    neighbors = _need(neighbors, "neighbors", torch.int32, 2)
+    axis_proj = _need(axis_proj, "axis_proj", torch.float32, 2)
+    axis_bias = _need(axis_bias, "axis_bias", torch.float32)
+    in_grads = _need(in_grads, "in_grads", torch.float32, 2)
+    d, hidden, t = _dims(pts), axis_proj.shape[1], neighbors.shape[0]
+    if tuple(in_grads.shape) != (t, hidden):
+        raise RuntimeError("in_grads must be [T, H]")
+    d_p, d_s = torch.empty_like(pts), torch.empty_like(samples)
+    d_a, d_b = torch.empty_like(axis_proj), torch.empty((1, hidden), dtype=torch.float32, device=pts.device)
+    with _on(pts.device):
+        _capi.check(_lib.pccnn_point_conv_basis_grads(d, pts.shape[0], samples.shape[0], t, _p(pts), _p(radii), _p(samples),
+                                                      _p(neighbors), _p(axis_proj), hidden, _p(in_grads), d_p.data_ptr(),
+                                                      d_s.data_ptr(), d_a.data_ptr(), d_b.data_ptr(), _stream()),
+                    "point_conv_basis_grads")
+    return [d_p, d_s, d_a, d_b]
+
+
+def _point_conv_args(basis, feats, neighbors, start_ids):
+    basis = _need(basis, "basis", torch.float32, 2)
+    feats = _need(feats, "features", torch.float32, 2)
+    neighbors = _need(neighbors, "neighbors", torch.int32, 2)
+    start_ids = _need(start_ids, "start_ids", torch.int32, 1)
+    if basis.shape[0] != neighbors.shape[0] or neighbors.shape[1] != 2:
+        raise RuntimeError("basis needs one row per neighbor pair")
+    if basis.shape[1] > 64:
+        raise RuntimeError("at most 64 basis functions are supported (got %d)" % basis.shape[1])
+    _maybe_validate(neighbors, start_ids, feats.shape[0])
+    return basis, feats, neighbors, start_ids
+
+
+def point_conv(basis, feats, neighbors, start_ids, weights):
+    """PointConv contraction on a caller-made basis [T, H] -> [M, Cout]; pointconv() of pointconv.cu:89-103."""
+    basis, feats, neighbors, start_ids = _point_conv_args(basis, feats, neighbors, start_ids)
+    weights = _need(weights, "weights", torch.float32, 2)
+    hidden, cin, cout, m = basis.shape[1], feats.shape[1], weights.shape[1], start_ids.shape[0]
+    if weights.shape[0] != hidden * cin:
+        raise RuntimeError("weights must be [H * Cin, Cout]")
+    out = torch.empty((m, cout), dtype=torch.float32, device=feats.device)
+    with _on(feats.device):
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, hidden, cout), feats.device)
+        _capi.check(_lib.pccnn_point_conv(feats.shape[0], _p(basis), hidden, _p(feats), cin, m, _p(neighbors), _p(start_ids),
+                                          _p(weights), cout, _p(out), ws.data_ptr(), ws.numel(), _stream()), "point_conv")
+    return out
+
+
+def point_conv_grads(basis, feats, neighbors, start_ids, weights, in_grads):
+    """[dW, dFeat, dBasis]; pointconv_grads() of pccnn_lib_ops/pcconvs/pointconv.cu:106-127."""
+    basis, feats, neighbors, start_ids = _point_conv_args(basis, feats, neighbors, start_ids)
+    weights = _need(weights, "weights", torch.float32, 2)
+    in_grads = _need(in_grads, "in_grads", torch.float32, 2)
+    hidden, cin, cout, m = basis.shape[1], feats.shape[1], weights.shape[1], start_ids.shape[0]
+    if weights.shape[0] != hidden * cin or tuple(in_grads.shape) != (m, cout):
+        raise RuntimeError("weights must be [H * Cin, Cout] and in_grads [M, Cout]")
+    d_w, d_f, d_b = torch.empty_like(weights), torch.empty_like(feats), torch.empty_like(basis)
+    with _on(feats.device):
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, hidden, cout), feats.device)
+        _capi.check(_lib.pccnn_point_conv_grads(feats.shape[0], _p(basis), hidden, _p(feats), cin, m, basis.shape[0],
+                                                _p(neighbors), _p(start_ids), _p(weights), cout, _p(in_grads),
+                                                d_w.data_ptr(), d_f.data_ptr(), d_b.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                _stream()), "point_conv_grads")
+    return [d_w, d_f, d_b]
+
+
+def point_conv_weight_var(basis, feats, neighbors, start_ids):
+    """pointconv_compute_weight_variance() of pccnn_lib_ops/pcconvs/pointconv.cu:130-139."""
+    basis, feats, neighbors, start_ids = _point_conv_args(basis, feats, neighbors, start_ids)
+    hidden, cin, m = basis.shape[1], feats.shape[1], start_ids.shape[0]
+    out = _variance_out(feats.device)
+    with _on(feats.device):
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, hidden), feats.device)
+        _capi.check(_lib.pccnn_point_conv_weight_var(feats.shape[0], _p(basis), hidden, _p(feats), cin, m, _p(neighbors),
+                                                     _p(start_ids), out.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+                    "point_conv_weight_var")
+    return out

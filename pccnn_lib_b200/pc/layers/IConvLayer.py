@@ -1,3 +1,4 @@
+import math
 from abc import ABC, abstractmethod
 
 import torch
@@ -22,11 +23,16 @@ class IConvLayer(torch.nn.Module, ABC):
         self.accum_weight_var_counter_ = 1.0
 
     def set_init_warmup_state(self, p_init_warmup_state):
-        """Variance-aware warm-up initialisation needs the *_weight_var operators, which are not
-        part of this package; the flag is kept for interface compatibility."""
-        if p_init_warmup_state and self.use_const_variance_init_:
-            raise NotImplementedError("variance-aware warm-up initialisation is not available in pccnn_lib_b200")
+        """While the flag is set (and the layer was built with the constant-variance initialisation), every forward
+        pass accumulates the weight variance its batch asks for (the *_weight_var operators) and re-draws the
+        weights with it (pccnn_lib/pc/layers/IConvLayer.py:47-57, KPConv.py:103-116 of the reference)."""
         self.wamup_state_ = p_init_warmup_state
+
+    def __warmup_weights__(self, p_variance):
+        """Shared tail of the layers' warm-up branch: accumulate 1 / variance, re-draw the weights."""
+        self.__update_weight_var__(1.0 / p_variance.item())
+        stdv = math.sqrt(self.out_constant_variance_ / self.accum_weight_var_)
+        self.conv_weights_.data.normal_(0.0, stdv)
 
     def __update_weight_var__(self, p_new_var):
         self.accum_weight_var_ += (p_new_var - self.accum_weight_var_) / self.accum_weight_var_counter_
@@ -61,15 +67,25 @@ class IConvLayer(torch.nn.Module, ABC):
 
 
 class IConvLayerFactory(ABC):
-    """Factory interface (pccnn_lib/pc/layers/IConvLayer.py:160-186 of the reference)."""
+    """Factory interface (pccnn_lib/pc/layers/IConvLayer.py:160-215 of the reference): number of basis functions,
+    whether the layers use the constant-variance initialisation, and the list of the layers created."""
 
-    def __init__(self, p_constant_weight_var=False, p_const_var_value=1.0):
-        self.use_const_variance_init_ = p_constant_weight_var
-        self.conv_var_value_ = p_const_var_value
+    def __init__(self, p_num_basis, p_const_var_w_init, p_const_var_value=1.0):
+        super(IConvLayerFactory, self).__init__()
+        self.num_basis_ = p_num_basis
+        self.conv_var_w_init_ = p_const_var_w_init
+        self.const_var_value_ = p_const_var_value
         self.conv_list_ = []
 
+    def set_init_warmup_state_convs(self, p_state):
+        for cur_conv in self.conv_list_:
+            cur_conv.set_init_warmup_state(p_state)
+
+    def define_num_basis(self, p_num_basis):
+        self.num_basis_ = p_num_basis
+
     def update_conv_const_var_value(self, p_const_var_value):
-        self.conv_var_value_ = p_const_var_value
+        self.const_var_value_ = p_const_var_value
 
     @abstractmethod
     def create_conv_layer(self, p_dims, p_in_features, p_out_features):

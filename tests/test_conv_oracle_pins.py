@@ -133,3 +133,53 @@ def test_prepared_kernel_points_are_the_reference_layers(dims, num_pts):
     pts, sigma = prepare_kernel_points(dims, num_pts)
     assert pts.dtype == np.float32 and np.array_equal(pts, golden["%d_%d_pts" % (dims, num_pts)])
     assert sigma == float(golden["%d_%d_sigma" % (dims, num_pts)])
+
+
+def test_weight_variance_double_sum_is_the_norm_of_the_projected_features(ref_clouds):
+    # pcconvs/shared/compute_variance_weights.cu:49-88 loops over all pairs (i, j) of a sample's neighbors; the CUDA
+    # implementation evaluates the same quantity as the squared norm of the sample's projected features
+    case = kp_case(ref_clouds, KP_CASES[0], normal_feats=True)
+    keys = ("pts", "feats", "samples", "neighbors", "start_ids", "radii", "kernel_pts")
+    var = conv_oracle.kp_conv_weight_var(*[case[k] for k in keys], case["sigma"])
+    t = lambda k: torch.as_tensor(case[k]).double()
+    nb = torch.as_tensor(case["neighbors"])
+    basis = conv_oracle.kernel_pts_basis(conv_oracle.pt_diff(t("pts"), t("samples"), nb, t("radii")), t("kernel_pts"),
+                                         case["sigma"])
+    proj = conv_oracle.feat_basis_proj(basis, t("feats"), nb, case["samples"].shape[0])
+    assert abs(float(var) - float(1.0 / (proj.reshape(proj.shape[0], -1) ** 2).sum(1).mean())) <= 1e-12 * abs(float(var))
+
+
+@pytest.mark.parametrize("c", KP_CASES[:2], ids=lambda c: "d%d_n%d" % (c["dims"], c["n"]))
+def test_density_normalised_kernel_point_backward_formulas(ref_clouds, c):
+    # pcconvs/pccnn.cu:69-139 and kpconvn.cu:71-130 restated by hand against autograd of the float64 forward
+    case = kp_case(ref_clouds, c, normal_feats=True, shrink=True)
+    pdf = np.random.RandomState(0).uniform(0.5, 2.0, size=case["pts"].shape[0])
+    g = np.random.RandomState(1).normal(size=(case["samples"].shape[0], c["cout"]))
+    args = dict(pts=case["pts"], feats=case["feats"], pdf=pdf, samples=case["samples"], neighbors=case["neighbors"],
+                start_ids=case["start_ids"], radii=case["radii"], kernel_pts=case["kernel_pts"], sigma=0.3,
+                weights=case["weights"])
+    dw, df, dk, dpdf, dp, ds = [x.numpy() for x in conv_oracle.pccnn_grads(**args, in_grads=g)]
+    _autograd_check(conv_oracle.pccnn, args, ["weights", "feats", "kernel_pts", "pdf"], g,
+                    dict(weights=dw, feats=df, kernel_pts=dk, pdf=dpdf))
+    _autograd_check(conv_oracle.pccnn, args, ["pts"], g, dict(pts=dp + ds), tie=("samples", "pts"))
+    args["sigma"] = case["sigma"]
+    dw, df, dk, dp, ds = [x.numpy() for x in conv_oracle.kp_conv_n_grads(**args, in_grads=g)]
+    _autograd_check(conv_oracle.kp_conv_n, args, ["weights", "feats", "kernel_pts"], g,
+                    dict(weights=dw, feats=df, kernel_pts=dk))
+
+
+def test_spherical_basis_is_one_hot_and_sphconv_averages(ref_clouds):
+    case = kp_case(ref_clouds, KP_CASES[1])
+    t = lambda k: torch.as_tensor(case[k]).double()
+    nb = torch.as_tensor(case["neighbors"])
+    diffs = conv_oracle.pt_diff(t("pts"), t("samples"), nb, t("radii"))
+    basis = conv_oracle.spherical_basis(diffs, [0.5, 1.0], [-0.5, 0.5, 1.6], [1.0, 2.0, 3.2])
+    assert tuple(basis.shape) == (nb.shape[0], 19) and bool((basis.sum(1) == 1.0).all())
+    self_pairs = (nb[:, 0] == nb[:, 1])
+    assert bool((basis[self_pairs, 0] == 1.0).all()) and float(basis[~self_pairs, 0].sum()) == 0.0
+    # with all-ones features and weights every output is (neighbors * Cin) / (neighbors + 1e-6)
+    ones_f = np.ones((case["pts"].shape[0], 2), np.float32)
+    w = np.ones((19 * 2, 3), np.float32)
+    out = conv_oracle.sph_conv(case["pts"], ones_f, case["samples"], case["neighbors"], case["start_ids"], case["radii"],
+                               [0.5, 1.0], [-0.5, 0.5, 1.6], [1.0, 2.0, 3.2], w)
+    assert np.allclose(out.numpy(), 2.0, rtol=1e-5)

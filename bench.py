@@ -975,7 +975,9 @@ def conv_entry(name, args, R, steps=None, with_gemm_alone=True):
                      "bytes_per_step": int(sum(p["weights"].numel() * 4 for p in params)),
                      "device_us_per_step": round(R.max(coll_us), 1), "exposed_us_per_step": round(R.max(exposed_us), 1),
                      "overlap": "weight gradients are summed on a side stream from the moment the backward operator "
-                                "records them final; the wait of the compute stream at the end of the step is the exposed part"}
+                                "records them final; the wait of the compute stream at the end of the step is the exposed part. "
+                                "Both figures include waiting for the slowest rank to reach the collective (the ranks' "
+                                "clouds differ), not only the transfer"}
     gsum.marks, wait_marks = [], []
 
     # ---- end to end: points, features and upstream gradients from pinned host memory, geometry rebuilt, output and

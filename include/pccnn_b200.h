@@ -269,8 +269,16 @@ int pccnn_poisson_disk_sampling_static(int D, int64_t n, const int64_t* sorted_k
  * neighbor search (row.x indexes pts and feats, row.y indexes samples); radii [D] on the device;
  * out [num_samples, cout] float32.  The contraction runs on the tensor cores with a bf16 hi/lo
  * split (three passes), which keeps the result within 1e-4 relative of an fp32 evaluation.
- * Scratch: pccnn_conv_workspace_bytes(num_samples, cin, basis_size, cout). */
-size_t pccnn_conv_workspace_bytes(int64_t num_samples, int cin, int basis_size, int cout);
+ * Scratch: pccnn_conv_workspace_bytes(num_pts, num_samples, cin, basis_size, cout) (it holds, besides the projected
+ * features of one chunk of samples and the weights, bf16 hi / lo copies of the feature rows for the tensor-core pair
+ * kernels, hence num_pts). */
+size_t pccnn_conv_workspace_bytes(int64_t num_pts, int64_t num_samples, int cin, int basis_size, int cout);
+
+/* Which kernels do the per-pair work of every convolution entry point below (no counterpart in the reference): 0, the
+ * default, uses tcgen05 pair kernels for 3-D points with at least 32 input channels and CUDA-core kernels otherwise;
+ * 1 uses the CUDA-core kernels everywhere.  Both give the same results within the stated tolerances; the switch
+ * exists so that they can be compared.  Process-wide. */
+int pccnn_conv_set_path(int path);
 
 /* KPConv forward: basis b[t,k] = clamp(1 - |kernel_pts[k] - d_t| / sigma, 0, 1), weights
  * [num_kernel_pts * cin, cout] with row index c * num_kernel_pts + k.
@@ -306,7 +314,7 @@ int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, co
 /* Gradients of the two convolutions for an upstream gradient in_grads [num_samples, cout].
  * Every output is zero-filled here and accumulated with float reductions (like the reference,
  * whose scatter steps use atomics), so results are reproducible only up to summation order.
- * Scratch: pccnn_conv_grads_workspace_bytes(num_samples, cin, basis_size, cout).
+ * Scratch: pccnn_conv_grads_workspace_bytes(num_pts, num_samples, cin, basis_size, cout).
  *
  * pccnn_kp_conv_grads replaces kpconv_grads()  pccnn_lib_ops/pcconvs/kpconv.cu:63-112
  * (shared/feat_basis_proj_grads.cu:158-223, shared/kernel_pts_basis.cu:41-70, shared/pt_diff.cu:51-80);
@@ -315,7 +323,7 @@ int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, co
  * pccnn_mc_conv_grads replaces mcconv_grads()  pccnn_lib_ops/pcconvs/mcconv.cu:73-143
  * (shared/mlp_basis.cu:50-96); outputs: weights (shape of the weights), features, axis [D, hidden],
  * bias [hidden], pdf [num_pts], points, samples. */
-size_t pccnn_conv_grads_workspace_bytes(int64_t num_samples, int cin, int basis_size, int cout);
+size_t pccnn_conv_grads_workspace_bytes(int64_t num_pts, int64_t num_samples, int cin, int basis_size, int cout);
 /* Data parallelism (no counterpart in the reference, which is single-process): `event` (a cudaEvent_t) is recorded
  * on the stream of the NEXT pccnn_kp_conv_grads / pccnn_mc_conv_grads call of this thread at the point where
  * out_weight_grads is final, i.e. before the last per-pair kernel of the call; a communication stream that waits
@@ -347,8 +355,8 @@ int pccnn_mc_conv_grads(int D, int64_t num_pts, const float* pts, const float* p
  * the squared norm of the sample's projected features, so it is computed in O(n) per sample, not O(n^2).
  * Replace kpconv_compute_weight_variance()  pccnn_lib_ops/pcconvs/kpconv.cu:115-135 and
  * mcconv_compute_weight_variance()  mcconv.cu:146-171 (kernel shared/compute_variance_weights.cu:24-170).
- * Scratch: pccnn_conv_weight_var_workspace_bytes(num_samples, cin, basis_size).  num_samples >= 1. */
-size_t pccnn_conv_weight_var_workspace_bytes(int64_t num_samples, int cin, int basis_size);
+ * Scratch: pccnn_conv_weight_var_workspace_bytes(num_pts, num_samples, cin, basis_size).  num_samples >= 1. */
+size_t pccnn_conv_weight_var_workspace_bytes(int64_t num_pts, int64_t num_samples, int cin, int basis_size);
 int pccnn_kp_conv_weight_var(int D, int64_t num_pts, const float* pts, const float* feats, int cin, int64_t num_samples,
                              const float* samples, const int32_t* neighbors, const int32_t* start_ids, const float* radii,
                              const float* kernel_pts, int num_kernel_pts, float sigma, float* out_variance,

@@ -49,14 +49,15 @@ SIGNATURES = {
     "pccnn_poisson_disk_sampling_static_max_points": (_c_i64, []),
     "pccnn_poisson_disk_sampling_static": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
                                                     ctypes.POINTER(_c_i64), _ptr]),
-    "pccnn_conv_workspace_bytes": (_size, [_c_i64, _c_int, _c_int, _c_int]),
+    "pccnn_conv_set_path": (_c_int, [_c_int]),
+    "pccnn_conv_workspace_bytes": (_size, [_c_i64, _c_i64, _c_int, _c_int, _c_int]),
     "pccnn_kp_conv": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
                                ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
     "pccnn_kp_conv_bf16": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
                                     ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
     "pccnn_mc_conv": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                                _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
-    "pccnn_conv_grads_workspace_bytes": (_size, [_c_i64, _c_int, _c_int, _c_int]),
+    "pccnn_conv_grads_workspace_bytes": (_size, [_c_i64, _c_i64, _c_int, _c_int, _c_int]),
     "pccnn_conv_grads_set_weight_grads_event": (_c_int, [_ptr]),
     "pccnn_kp_conv_grads": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
                                      ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _size,
@@ -64,7 +65,7 @@ SIGNATURES = {
     "pccnn_mc_conv_grads": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
                                      _ptr, _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                                      _ptr, _size, _ptr]),
-    "pccnn_conv_weight_var_workspace_bytes": (_size, [_c_i64, _c_int, _c_int]),
+    "pccnn_conv_weight_var_workspace_bytes": (_size, [_c_i64, _c_i64, _c_int, _c_int]),
     "pccnn_kp_conv_weight_var": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
                                           ctypes.c_float, _ptr, _ptr, _size, _ptr]),
     "pccnn_mc_conv_weight_var": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,

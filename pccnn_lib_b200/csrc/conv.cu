@@ -22,6 +22,7 @@
 
 namespace pccnn {
 thread_local cudaEvent_t g_weight_grads_event = nullptr;
+int g_conv_path = 0;
 }
 
 
@@ -29,8 +30,8 @@ using namespace pccnn;
 
 extern "C" {
 
-size_t pccnn_conv_workspace_bytes(int64_t num_samples, int cin, int basis_size, int cout) {
-    return conv_layout(num_samples < 0 ? 0 : num_samples, cin, basis_size, cout).total;
+size_t pccnn_conv_workspace_bytes(int64_t num_pts, int64_t num_samples, int cin, int basis_size, int cout) {
+    return conv_layout(num_pts < 0 ? 0 : num_pts, num_samples < 0 ? 0 : num_samples, cin, basis_size, cout).total;
 }
 
 int pccnn_kp_conv(int D, int64_t num_pts, const float* pts, const float* feats, int cin, int64_t num_samples,
@@ -67,13 +68,19 @@ int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, co
                                                 workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+int pccnn_conv_set_path(int path) {
+    PCCNN_CHECK_ARG(path == 0 || path == 1, "conv_set_path: 0 (tensor-core pair kernels where they apply) or 1 (CUDA cores)");
+    g_conv_path = path;
+    return PCCNN_OK;
+}
+
 int pccnn_conv_grads_set_weight_grads_event(void* event) {
     g_weight_grads_event = (cudaEvent_t)event;
     return PCCNN_OK;
 }
 
-size_t pccnn_conv_weight_var_workspace_bytes(int64_t num_samples, int cin, int basis_size) {
-    return conv_weight_var_workspace(num_samples < 0 ? 0 : num_samples, cin, basis_size);
+size_t pccnn_conv_weight_var_workspace_bytes(int64_t num_pts, int64_t num_samples, int cin, int basis_size) {
+    return conv_weight_var_workspace(num_pts < 0 ? 0 : num_pts, num_samples < 0 ? 0 : num_samples, cin, basis_size);
 }
 
 int pccnn_kp_conv_weight_var(int D, int64_t num_pts, const float* pts, const float* feats, int cin, int64_t num_samples,
@@ -98,8 +105,8 @@ int pccnn_mc_conv_weight_var(int D, int64_t num_pts, const float* pts, const flo
                                                    workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
-size_t pccnn_conv_grads_workspace_bytes(int64_t num_samples, int cin, int basis_size, int cout) {
-    return conv_backward_layout(num_samples < 0 ? 0 : num_samples, cin, basis_size, cout).total;
+size_t pccnn_conv_grads_workspace_bytes(int64_t num_pts, int64_t num_samples, int cin, int basis_size, int cout) {
+    return conv_backward_layout(num_pts < 0 ? 0 : num_pts, num_samples < 0 ? 0 : num_samples, cin, basis_size, cout).total;
 }
 
 int pccnn_kp_conv_grads(int D, int64_t num_pts, const float* pts, const float* feats, int cin, int64_t num_samples,

@@ -10,8 +10,16 @@
 #include "common.cuh"
 #include "gemm.cuh"
 #include "status.cuh"
+#include "conv_tc.cuh"
 
 namespace pccnn {
+
+// 0: the pair-level work runs on the tensor cores where those kernels apply (3-D points, at least 32 input
+// channels); 1: CUDA-core kernels everywhere (kept for the other dimensions and narrow inputs, and selectable so
+// that the two paths can be compared).  Defined in conv.cu, changed by pccnn_conv_set_path.
+extern int g_conv_path;
+
+static bool use_tensor_core_pairs(int D, int cin) { return g_conv_path == 0 && D == 3 && cin >= 32; }
 
 // Warps per block: the two per-warp basis buffers of the backward kernel must fit in 48 KB.
 template <int KP>
@@ -109,6 +117,30 @@ struct KPBasis {
             }
         }
     }
+    // Same gradient without any cross-lane work: the parameter gradients of this thread's pairs are added to its
+    // own accumulators acc[kGradFloats] (laid out like s_grad), which the caller reduces once at the end.
+    __device__ static void grad_local(const float* sp, const KPBasisArgs& a, int K, const float (&d)[D], int /*n0*/,
+                                      int /*t*/, int /*m*/, bool active, const float* db, float (&d_off)[D],
+                                      float (&acc_g)[kGradFloats], float& /*d_pdf*/) {
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+            float v[D], acc = 0.f;
+#pragma unroll
+            for (int x = 0; x < D; ++x) {
+                v[x] = sp[k * D + x] - d[x];
+                acc = fmaf(v[x], v[x], acc);
+            }
+            const float dist = sqrtf(fmaxf(acc, 0.f));
+            float gk = 0.f;
+            if (active && k < K && 1.0f - dist * a.inv_sigma >= 0.f) gk = -db[k] * a.inv_sigma / (dist + 1e-6f);
+#pragma unroll
+            for (int x = 0; x < D; ++x) {
+                const float t = gk * v[x];
+                d_off[x] -= t;
+                acc_g[k * D + x] += t;
+            }
+        }
+    }
     __device__ static void flush(const float* s_grad, int K, float* g0, float* /*g1*/) {
         for (int i = threadIdx.x; i < K * D; i += blockDim.x)
             if (s_grad[i] != 0.f) atomicAdd(g0 + i, s_grad[i]);
@@ -165,6 +197,28 @@ struct MLPBasis {
                 d_off[x] = fmaf(cur, sp[x * KP + k], d_off[x]);
                 const float tot = warp_sum(d[x] * cur);
                 if (lane == 0) atomicAdd(s_grad + x * KP + k, tot);
+            }
+        }
+    }
+    __device__ static void grad_local(const float* sp, const MLPBasisArgs& a, int K, const float (&d)[D], int n0,
+                                      int /*t*/, int /*m*/, bool active, const float* db, float (&d_off)[D],
+                                      float (&acc_g)[kGradFloats], float& d_pdf) {
+        const float inv_pdf = active ? 1.0f / __ldg(a.pdf + n0) : 0.f;
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+            float pre = 0.f;
+#pragma unroll
+            for (int x = 0; x < D; ++x) pre = fmaf(d[x], sp[x * KP + k], pre);
+            pre += sp[D * KP + k];
+            const float act = pre > 0.f ? pre : 0.2f * pre;
+            const float dbk = (active && k < K) ? db[k] : 0.f;
+            d_pdf -= act * dbk * inv_pdf * inv_pdf;
+            const float cur = dbk * inv_pdf * (act > 0.f ? 1.0f : 0.2f);
+            acc_g[D * KP + k] += cur;
+#pragma unroll
+            for (int x = 0; x < D; ++x) {
+                d_off[x] = fmaf(cur, sp[x * KP + k], d_off[x]);
+                acc_g[x * KP + k] = fmaf(d[x], cur, acc_g[x * KP + k]);
             }
         }
     }
@@ -674,11 +728,17 @@ constexpr int64_t kConvChunk = 1 << 17;
 
 struct ConvLayout {
     int ld_p;      // padded Cin * K
+    int ld_f;      // elements per row of the bf16 feature planes (Cin rounded up to 8)
     int64_t chunk;
-    size_t p_hi_off, p_lo_off, w_hi_off, w_lo_off, status_off, total;
+    size_t p_hi_off, p_lo_off, w_hi_off, w_lo_off, status_off, f_hi_off, f_lo_off, total;
 };
 
-static ConvLayout conv_layout(int64_t num_samples, int cin, int K, int cout) {
+// Bytes of one bf16 feature plane [num_pts, ld_f] for the tensor-core pair kernels (0 when they cannot apply).
+static size_t feature_plane_bytes(int64_t num_pts, int cin) {
+    return cin >= 32 ? align_up((size_t)(num_pts > 0 ? num_pts : 1) * ((cin + 7) / 8 * 8) * 2) : 0;
+}
+
+static ConvLayout conv_layout(int64_t num_pts, int64_t num_samples, int cin, int K, int cout) {
     ConvLayout L;
     L.ld_p = (cin * K + 63) / 64 * 64;
     L.chunk = num_samples < kConvChunk ? (num_samples > 0 ? num_samples : 1) : kConvChunk;
@@ -689,7 +749,10 @@ static ConvLayout conv_layout(int64_t num_samples, int cin, int K, int cout) {
     L.w_hi_off = 2 * p_bytes;
     L.w_lo_off = L.w_hi_off + w_bytes;
     L.status_off = L.w_lo_off + w_bytes;
-    L.total = L.status_off + 256;
+    L.ld_f = (cin + 7) / 8 * 8;
+    L.f_hi_off = L.status_off + 256;
+    L.f_lo_off = L.f_hi_off + feature_plane_bytes(num_pts, cin);
+    L.total = L.f_lo_off + feature_plane_bytes(num_pts, cin);
     return L;
 }
 
@@ -717,7 +780,7 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
                     "%s: with several MLPs, Cin*K per MLP must be a multiple of 8", who);
     if (num_samples == 0) return PCCNN_OK;
     PCCNN_CHECK_ARG(pts && feats && samples && start_ids && radii && weights && out, "%s: null pointer", who);
-    const ConvLayout L = conv_layout(num_samples, cin, K, cout);
+    const ConvLayout L = conv_layout(num_pts, num_samples, cin, K, cout);
     if (!workspace || workspace_bytes < L.total) {
         set_error("%s: workspace of %zu bytes, need %zu", who, workspace_bytes, L.total);
         return PCCNN_ERR_WORKSPACE;
@@ -742,14 +805,27 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
                                       ws + L.w_hi_off + off, ws + L.w_lo_off + off, s);
         if (rc) return rc;
     }
+    const bool tc = use_tensor_core_pairs(D, cin) && (!io_bf16 || cin % 8 == 0);
+    FeaturePlanes planes{(const __nv_bfloat16*)(ws + L.f_hi_off), (const __nv_bfloat16*)(ws + L.f_lo_off), L.ld_f};
+    if (tc && io_bf16) planes = FeaturePlanes{(const __nv_bfloat16*)feats_any, nullptr, cin};  // used as they are
+    if (tc && !io_bf16)
+        if (int rc = split_features(num_pts, cin, feats, ws + L.f_hi_off, ws + L.f_lo_off, s)) return rc;
     for (int64_t m0 = 0; m0 < num_samples; m0 += L.chunk) {
         const int64_t m1 = (m0 + L.chunk < num_samples) ? m0 + L.chunk : num_samples;
         int rc = PCCNN_OK;
         if (io_bf16) {
-            if constexpr (WITH_BF16)  // only the operators that offer the bf16 path instantiate its kernels
-                rc = launch_project<3, ARGS, BASIS, __nv_bfloat16>(K, args, pts, (const __nv_bfloat16*)feats_any, cin,
-                                                                   samples, neighbors, start_ids, radii, (int)m0, (int)m1,
-                                                                   ws + L.p_hi_off, nullptr, L.ld_p, s);
+            if constexpr (WITH_BF16) {  // only the operators that offer the bf16 path instantiate its kernels
+                if (tc)
+                    rc = launch_project_tc<ARGS, BASIS, false>(K, args, pts, planes, cin, samples, neighbors, start_ids, radii,
+                                                               (int)m0, (int)m1, ws + L.p_hi_off, nullptr, L.ld_p, status, s);
+                else
+                    rc = launch_project<3, ARGS, BASIS, __nv_bfloat16>(K, args, pts, (const __nv_bfloat16*)feats_any, cin,
+                                                                       samples, neighbors, start_ids, radii, (int)m0,
+                                                                       (int)m1, ws + L.p_hi_off, nullptr, L.ld_p, s);
+            }
+        } else if (tc) {
+            rc = launch_project_tc<ARGS, BASIS, true>(K, args, pts, planes, cin, samples, neighbors, start_ids, radii, (int)m0,
+                                                      (int)m1, ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, status, s);
         } else {
             rc = dispatch_dims<BasisTraits<BASIS>::kOnly3D>(D, [&](auto dim) {
             constexpr int DIM = decltype(dim)::value;
@@ -780,10 +856,11 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
 struct ConvBackwardLayout {
     int ld_p, ld_g;
     int64_t chunk;
-    size_t p_hi_off, p_lo_off, g_hi_off, g_lo_off, dproj_off, w_hi_off, w_lo_off, status_off, total;
+    int ld_f;
+    size_t p_hi_off, p_lo_off, g_hi_off, g_lo_off, dproj_off, w_hi_off, w_lo_off, status_off, f_hi_off, f_lo_off, total;
 };
 
-static ConvBackwardLayout conv_backward_layout(int64_t num_samples, int cin, int K, int cout) {
+static ConvBackwardLayout conv_backward_layout(int64_t num_pts, int64_t num_samples, int cin, int K, int cout) {
     ConvBackwardLayout L;
     const int inner = cin * K;
     L.ld_p = (inner + 63) / 64 * 64;
@@ -801,7 +878,10 @@ static ConvBackwardLayout conv_backward_layout(int64_t num_samples, int cin, int
     L.w_hi_off = L.dproj_off + d_bytes;
     L.w_lo_off = L.w_hi_off + w_bytes;
     L.status_off = L.w_lo_off + w_bytes;
-    L.total = L.status_off + 256;
+    L.ld_f = (cin + 7) / 8 * 8;
+    L.f_hi_off = L.status_off + 256;
+    L.f_lo_off = L.f_hi_off + feature_plane_bytes(num_pts, cin);
+    L.total = L.f_lo_off + feature_plane_bytes(num_pts, cin);
     return L;
 }
 
@@ -839,7 +919,7 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
     if (d_samples) PCCNN_CUDA(cudaMemsetAsync(d_samples, 0, (size_t)num_samples * D * 4, s));
     if (num_samples == 0) return PCCNN_OK;
     PCCNN_CHECK_ARG(pts && feats && samples && start_ids && radii && weights && in_grads, "%s: null pointer", who);
-    const ConvBackwardLayout L = conv_backward_layout(num_samples, cin, K, cout);
+    const ConvBackwardLayout L = conv_backward_layout(num_pts, num_samples, cin, K, cout);
     if (!workspace || workspace_bytes < L.total) {
         set_error("%s: workspace of %zu bytes, need %zu", who, workspace_bytes, L.total);
         return PCCNN_ERR_WORKSPACE;
@@ -857,16 +937,23 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
             return rc;
     }
     float* d_proj = (float*)(ws + L.dproj_off);
+    const bool tc = use_tensor_core_pairs(D, cin);
+    const FeaturePlanes planes{(const __nv_bfloat16*)(ws + L.f_hi_off), (const __nv_bfloat16*)(ws + L.f_lo_off), L.ld_f};
+    if (tc)
+        if (int rc = split_features(num_pts, cin, feats, ws + L.f_hi_off, ws + L.f_lo_off, s)) return rc;
     for (int64_t m0 = 0; m0 < num_samples; m0 += L.chunk) {
         const int64_t m1 = (m0 + L.chunk < num_samples) ? m0 + L.chunk : num_samples;
         const int64_t rows = m1 - m0;
         int rc = PCCNN_OK;
-        rc = dispatch_dims<BasisTraits<BASIS>::kOnly3D>(D, [&](auto dim) {
-            constexpr int DIM = decltype(dim)::value;
-            return launch_project<DIM, ARGS, BASIS>(K, args, pts, feats, cin, samples, neighbors,
-                                                                     start_ids, radii, (int)m0, (int)m1,
-                                                                     ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, s);
-        });
+        if (tc)
+            rc = launch_project_tc<ARGS, BASIS, true>(K, args, pts, planes, cin, samples, neighbors, start_ids, radii, (int)m0,
+                                                      (int)m1, ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, status, s);
+        else
+            rc = dispatch_dims<BasisTraits<BASIS>::kOnly3D>(D, [&](auto dim) {
+                constexpr int DIM = decltype(dim)::value;
+                return launch_project<DIM, ARGS, BASIS>(K, args, pts, feats, cin, samples, neighbors, start_ids, radii,
+                                                        (int)m0, (int)m1, ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, s);
+            });
         if (rc) return rc;
         if ((rc = split_bf16(rows, cout, in_grads + (size_t)m0 * cout, cout, L.ld_g, ws + L.g_hi_off, ws + L.g_lo_off, s)))
             return rc;
@@ -888,12 +975,17 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
                 PCCNN_CUDA(cudaEventRecord(weight_grads_event, s));  // dW is final from here on
             if ((rc = gemm_bf16_nt(g, w, d_proj + (size_t)j * inner_j, rows, inner_j, kp, inner, status, s))) return rc;
         }
-        rc = dispatch_dims<BasisTraits<BASIS>::kOnly3D>(D, [&](auto dim) {
-            constexpr int DIM = decltype(dim)::value;
-            return launch_backward_pairs<DIM, ARGS, BASIS>(
-                                   K, args, pts, feats, cin, samples, neighbors, start_ids, radii, (int)m0, (int)m1,
-                                   d_proj, d_feat, d_pts, d_samples, d_param0, d_param1, d_pdf, s);
-        });
+        if (tc)
+            rc = launch_backward_tc<ARGS, BASIS>(K, args, pts, planes, cin, samples, neighbors, start_ids, radii, (int)m0,
+                                                 (int)m1, d_proj, d_feat, d_pts, d_samples, d_param0, d_param1, d_pdf, status,
+                                                 s);
+        else
+            rc = dispatch_dims<BasisTraits<BASIS>::kOnly3D>(D, [&](auto dim) {
+                constexpr int DIM = decltype(dim)::value;
+                return launch_backward_pairs<DIM, ARGS, BASIS>(
+                                       K, args, pts, feats, cin, samples, neighbors, start_ids, radii, (int)m0, (int)m1,
+                                       d_proj, d_feat, d_pts, d_samples, d_param0, d_param1, d_pdf, s);
+            });
         if (rc) return rc;
     }
     return publish_status(status, kOriginConvBackward, s);
@@ -941,9 +1033,9 @@ static __global__ void finish_weight_var_kernel(const double* __restrict__ accum
     out[0] = (float)(1.0 / (accum[0] / (double)num_samples));
 }
 
-static size_t conv_weight_var_workspace(int64_t num_samples, int cin, int K) {
-    const ConvLayout L = conv_layout(num_samples, cin, K, 1);
-    return L.w_hi_off + 256;  // the two P planes + the accumulator
+static size_t conv_weight_var_workspace(int64_t num_pts, int64_t num_samples, int cin, int K) {
+    const ConvLayout L = conv_layout(num_pts, num_samples, cin, K, 1);
+    return L.w_hi_off + 256 + 2 * feature_plane_bytes(num_pts, cin);  // the two P planes, the accumulator, the feature planes
 }
 
 template <class ARGS, template <int, int> class BASIS>
@@ -955,24 +1047,34 @@ static int conv_weight_var(const char* who, int D, int K, const ARGS& args, int6
     PCCNN_CHECK_ARG(K >= 1 && K <= 64, "%s: basis size %d outside [1, 64]", who, K);
     PCCNN_CHECK_ARG(cin >= 1 && num_samples >= 1 && num_samples < 0x7fffffffLL && num_pts >= 0, "%s: bad sizes", who);
     PCCNN_CHECK_ARG(pts && feats && samples && start_ids && radii && out_variance, "%s: null pointer", who);
-    const ConvLayout L = conv_layout(num_samples, cin, K, 1);
-    const size_t need = conv_weight_var_workspace(num_samples, cin, K);
+    const ConvLayout L = conv_layout(num_pts, num_samples, cin, K, 1);
+    const size_t need = conv_weight_var_workspace(num_pts, num_samples, cin, K);
     if (!workspace || workspace_bytes < need) {
         set_error("%s: workspace of %zu bytes, need %zu", who, workspace_bytes, need);
         return PCCNN_ERR_WORKSPACE;
     }
     char* ws = (char*)workspace;
     double* accum = (double*)(ws + L.w_hi_off);
-    PCCNN_CUDA(cudaMemsetAsync(accum, 0, 8, s));
+    PCCNN_CUDA(cudaMemsetAsync(accum, 0, 128, s));  // the accumulator and, 64 bytes on, the status word of the kernels
+    const bool tc = use_tensor_core_pairs(D, cin);
+    const size_t plane = feature_plane_bytes(num_pts, cin);
+    const FeaturePlanes planes{(const __nv_bfloat16*)(ws + L.w_hi_off + 256), (const __nv_bfloat16*)(ws + L.w_hi_off + 256 + plane),
+                               L.ld_f};
+    if (tc)
+        if (int rc = split_features(num_pts, cin, feats, ws + L.w_hi_off + 256, ws + L.w_hi_off + 256 + plane, s)) return rc;
     for (int64_t m0 = 0; m0 < num_samples; m0 += L.chunk) {
         const int64_t m1 = (m0 + L.chunk < num_samples) ? m0 + L.chunk : num_samples;
         int rc = PCCNN_OK;
-        rc = dispatch_dims<BasisTraits<BASIS>::kOnly3D>(D, [&](auto dim) {
-            constexpr int DIM = decltype(dim)::value;
-            return launch_project<DIM, ARGS, BASIS>(K, args, pts, feats, cin, samples, neighbors,
-                                                                     start_ids, radii, (int)m0, (int)m1,
-                                                                     ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, s);
-        });
+        if (tc)
+            rc = launch_project_tc<ARGS, BASIS, true>(K, args, pts, planes, cin, samples, neighbors, start_ids, radii, (int)m0,
+                                                      (int)m1, ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p,
+                                                      (int*)(ws + L.w_hi_off + 64), s);
+        else
+            rc = dispatch_dims<BasisTraits<BASIS>::kOnly3D>(D, [&](auto dim) {
+                constexpr int DIM = decltype(dim)::value;
+                return launch_project<DIM, ARGS, BASIS>(K, args, pts, feats, cin, samples, neighbors, start_ids, radii,
+                                                        (int)m0, (int)m1, ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, s);
+            });
         if (rc) return rc;
         row_sq_norm_kernel<<<grid_for((m1 - m0) * 32, 256, 8), 256, 0, s>>>(
             (int)(m1 - m0), L.ld_p, (const __nv_bfloat16*)(ws + L.p_hi_off), (const __nv_bfloat16*)(ws + L.p_lo_off),
@@ -981,7 +1083,7 @@ static int conv_weight_var(const char* who, int D, int K, const ARGS& args, int6
     }
     finish_weight_var_kernel<<<1, 1, 0, s>>>(accum, (long long)num_samples, out_variance);
     PCCNN_LAUNCH_CHECK();
-    return PCCNN_OK;
+    return publish_status((const int*)(ws + L.w_hi_off + 64), kOriginWeightVar, s);
 }
 
 }  // namespace pccnn

@@ -1,0 +1,701 @@
+// Pair-level contractions of the convolutions on the tensor cores (3-D points).
+//
+// The projection P[m, c, k] = sum_t F[n0(t), c] b[t, k] of the reference (pcconvs/shared/feat_basis_proj.cu:30-129
+// of phermosilla/pccnn_lib) and the two contractions of its backward (feat_basis_proj_grads.cu:32-154)
+//     dF[n0(t), c] += sum_k dP[m, c, k] b[t, k]          db[t, k] = sum_c dP[m, c, k] F[n0(t), c]
+// are, per sample, small matrix products over the sample's neighbors.  The kernels here run them with tcgen05.mma:
+// a CTA takes one sample at a time, its threads gather the neighbors' feature rows (once, as bf16 hi + lo planes) and
+// evaluate the basis into 128-byte-swizzled shared-memory tiles, one thread issues the MMAs into tensor memory,
+// and all threads read the result back (tcgen05.ld) for the epilogue.  Compared with the CUDA-core kernels of
+// conv_impl.cuh the arithmetic per pair drops from ~70 (forward) / ~230 (backward) warp instructions to the few
+// that move the pair's data.
+//
+// Shared-memory tiles (every operand is a K-major or MN-major SW128 tile, the layouts gemm.cu already uses):
+//   F   [128 neighbors x 128 channels]  two 64-channel blocks of [128 rows x 128 B], hi and lo planes.
+//       forward:  A operand, MN-major (M = channel, K = neighbor);  backward db: A operand, K-major (M = neighbor,
+//       K = channel) -- the same bytes, two descriptor views.
+//   BT  [NB basis x 128 neighbors]      forward B operand, K-major (N = basis, K = neighbor).
+//   BM  [128 neighbors x 64 (NB used)]  backward dF A operand, K-major (M = neighbor, K = basis), rows padded to 128 B.
+//   GP  [NB basis x 128 channels]       backward db B operand, K-major (N = basis, K = channel).
+//   GQ  [128 channels x 64 (NB used)]   backward dF B operand, K-major (N = channel, K = basis), rows padded to 128 B.
+// fp32 accuracy comes from the hi/lo split of both factors (three MMAs per product, lo * lo dropped).
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+namespace pccnn {
+
+constexpr int kTcRows = 128;  // neighbors per pass of a sample
+constexpr int kTcChan = 128;  // channels per pass
+
+__device__ __forceinline__ uint32_t pack_bf16x2(__nv_bfloat16 a, __nv_bfloat16 b) {
+    return (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+}
+
+// hi / lo bf16 parts of four floats, packed as two 32-bit words each
+__device__ __forceinline__ void split4(const float (&v)[4], uint2& hi, uint2& lo) {
+    __nv_bfloat16 h[4], l[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        h[i] = __float2bfloat16_rn(v[i]);
+        l[i] = __float2bfloat16_rn(v[i] - __bfloat162float(h[i]));
+    }
+    hi = make_uint2(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]));
+    lo = make_uint2(pack_bf16x2(l[0], l[1]), pack_bf16x2(l[2], l[3]));
+}
+
+// Features reach the pair kernels as bf16 planes (hi, and lo for fp32 inputs) with rows padded to a multiple of 8
+// channels, so that a neighbor's row is a sequence of 16-byte chunks that can be copied without passing through
+// registers.  fp32 features are split once per operator call (split_features below); bf16 features are used as they are.
+struct FeaturePlanes {
+    const __nv_bfloat16* hi;
+    const __nv_bfloat16* lo;  // null: single plane
+    int ld;                   // elements per row, a multiple of 8
+};
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+    // 16 bytes global -> shared without registers; src-size 0 writes zeros instead
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Starts the copies of the feature rows of the staged neighbors (s_n0[0 .. rows), -1 = no neighbor) for the channels
+// [cb, cb + 128) into the F tile: warp w takes rows w, w + 4, ...; with two planes lanes 0-15 copy the 16 chunks of
+// the hi plane and lanes 16-31 those of the lo plane (one warp instruction per row); with one plane the two half
+// warps take two rows.  Chunks past the row's end and rows without a neighbor are zero-filled.  Asynchronous: the
+// caller waits (cp_async_wait_all) before the tile is used.
+template <bool SPLIT_F>
+__device__ __forceinline__ void gather_features_async(uint32_t f_hi, uint32_t f_lo, const int* s_n0, int rows,
+                                                      const FeaturePlanes& f, int cb) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunk = lane & 15;       // 8 channels
+    const int c = cb + 8 * chunk;
+    const uint32_t in_tile = (uint32_t)(chunk >> 3) * (kTcRows * 128);
+    if (SPLIT_F) {
+        const __nv_bfloat16* plane = (lane < 16) ? f.hi : f.lo;
+        const uint32_t tile = (lane < 16) ? f_hi : f_lo;
+        for (int r = warp; r < rows; r += 4) {
+            const int n0 = s_n0[r];
+            const bool valid = n0 >= 0 && c < f.ld;
+            cp_async_16(tile + in_tile + sw128_offset(r, chunk & 7), plane + (valid ? (int64_t)n0 * f.ld + c : 0), valid);
+        }
+    } else {
+        for (int r = 2 * warp + (lane >> 4); r < rows; r += 8) {
+            const int n0 = s_n0[r];
+            const bool valid = n0 >= 0 && c < f.ld;
+            cp_async_16(f_hi + in_tile + sw128_offset(r, chunk & 7), f.hi + (valid ? (int64_t)n0 * f.ld + c : 0), valid);
+        }
+    }
+}
+
+// fp32 [rows, cin] -> bf16 hi / lo planes [rows, ld] (ld = cin rounded up to 8, zero padded)
+static __global__ void __launch_bounds__(256)
+split_features_kernel(int64_t rows, int cin, int ld, const float* __restrict__ src, __nv_bfloat16* __restrict__ hi,
+                      __nv_bfloat16* __restrict__ lo) {
+    const int64_t total = rows * (ld / 8);
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t r = i / (ld / 8);
+        const int c = (int)(i - r * (ld / 8)) * 8;
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = (c + e < cin) ? __ldg(src + r * cin + c + e) : 0.f;
+        uint32_t hw[4], lw[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+            const __nv_bfloat162 l2 = __floats2bfloat162_rn(v[2 * q] - __low2float(h2), v[2 * q + 1] - __high2float(h2));
+            hw[q] = *reinterpret_cast<const uint32_t*>(&h2);
+            lw[q] = *reinterpret_cast<const uint32_t*>(&l2);
+        }
+        *reinterpret_cast<uint4*>(hi + r * ld + c) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        *reinterpret_cast<uint4*>(lo + r * ld + c) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+    }
+}
+
+static int split_features(int64_t rows, int cin, const float* src, void* hi, void* lo, cudaStream_t s) {
+    if (rows == 0) return PCCNN_OK;
+    const int ld = (cin + 7) / 8 * 8;
+    split_features_kernel<<<grid_for(rows * (ld / 8), 256, 8), 256, 0, s>>>(rows, cin, ld, src, (__nv_bfloat16*)hi,
+                                                                            (__nv_bfloat16*)lo);
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
+template <int NB>
+struct TcForwardSmem {
+    static constexpr int kF = 2 * kTcRows * 128;  // one plane of the F tile: 32 KB
+    static constexpr int kBT = 2 * NB * 128;      // one plane of the BT tile: two 64-neighbor blocks of [NB x 128 B]
+    static constexpr int kFHi = 0, kFLo = kF, kBTHi = 2 * kF, kBTLo = 2 * kF + kBT;
+    static constexpr int kTiles = 2 * kF + 2 * kBT;
+    static constexpr int kMisc = 2048;  // barrier, tensor-memory slot, neighbor ids, basis parameters
+    static constexpr int kBytes = kTiles + kMisc;
+};
+
+// P rows (bf16 hi [+ lo]) of the samples [m_begin, m_end).  One CTA = one sample at a time.
+template <int NB, class BASIS, class ARGS, bool SPLIT_F>
+__global__ void __launch_bounds__(128)
+project_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes feats, int cin,
+                  const float* __restrict__ samples, const int2* __restrict__ neighbors,
+                  const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
+                  __nv_bfloat16* __restrict__ p_hi, __nv_bfloat16* __restrict__ p_lo, int ld_p, uint32_t poll_limit,
+                  int* __restrict__ status) {
+    using SM = TcForwardSmem<NB>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];  // the swizzled tiles need 1024-byte alignment
+    uint8_t* smem = smem_raw;
+    uint8_t* misc = smem + SM::kTiles;
+    uint64_t* bar = (uint64_t*)misc;
+    uint32_t* tmem_slot = (uint32_t*)(misc + 8);
+    int* s_fail = (int*)(misc + 12);
+    int* s_n0 = (int*)(misc + 64);              // [128]
+    float* s_params = (float*)(misc + 64 + 512);  // up to 256 floats
+    static_assert(BASIS::kParamFloats <= 256, "basis parameters do not fit the shared-memory slot");
+    constexpr uint32_t kTmemCols = NB < 32 ? 32 : NB;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        *s_fail = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    BASIS::load_params(s_params, args, K);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    float inv[3];
+#pragma unroll
+    for (int d = 0; d < 3; ++d) inv[d] = BASIS::kUsesOffset ? __frcp_rn(__ldg(radii + d)) : 0.f;
+    const int inner = cin * K;
+    const uint32_t f_hi = smem_u32(smem + SM::kFHi), f_lo = smem_u32(smem + SM::kFLo);
+    const uint32_t bt_hi = smem_u32(smem + SM::kBTHi), bt_lo = smem_u32(smem + SM::kBTLo);
+    // fp32 accumulate, bf16 x bf16, A MN-major (bit 15), B K-major, N = NB, M = 128
+    constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)(NB >> 3) << 17) |
+                               ((uint32_t)(128 >> 4) << 24);
+    uint32_t parity = 0;
+    bool failed = false;
+
+    for (int m = m_begin + blockIdx.x; m < m_end && !failed; m += gridDim.x) {
+        const int lo = (m > 0) ? __ldg(start_ids + m - 1) : 0;
+        const int hi = __ldg(start_ids + m);
+        float s[3];
+#pragma unroll
+        for (int d = 0; d < 3; ++d) s[d] = BASIS::kUsesOffset ? __ldg(samples + (int64_t)m * 3 + d) : 0.f;
+        const size_t row = (size_t)(m - m_begin) * ld_p;
+
+        for (int cb = 0; cb < cin && !failed; cb += kTcChan) {
+            bool first = true;
+            for (int t0 = lo; t0 < hi; t0 += kTcRows) {
+                const int cnt = min(kTcRows, hi - t0);
+                const int rows = (cnt + 15) & ~15;
+                // ---- the neighbor of this thread; the copies of all feature rows start as soon as the ids are staged
+                const int t = t0 + tid;
+                const int n0 = (tid < cnt) ? __ldg(&neighbors[t]).x : -1;
+                s_n0[tid] = n0;
+                __syncthreads();
+                gather_features_async<SPLIT_F>(f_hi, f_lo, s_n0, rows, feats, cb);
+                // ---- lanes as neighbors, while the copies are in flight: offset, basis, BT column of pair t0 + tid
+                {
+                    float b[NB];
+                    if (tid < cnt) {
+                        float d[3];
+#pragma unroll
+                        for (int x = 0; x < 3; ++x)
+                            d[x] = BASIS::kUsesOffset ? (__ldg(pts + (int64_t)n0 * 3 + x) - s[x]) * inv[x] : 0.f;
+                        BASIS::eval(s_params, args, K, d, n0, t, m, b);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < NB; ++k) b[k] = 0.f;
+                    }
+                    if (tid < rows) {
+                        uint8_t* base_hi = smem + SM::kBTHi + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                        uint8_t* base_lo = smem + SM::kBTLo + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                        const int chunk = (tid & 63) >> 3;
+#pragma unroll
+                        for (int k = 0; k < NB; ++k) {
+                            const __nv_bfloat16 h = __float2bfloat16_rn(b[k]);
+                            const uint32_t off = sw128_offset(k, chunk);
+                            *reinterpret_cast<__nv_bfloat16*>(base_hi + off) = h;
+                            *reinterpret_cast<__nv_bfloat16*>(base_lo + off) = __float2bfloat16_rn(b[k] - __bfloat162float(h));
+                        }
+                    }
+                }
+                cp_async_wait_all();
+                fence_smem_to_async_proxy();
+                __syncthreads();
+                if (tid == 0) {
+                    tc_fence_after();
+                    for (int kb = 0; kb < rows / 16; ++kb) {
+                        // A: 16 neighbor rows further = 2048 bytes = +128 in 16-byte units; the two 64-channel blocks
+                        // are 16 KB apart (leading byte offset).  B: 64-neighbor block kb / 4, 16 neighbors = +2.
+                        const uint64_t a_hi = umma_desc_mn_sw128(f_hi, kTcRows * 128) + 128ull * kb;
+                        const uint64_t b_off = (uint64_t)(kb >> 2) * ((NB * 128) >> 4) + 2ull * (kb & 3);
+                        const uint64_t b_hi = umma_desc_k_sw128(bt_hi) + b_off, b_lo = umma_desc_k_sw128(bt_lo) + b_off;
+                        tc_mma_bf16(tmem_base, a_hi, b_hi, idesc, (!first || kb > 0) ? 1u : 0u);
+                        tc_mma_bf16(tmem_base, a_hi, b_lo, idesc, 1u);
+                        if (SPLIT_F) {
+                            const uint64_t a_lo = umma_desc_mn_sw128(f_lo, kTcRows * 128) + 128ull * kb;
+                            tc_mma_bf16(tmem_base, a_lo, b_hi, idesc, 1u);
+                        }
+                    }
+                    tc_commit(bar);
+                }
+                // one thread polls for the MMAs (they have read the tiles, which the next pass overwrites); the others
+                // wait at the block barrier, which costs no issue slots
+                const bool ok = (tid != 0) || mbar_wait(bar, parity, poll_limit);
+                parity ^= 1u;
+                if (__syncthreads_or(ok ? 0 : 1)) {
+                    failed = true;
+                    break;
+                }
+                first = false;
+            }
+            if (failed) break;
+            // ---- epilogue: thread = channel cb + tid, NB accumulator columns -> K entries of the P row
+            tc_fence_after();
+            const int c = cb + tid;
+            float acc[NB];
+            if (first) {  // no neighbor at all: the accumulator was never written
+#pragma unroll
+                for (int k = 0; k < NB; ++k) acc[k] = 0.f;
+            } else {
+#pragma unroll
+                for (int k0 = 0; k0 < NB; k0 += 16) {
+                    uint32_t r[16];
+                    tc_ld_32x16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)k0, r);
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) acc[k0 + k] = __uint_as_float(r[k]);
+                }
+            }
+            if (c < cin) {
+                if (K == NB) {
+#pragma unroll
+                    for (int k = 0; k < NB; k += 8) {
+                        uint32_t hw[4], lw[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float v0 = acc[k + 2 * q], v1 = acc[k + 2 * q + 1];
+                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+                            const __nv_bfloat162 l2 = __floats2bfloat162_rn(v0 - __low2float(h2), v1 - __high2float(h2));
+                            hw[q] = *reinterpret_cast<const uint32_t*>(&h2);
+                            lw[q] = *reinterpret_cast<const uint32_t*>(&l2);
+                        }
+                        *reinterpret_cast<uint4*>(p_hi + row + (size_t)c * K + k) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                        if (p_lo) *reinterpret_cast<uint4*>(p_lo + row + (size_t)c * K + k) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < NB; ++k) {
+                        if (k < K) {
+                            const __nv_bfloat16 h = __float2bfloat16_rn(acc[k]);
+                            p_hi[row + (size_t)c * K + k] = h;
+                            if (p_lo) p_lo[row + (size_t)c * K + k] = __float2bfloat16_rn(acc[k] - __bfloat162float(h));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncthreads();  // the accumulator is free for the next channel block / sample
+        }
+        // padding columns feed the contraction too: keep them zero
+        for (int c = inner + tid; c < ld_p; c += 128) {
+            p_hi[row + c] = __float2bfloat16_rn(0.f);
+            if (p_lo) p_lo[row + c] = __float2bfloat16_rn(0.f);
+        }
+    }
+    if (failed && tid == 0) {
+        atomicExch(status, 5);
+        mbar_wait(bar, parity ^ 1u, poll_limit);  // once more, bounded: MMAs still in flight must not outlive tensor memory
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+template <int NB>
+struct TcBackwardSmem {
+    static constexpr int kF = 2 * kTcRows * 128;   // F plane: 32 KB
+    static constexpr int kBM = kTcRows * 128;      // BM plane: 16 KB (rows padded to 128 bytes)
+    static constexpr int kGP = 2 * NB * 128;       // GP plane: two 64-channel blocks of [NB x 128 B]
+    static constexpr int kGQ = kTcChan * 128;      // GQ plane: 16 KB
+    static constexpr int kFHi = 0, kFLo = kF, kBMHi = 2 * kF, kBMLo = kBMHi + kBM, kGPHi = kBMLo + kBM,
+                         kGPLo = kGPHi + kGP, kGQHi = kGPLo + kGP, kGQLo = kGQHi + kGQ;
+    static constexpr int kTiles = kGQLo + kGQ;
+    static constexpr int kMisc = 4096;  // barrier, tensor-memory slot, neighbor ids, basis parameters, parameter gradients
+    static constexpr int kBytes = kTiles + kMisc;
+};
+
+__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Everything of the backward pass that runs per neighbor pair, given dP = g W^T (rows of `inner` floats) for the
+// samples [m_begin, m_end): dF (reduced into d_feat), db -> basis / offset / point / parameter gradients.
+// Thread r of the CTA owns neighbor r of the current pass in the "lanes as neighbors" stages and channel cb + r in
+// the "lanes as channels" stage that lays out the sample's dP row.
+template <int NB, class BASIS, class ARGS>
+__global__ void __launch_bounds__(128)
+backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes feats, int cin,
+                   const float* __restrict__ samples, const int2* __restrict__ neighbors,
+                   const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
+                   const float* __restrict__ d_proj, float* __restrict__ d_feat, float* __restrict__ d_pts,
+                   float* __restrict__ d_samples, float* __restrict__ d_param0, float* __restrict__ d_param1,
+                   float* __restrict__ d_pdf, uint32_t poll_limit, int* __restrict__ status) {
+    using SM = TcBackwardSmem<NB>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];  // the swizzled tiles need 1024-byte alignment
+    uint8_t* smem = smem_raw;
+    uint8_t* misc = smem + SM::kTiles;
+    uint64_t* bar = (uint64_t*)misc;
+    uint32_t* tmem_slot = (uint32_t*)(misc + 8);
+    int* s_n0 = (int*)(misc + 64);                     // [128]
+    float* s_params = (float*)(misc + 64 + 512);       // up to 256 floats
+    float* s_grad = (float*)(misc + 64 + 512 + 1024);  // up to 256 floats
+    static_assert(BASIS::kParamFloats <= 256 && BASIS::kGradFloats <= 256, "basis parameters do not fit their slots");
+    constexpr uint32_t kTmemCols = 256;  // db in columns [0, NB), dF in columns [128, 256)
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    BASIS::load_params(s_params, args, K);
+    for (int i = tid; i < BASIS::kGradFloats; i += 128) s_grad[i] = 0.f;
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    float inv[3];
+#pragma unroll
+    for (int d = 0; d < 3; ++d) inv[d] = BASIS::kUsesOffset ? __frcp_rn(__ldg(radii + d)) : 0.f;
+    const int inner = cin * K;
+    const bool vec = (cin & 3) == 0;
+    const uint32_t f_hi = smem_u32(smem + SM::kFHi), f_lo = smem_u32(smem + SM::kFLo);
+    const uint32_t bm_hi = smem_u32(smem + SM::kBMHi), bm_lo = smem_u32(smem + SM::kBMLo);
+    const uint32_t gp_hi = smem_u32(smem + SM::kGPHi), gp_lo = smem_u32(smem + SM::kGPLo);
+    const uint32_t gq_hi = smem_u32(smem + SM::kGQHi), gq_lo = smem_u32(smem + SM::kGQLo);
+    // fp32 accumulate, bf16 x bf16, both operands K-major, M = 128
+    constexpr uint32_t idesc_db = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    constexpr uint32_t idesc_df = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    uint32_t parity = 0;
+    bool failed = false;
+    // Parameter gradients: with a small basis every thread keeps its own partial sums in registers and the block
+    // reduces them once at the end; a chain of warp reductions per pass would dominate a kernel that has only
+    // four warps to hide it.  Larger bases reduce per pass in shared memory.
+    constexpr bool kLocalGrads = NB <= 16;
+    float g_acc[kLocalGrads ? BASIS::kGradFloats : 1];
+#pragma unroll
+    for (int i = 0; i < (kLocalGrads ? BASIS::kGradFloats : 1); ++i) g_acc[i] = 0.f;
+
+    for (int m = m_begin + blockIdx.x; m < m_end && !failed; m += gridDim.x) {
+        const int lo = (m > 0) ? __ldg(start_ids + m - 1) : 0;
+        const int hi = __ldg(start_ids + m);
+        float s[3], ds_acc[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+        for (int d = 0; d < 3; ++d) s[d] = BASIS::kUsesOffset ? __ldg(samples + (int64_t)m * 3 + d) : 0.f;
+        const float* grow = d_proj + (size_t)(m - m_begin) * inner;
+
+        for (int t0 = lo; t0 < hi && !failed; t0 += kTcRows) {
+            const int cnt = min(kTcRows, hi - t0);
+            // ---- lanes as neighbors: offset and basis of pair t0 + tid, BM row tid
+            const int t = t0 + tid;
+            const bool active = tid < cnt;
+            int n0 = -1;
+            float d[3] = {0.f, 0.f, 0.f};
+            {
+                float b[NB];
+                if (active) {
+                    n0 = __ldg(&neighbors[t]).x;
+#pragma unroll
+                    for (int x = 0; x < 3; ++x)
+                        d[x] = BASIS::kUsesOffset ? (__ldg(pts + (int64_t)n0 * 3 + x) - s[x]) * inv[x] : 0.f;
+                    BASIS::eval(s_params, args, K, d, n0, t, m, b);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < NB; ++k) b[k] = 0.f;
+                }
+                s_n0[tid] = n0;
+#pragma unroll
+                for (int j = 0; j < NB / 8; ++j) {
+                    uint32_t hw[4], lw[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float v0 = b[8 * j + 2 * q], v1 = b[8 * j + 2 * q + 1];
+                        const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+                        const __nv_bfloat162 l2 = __floats2bfloat162_rn(v0 - __low2float(h2), v1 - __high2float(h2));
+                        hw[q] = *reinterpret_cast<const uint32_t*>(&h2);
+                        lw[q] = *reinterpret_cast<const uint32_t*>(&l2);
+                    }
+                    const uint32_t off = sw128_offset(tid, j);
+                    *reinterpret_cast<uint4*>(smem + SM::kBMHi + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                    *reinterpret_cast<uint4*>(smem + SM::kBMLo + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+                }
+            }
+            __syncthreads();
+
+            for (int cb = 0; cb < cin; cb += kTcChan) {
+                gather_features_async<true>(f_hi, f_lo, s_n0, cnt, feats, cb);
+                // ---- lanes as channels: the dP entries of channel cb + tid -> GQ row tid and GP column tid
+                {
+                    const int c = cb + tid;
+                    float g[NB];
+                    if (c < cin) {
+                        if (K == NB) {
+#pragma unroll
+                            for (int k = 0; k < NB; k += 4) {
+                                const float4 v = __ldg(reinterpret_cast<const float4*>(grow + (size_t)c * K + k));
+                                g[k] = v.x; g[k + 1] = v.y; g[k + 2] = v.z; g[k + 3] = v.w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int k = 0; k < NB; ++k) g[k] = (k < K) ? __ldg(grow + (size_t)c * K + k) : 0.f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < NB; ++k) g[k] = 0.f;
+                    }
+                    uint8_t* gp_base_hi = smem + SM::kGPHi + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                    uint8_t* gp_base_lo = smem + SM::kGPLo + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                    const int chunk = (tid & 63) >> 3;
+#pragma unroll
+                    for (int j = 0; j < NB / 8; ++j) {
+                        uint32_t hw[4], lw[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float v0 = g[8 * j + 2 * q], v1 = g[8 * j + 2 * q + 1];
+                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+                            const __nv_bfloat162 l2 = __floats2bfloat162_rn(v0 - __low2float(h2), v1 - __high2float(h2));
+                            hw[q] = *reinterpret_cast<const uint32_t*>(&h2);
+                            lw[q] = *reinterpret_cast<const uint32_t*>(&l2);
+                            // the same values, transposed: (row k, column = this channel) of GP
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int k = 8 * j + 2 * q + e;
+                                const uint32_t off = sw128_offset(k, chunk);
+                                *reinterpret_cast<__nv_bfloat16*>(gp_base_hi + off) = e ? __high2bfloat16(h2) : __low2bfloat16(h2);
+                                *reinterpret_cast<__nv_bfloat16*>(gp_base_lo + off) = e ? __high2bfloat16(l2) : __low2bfloat16(l2);
+                            }
+                        }
+                        const uint32_t off = sw128_offset(tid, j);
+                        *reinterpret_cast<uint4*>(smem + SM::kGQHi + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                        *reinterpret_cast<uint4*>(smem + SM::kGQLo + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+                    }
+                }
+                cp_async_wait_all();
+                fence_smem_to_async_proxy();
+                __syncthreads();
+                if (tid == 0) {
+                    tc_fence_after();
+                    // db[neighbor, k] (+)= F[neighbor, c] * dP[c, k]: 8 steps of 16 channels, accumulated over the blocks
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint64_t a_off = (uint64_t)(ks >> 2) * ((kTcRows * 128) >> 4) + 2ull * (ks & 3);
+                        const uint64_t b_off = (uint64_t)(ks >> 2) * ((NB * 128) >> 4) + 2ull * (ks & 3);
+                        const uint64_t a_hi = umma_desc_k_sw128(f_hi) + a_off, a_lo = umma_desc_k_sw128(f_lo) + a_off;
+                        const uint64_t b_hi = umma_desc_k_sw128(gp_hi) + b_off, b_lo = umma_desc_k_sw128(gp_lo) + b_off;
+                        tc_mma_bf16(tmem_base, a_hi, b_hi, idesc_db, (cb > 0 || ks > 0) ? 1u : 0u);
+                        tc_mma_bf16(tmem_base, a_lo, b_hi, idesc_db, 1u);
+                        tc_mma_bf16(tmem_base, a_hi, b_lo, idesc_db, 1u);
+                    }
+                    // dF[neighbor, c] = b[neighbor, k] * dP[c, k]: NB / 16 steps
+#pragma unroll
+                    for (int ks = 0; ks < NB / 16; ++ks) {
+                        const uint64_t a_hi = umma_desc_k_sw128(bm_hi) + 2ull * ks, a_lo = umma_desc_k_sw128(bm_lo) + 2ull * ks;
+                        const uint64_t b_hi = umma_desc_k_sw128(gq_hi) + 2ull * ks, b_lo = umma_desc_k_sw128(gq_lo) + 2ull * ks;
+                        tc_mma_bf16(tmem_base + 128, a_hi, b_hi, idesc_df, ks > 0 ? 1u : 0u);
+                        tc_mma_bf16(tmem_base + 128, a_lo, b_hi, idesc_df, 1u);
+                        tc_mma_bf16(tmem_base + 128, a_hi, b_lo, idesc_df, 1u);
+                    }
+                    tc_commit(bar);
+                }
+                const bool ok = (tid != 0) || mbar_wait(bar, parity, poll_limit);
+                parity ^= 1u;
+                if (__syncthreads_or(ok ? 0 : 1)) {
+                    failed = true;
+                    break;
+                }
+                tc_fence_after();
+                // ---- dF row of this neighbor, 32 channels at a time, reduced into the feature gradient
+#pragma unroll 1
+                for (int c0 = 0; c0 < kTcChan && cb + c0 < cin; c0 += 32) {
+                    uint32_t r[32];
+                    tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + 128u + (uint32_t)c0, r);
+                    if (active) {
+                        float* dst = d_feat + (int64_t)n0 * cin + cb + c0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            if (vec && cb + c0 + j + 3 < cin) {
+                                red_add_f32x4(dst + j, __uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (cb + c0 + j + e < cin) atomicAdd(dst + j + e, __uint_as_float(r[j + e]));
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncthreads();  // the tiles and the dF accumulator are free for the next channel block
+            }
+            if (failed) break;
+
+            // ---- lanes as neighbors again: db row -> basis gradient, offset gradient, point gradients
+            float db[NB];
+            tc_fence_after();
+#pragma unroll
+            for (int k0 = 0; k0 < NB; k0 += 16) {
+                uint32_t r[16];
+                tc_ld_32x16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)k0, r);
+#pragma unroll
+                for (int k = 0; k < 16; ++k) db[k0 + k] = active ? __uint_as_float(r[k]) : 0.f;
+            }
+            float d_off[3] = {0.f, 0.f, 0.f}, dpdf = 0.f;
+            if constexpr (kLocalGrads)
+                BASIS::grad_local(s_params, args, K, d, max(n0, 0), t, m, active, db, d_off, g_acc, dpdf);
+            else
+                BASIS::grad(s_params, args, K, d, max(n0, 0), t, m, active, db, d_off, s_grad, dpdf);
+            if (active) {
+#pragma unroll
+                for (int x = 0; x < 3; ++x) {
+                    const float gx = d_off[x] * inv[x];
+                    if (d_pts && gx != 0.f) atomicAdd(d_pts + (int64_t)n0 * 3 + x, gx);
+                    ds_acc[x] += gx;
+                }
+                if (d_pdf && dpdf != 0.f) atomicAdd(d_pdf + n0, dpdf);
+            }
+            tc_fence_before();
+            __syncthreads();  // db accumulator and BM tile are free for the next pass
+        }
+        if (d_samples) {
+#pragma unroll
+            for (int x = 0; x < 3; ++x) {
+                const float tot = warp_sum(ds_acc[x]);
+                if (lane == 0 && tot != 0.f) atomicAdd(d_samples + (int64_t)m * 3 + x, -tot);
+            }
+        }
+    }
+    if (failed && tid == 0) {
+        atomicExch(status, 6);
+        mbar_wait(bar, parity ^ 1u, poll_limit);
+    }
+    if constexpr (kLocalGrads) {
+#pragma unroll
+        for (int i = 0; i < BASIS::kGradFloats; ++i) {
+            const float tot = warp_sum(g_acc[i]);
+            if (lane == 0 && tot != 0.f) atomicAdd(s_grad + i, tot);
+        }
+    }
+    __syncthreads();
+    BASIS::flush(s_grad, K, d_param0, d_param1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+// Poll limit of the bounded waits (gemm.cu owns it, together with the test hook that shortens it).
+uint32_t tensor_core_poll_limit();
+
+template <int NB, class BASIS, class ARGS, bool SPLIT_F>
+static int launch_project_tc_nb(int K, const ARGS& args, const float* pts, const FeaturePlanes& feats, int cin, const float* samples,
+                                const int32_t* neighbors, const int32_t* start_ids, const float* radii, int m_begin,
+                                int m_end, void* p_hi, void* p_lo, int ld_p, int* status, cudaStream_t s) {
+    auto kernel = project_tc_kernel<NB, BASIS, ARGS, SPLIT_F>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcForwardSmem<NB>::kBytes);
+    });
+    PCCNN_CUDA(attr_err);
+    const int per_sm = (227 * 1024) / (TcForwardSmem<NB>::kBytes + 1024);
+    const int64_t cap = (int64_t)sm_count() * (per_sm < 1 ? 1 : per_sm);
+    const int count = m_end - m_begin;
+    const unsigned grid = (unsigned)(count < cap ? count : cap);
+    kernel<<<grid, 128, TcForwardSmem<NB>::kBytes, s>>>(args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids,
+                                                        radii, m_begin, m_end, (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo,
+                                                        ld_p, tensor_core_poll_limit(), status);
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
+// Tensor-core projection of the samples [m_begin, m_end) (3-D points, K <= 64).
+template <class ARGS, template <int, int> class BASIS, bool SPLIT_F>
+static int launch_project_tc(int K, const ARGS& args, const float* pts, const FeaturePlanes& feats, int cin, const float* samples,
+                             const int32_t* neighbors, const int32_t* start_ids, const float* radii, int m_begin,
+                             int m_end, void* p_hi, void* p_lo, int ld_p, int* status, cudaStream_t s) {
+    if (m_end <= m_begin) return PCCNN_OK;
+    if (K <= 16)
+        return launch_project_tc_nb<16, BASIS<3, 16>, ARGS, SPLIT_F>(K, args, pts, feats, cin, samples, neighbors, start_ids,
+                                                                         radii, m_begin, m_end, p_hi, p_lo, ld_p, status, s);
+    if (K <= 32)
+        return launch_project_tc_nb<32, BASIS<3, 32>, ARGS, SPLIT_F>(K, args, pts, feats, cin, samples, neighbors, start_ids,
+                                                                         radii, m_begin, m_end, p_hi, p_lo, ld_p, status, s);
+    return launch_project_tc_nb<64, BASIS<3, 64>, ARGS, SPLIT_F>(K, args, pts, feats, cin, samples, neighbors, start_ids,
+                                                                     radii, m_begin, m_end, p_hi, p_lo, ld_p, status, s);
+}
+
+template <int NB, class BASIS, class ARGS>
+static int launch_backward_tc_nb(int K, const ARGS& args, const float* pts, const FeaturePlanes& feats, int cin,
+                                 const float* samples, const int32_t* neighbors, const int32_t* start_ids,
+                                 const float* radii, int m_begin, int m_end, const float* d_proj, float* d_feat,
+                                 float* d_pts, float* d_samples, float* d_param0, float* d_param1, float* d_pdf,
+                                 int* status, cudaStream_t s) {
+    auto kernel = backward_tc_kernel<NB, BASIS, ARGS>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcBackwardSmem<NB>::kBytes);
+    });
+    PCCNN_CUDA(attr_err);
+    const int count = m_end - m_begin;
+    const unsigned grid = (unsigned)(count < sm_count() ? count : sm_count());
+    kernel<<<grid, 128, TcBackwardSmem<NB>::kBytes, s>>>(args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids,
+                                                         radii, m_begin, m_end, d_proj, d_feat, d_pts, d_samples, d_param0,
+                                                         d_param1, d_pdf, tensor_core_poll_limit(), status);
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
+template <class ARGS, template <int, int> class BASIS>
+static int launch_backward_tc(int K, const ARGS& args, const float* pts, const FeaturePlanes& feats, int cin, const float* samples,
+                              const int32_t* neighbors, const int32_t* start_ids, const float* radii, int m_begin,
+                              int m_end, const float* d_proj, float* d_feat, float* d_pts, float* d_samples,
+                              float* d_param0, float* d_param1, float* d_pdf, int* status, cudaStream_t s) {
+    if (m_end <= m_begin) return PCCNN_OK;
+    if (K <= 16)
+        return launch_backward_tc_nb<16, BASIS<3, 16>, ARGS>(K, args, pts, feats, cin, samples, neighbors, start_ids, radii,
+                                                             m_begin, m_end, d_proj, d_feat, d_pts, d_samples, d_param0,
+                                                             d_param1, d_pdf, status, s);
+    if (K <= 32)
+        return launch_backward_tc_nb<32, BASIS<3, 32>, ARGS>(K, args, pts, feats, cin, samples, neighbors, start_ids, radii,
+                                                             m_begin, m_end, d_proj, d_feat, d_pts, d_samples, d_param0,
+                                                             d_param1, d_pdf, status, s);
+    return launch_backward_tc_nb<64, BASIS<3, 64>, ARGS>(K, args, pts, feats, cin, samples, neighbors, start_ids, radii,
+                                                         m_begin, m_end, d_proj, d_feat, d_pts, d_samples, d_param0,
+                                                         d_param1, d_pdf, status, s);
+}
+
+}  // namespace pccnn

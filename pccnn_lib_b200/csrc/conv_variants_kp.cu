@@ -63,6 +63,29 @@ struct KPNBasis {
             }
         }
     }
+    __device__ static void grad_local(const float* sp, const KPDensityArgs& a, int K, const float (&d)[D], int n0, int,
+                                      int, bool active, const float* db, float (&d_off)[D], float (&acc_g)[kGradFloats],
+                                      float&) {
+        const float inv_pdf = active ? 1.0f / __ldg(a.pdf + n0) : 0.f;
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+            float v[D], acc = 0.f;
+#pragma unroll
+            for (int x = 0; x < D; ++x) {
+                v[x] = sp[k * D + x] - d[x];
+                acc = fmaf(v[x], v[x], acc);
+            }
+            const float dist = sqrtf(fmaxf(acc, 0.f));
+            float gk = 0.f;
+            if (active && k < K && 1.0f - dist * a.inv_sigma >= 0.f) gk = -db[k] * inv_pdf * a.inv_sigma / (dist + 1e-6f);
+#pragma unroll
+            for (int x = 0; x < D; ++x) {
+                const float t = gk * v[x];
+                d_off[x] -= t;
+                acc_g[k * D + x] += t;
+            }
+        }
+    }
     __device__ static void flush(const float* s_grad, int K, float* g0, float*) {
         for (int i = threadIdx.x; i < K * D; i += blockDim.x)
             if (s_grad[i] != 0.f) atomicAdd(g0 + i, s_grad[i]);
@@ -115,6 +138,30 @@ struct GaussBasis {
                 d_off[x] += t;
                 const float tot = warp_sum(t);
                 if (lane == 0) atomicAdd(s_grad + k * D + x, -tot);
+            }
+        }
+    }
+    __device__ static void grad_local(const float* sp, const KPDensityArgs& a, int K, const float (&d)[D], int n0, int,
+                                      int, bool active, const float* db, float (&d_off)[D], float (&acc_g)[kGradFloats],
+                                      float& d_pdf) {
+        const float inv_pdf = active ? 1.0f / __ldg(a.pdf + n0) : 0.f;
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+            float v[D], acc = 0.f;
+#pragma unroll
+            for (int x = 0; x < D; ++x) {
+                v[x] = sp[k * D + x] - d[x];
+                acc = fmaf(v[x], v[x], acc);
+            }
+            const float e = expf(-0.5f * acc * a.inv_sigma);
+            const float dbk = (active && k < K) ? db[k] : 0.f;
+            d_pdf -= e * dbk * inv_pdf * inv_pdf;
+            const float g = dbk * inv_pdf * e * a.inv_sigma;
+#pragma unroll
+            for (int x = 0; x < D; ++x) {
+                const float t = g * v[x];
+                d_off[x] += t;
+                acc_g[k * D + x] -= t;
             }
         }
     }

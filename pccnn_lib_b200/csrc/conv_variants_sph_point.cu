@@ -59,6 +59,8 @@ struct SphBasis {
     // The reference returns weight and feature gradients only (sphconv.cu:106): the bins are not differentiable.
     __device__ static void grad(const float*, const SphArgs&, int, const float (&)[D], int, int, int, bool, const float*,
                                 float (&)[D], float*, float&) {}
+    __device__ static void grad_local(const float*, const SphArgs&, int, const float (&)[D], int, int, int, bool,
+                                      const float*, float (&)[D], float (&)[kGradFloats], float&) {}
     __device__ static void flush(const float*, int, float*, float*) {}
 };
 template <>
@@ -87,6 +89,10 @@ struct TableBasis {
                                 const float* db, float (&)[D], float*, float&) {
         if (active)
             for (int k = 0; k < K; ++k) a.d_basis[(size_t)t * K + k] = db[k];
+    }
+    __device__ static void grad_local(const float* sp, const TableArgs& a, int K, const float (&d)[D], int n0, int t, int m,
+                                      bool active, const float* db, float (&d_off)[D], float (&)[kGradFloats], float& dp) {
+        grad(sp, a, K, d, n0, t, m, active, db, d_off, nullptr, dp);
     }
     __device__ static void flush(const float*, int, float*, float*) {}
 };

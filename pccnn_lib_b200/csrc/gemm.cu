@@ -30,85 +30,15 @@
 
 #include "common.cuh"
 #include "gemm.cuh"
+#include "tc_ptx.cuh"
 
 namespace pccnn {
 
-// ---- PTX wrappers ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
 // Poll limit of every wait (about 2^21 polls are tens of milliseconds) and a test hook: a producer that stops
 // issuing loads from a given K block on, so that a test can watch the consumers' waits run out with no copy in
 // flight.  Both are read once per kernel; pccnn_gemm_set_test_hooks changes them.
 __device__ uint32_t d_poll_limit = 1u << 21;
 __device__ int d_withhold_from = -1;
-
-// Bounded wait: false when the barrier did not flip within `limit` polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < limit; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n.reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-            "selp.u32 %0, 1, 0, p;\n}"
-            : "=r"(ok)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes, stored with the
-// 128-byte swizzle TMA produces: 8-row groups are 1024 bytes apart (stride byte offset), the
-// leading byte offset is unused for swizzled K-major tiles, descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);       // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                            // leading byte offset (ignored)
-    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
-    d |= (uint64_t)1 << 46;                            // version
-    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
-    return d;
-}
 
 // One accumulator segment of 32 columns (starting at column col0) of output row `row`: fp32 or bf16 stores,
 // 128-bit wide where the destination allows.
@@ -321,9 +251,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     }
 }
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 // Persistent form of the kernel above: one CTA per SM walks the output tiles, the accumulator is
 // double-buffered in tensor memory (2 x BN columns), and the roles never meet inside a tile:
@@ -482,20 +409,6 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
-}
-
-// Shared-memory matrix descriptor of an MN-major bf16 tile: rows of the tile in memory are K
-// indices, each row holds 64 contiguous MN elements (128 bytes, 128-byte swizzle).  8-row K groups
-// are 1024 bytes apart (stride byte offset); the next 64 MN elements live `mn_group_bytes`
-// further (leading byte offset).
-__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_group_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
-    d |= (uint64_t)(mn_group_bytes >> 4) << 16;        // leading byte offset
-    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
-    d |= (uint64_t)1 << 46;                            // version
-    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
-    return d;
 }
 
 // C[I, N] += A[rows, I]^T * B[rows, N]: both operands are row-major with the reduction index as
@@ -682,6 +595,9 @@ transpose_bf16_kernel(int rows, int cols, const __nv_bfloat16* __restrict__ src,
 }
 
 // ---- host side ------------------------------------------------------------------------------
+static uint32_t g_host_poll_limit = 1u << 21;  // host mirror of d_poll_limit for kernels of other translation units
+uint32_t tensor_core_poll_limit() { return g_host_poll_limit; }
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -853,6 +769,7 @@ extern "C" {
 
 int pccnn_gemm_set_test_hooks(int poll_limit, int withhold_from) {
     const uint32_t limit = poll_limit > 0 ? (uint32_t)poll_limit : (1u << 21);
+    g_host_poll_limit = limit;
     const int withhold = withhold_from >= 0 ? withhold_from : -1;
     PCCNN_CUDA(cudaMemcpyToSymbol(d_poll_limit, &limit, sizeof(limit)));
     PCCNN_CUDA(cudaMemcpyToSymbol(d_withhold_from, &withhold, sizeof(withhold)));

@@ -17,6 +17,16 @@ from . import _capi
 _lib = _capi.lib
 
 
+def set_conv_path(path):
+    """Which kernels do the per-pair work of the convolutions: "tensor" (default: tcgen05 pair kernels for 3-D points
+    with at least 32 input channels, CUDA-core kernels otherwise) or "simt" (CUDA-core kernels everywhere).  The
+    environment variable PCCNN_CONV_PATH selects it at import."""
+    _capi.check(_lib.pccnn_conv_set_path({"tensor": 0, "simt": 1}[path]), "conv_set_path")
+
+
+set_conv_path(os.environ.get("PCCNN_CONV_PATH", "tensor"))
+
+
 # ---- argument plumbing -----------------------------------------------------------------------
 def _need(t, name, dtype, ndim=None):
     if not isinstance(t, torch.Tensor):
@@ -430,7 +440,7 @@ def kp_conv(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma,
     m = samples.shape[0]
     out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(feats.shape[0], m, cin, k, cout), pts.device)
         _capi.check(_lib.pccnn_kp_conv(d, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
                                        _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
                                        _p(out), ws.data_ptr(), ws.numel(), _stream()), "kp_conv")
@@ -448,7 +458,7 @@ def _kp_conv_bf16(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, 
     m = samples.shape[0]
     out = torch.empty((m, cout), dtype=torch.bfloat16, device=pts.device)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(feats.shape[0], m, cin, k, cout), pts.device)
         _capi.check(_lib.pccnn_kp_conv_bf16(d, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
                                             _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights),
                                             cout, _p(out), ws.data_ptr(), ws.numel(), _stream()), "kp_conv_bf16")
@@ -470,7 +480,7 @@ def mc_conv(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_proj, ax
     m = samples.shape[0]
     out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, hidden, cout), pts.device)
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(feats.shape[0], m, cin, hidden, cout), pts.device)
         _capi.check(_lib.pccnn_mc_conv(d, pts.shape[0], _p(pts), _p(pdf), _p(feats), cin, m, _p(samples), _p(neighbors),
                                        _p(start_ids), _p(radii), _p(axis_proj), _p(axis_bias), hidden, n_mlps,
                                        _p(weights), cout, _p(out), ws.data_ptr(), ws.numel(), _stream()), "mc_conv")
@@ -545,7 +555,7 @@ def kp_conv_grads(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, 
     d_w, d_f = torch.empty_like(weights), torch.empty_like(feats)
     d_k, d_p, d_s = torch.empty_like(kernel_pts), torch.empty_like(pts), torch.empty_like(samples)
     with _on(dev):
-        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, k, cout), dev)
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(feats.shape[0], m, cin, k, cout), dev)
         _arm_weight_grads_event(weight_grads_event)
         _capi.check(_lib.pccnn_kp_conv_grads(d, n, _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
                                              _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights),
@@ -575,7 +585,7 @@ def mc_conv_grads(pts, pdf, feats, samples, neighbors, start_ids, radii, axis_pr
     d_a, d_b, d_pdf = torch.empty_like(axis_proj), torch.empty_like(axis_bias), torch.empty_like(pdf)
     d_p, d_s = torch.empty_like(pts), torch.empty_like(samples)
     with _on(dev):
-        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, hidden, cout), dev)
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(feats.shape[0], m, cin, hidden, cout), dev)
         _arm_weight_grads_event(weight_grads_event)
         _capi.check(_lib.pccnn_mc_conv_grads(d, n, _p(pts), _p(pdf), _p(feats), cin, m, _p(samples), _p(neighbors),
                                              _p(start_ids), _p(radii), _p(axis_proj), _p(axis_bias), hidden, n_mlps,
@@ -597,7 +607,7 @@ def kp_conv_weight_var(pts, feats, samples, neighbors, start_ids, radii, kernel_
     k, cin, m = kernel_pts.shape[0], feats.shape[1], samples.shape[0]
     out = _variance_out(pts.device)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, k), pts.device)
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(feats.shape[0], m, cin, k), pts.device)
         _capi.check(_lib.pccnn_kp_conv_weight_var(d, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
                                                   _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), out.data_ptr(),
                                                   ws.data_ptr(), ws.numel(), _stream()), "kp_conv_weight_var")
@@ -613,7 +623,7 @@ def mc_conv_weight_var(pts, pdf, feats, samples, neighbors, start_ids, radii, ax
     hidden, cin, m = axis_proj.shape[1], feats.shape[1], samples.shape[0]
     out = _variance_out(pts.device)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, hidden), pts.device)
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(feats.shape[0], m, cin, hidden), pts.device)
         _capi.check(_lib.pccnn_mc_conv_weight_var(d, pts.shape[0], _p(pts), _p(pdf), _p(feats), cin, m, _p(samples),
                                                   _p(neighbors), _p(start_ids), _p(radii), _p(axis_proj), _p(axis_bias),
                                                   hidden, out.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
@@ -650,7 +660,7 @@ def kp_conv_n(pts, pdf, feats, samples, neighbors, start_ids, radii, kernel_pts,
     m = samples.shape[0]
     out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(feats.shape[0], m, cin, k, cout), pts.device)
         _capi.check(_lib.pccnn_kp_conv_n(d, pts.shape[0], _p(pts), _p(pdf), _p(feats), cin, m, _p(samples), _p(neighbors),
                                          _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
                                          _p(out), ws.data_ptr(), ws.numel(), _stream()), "kp_conv_n")
@@ -665,7 +675,7 @@ def kp_conv_n_grads(pts, pdf, feats, samples, neighbors, start_ids, radii, kerne
     d_w, d_f = torch.empty_like(weights), torch.empty_like(feats)
     d_k, d_p, d_s = torch.empty_like(kernel_pts), torch.empty_like(pts), torch.empty_like(samples)
     with _on(dev):
-        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, k, cout), dev)
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(feats.shape[0], m, cin, k, cout), dev)
         _capi.check(_lib.pccnn_kp_conv_n_grads(d, n, _p(pts), _p(pdf), _p(feats), cin, m, _p(samples), _p(neighbors),
                                                _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
                                                _p(in_grads), d_w.data_ptr(), d_f.data_ptr(), d_k.data_ptr(), d_p.data_ptr(),
@@ -680,7 +690,7 @@ def kp_conv_n_weight_var(pts, pdf, feats, samples, neighbors, start_ids, radii, 
     m = samples.shape[0]
     out = _variance_out(pts.device)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, k), pts.device)
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(feats.shape[0], m, cin, k), pts.device)
         _capi.check(_lib.pccnn_kp_conv_n_weight_var(d, pts.shape[0], _p(pts), _p(pdf), _p(feats), cin, m, _p(samples),
                                                     _p(neighbors), _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma),
                                                     out.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
@@ -696,7 +706,7 @@ def pccnn(pts, feats, pdf, samples, neighbors, start_ids, radii, kernel_pts, sig
     m = samples.shape[0]
     out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(feats.shape[0], m, cin, k, cout), pts.device)
         _capi.check(_lib.pccnn_pccnn_conv(d, pts.shape[0], _p(pts), _p(feats), cin, _p(pdf), m, _p(samples), _p(neighbors),
                                           _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
                                           _p(out), ws.data_ptr(), ws.numel(), _stream()), "pccnn")
@@ -711,7 +721,7 @@ def pccnn_grads(pts, feats, pdf, samples, neighbors, start_ids, radii, kernel_pt
     d_w, d_f, d_k = torch.empty_like(weights), torch.empty_like(feats), torch.empty_like(kernel_pts)
     d_pdf, d_p, d_s = torch.empty_like(pdf), torch.empty_like(pts), torch.empty_like(samples)
     with _on(dev):
-        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, k, cout), dev)
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(feats.shape[0], m, cin, k, cout), dev)
         _capi.check(_lib.pccnn_pccnn_conv_grads(d, n, _p(pts), _p(feats), cin, _p(pdf), m, _p(samples), _p(neighbors),
                                                 _p(start_ids), _p(radii), _p(kernel_pts), k, float(sigma), _p(weights), cout,
                                                 _p(in_grads), d_w.data_ptr(), d_f.data_ptr(), d_k.data_ptr(),
@@ -727,7 +737,7 @@ def pccnn_weight_variance(pts, feats, pdf, samples, neighbors, start_ids, radii,
     m = samples.shape[0]
     out = _variance_out(pts.device)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, k), pts.device)
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(feats.shape[0], m, cin, k), pts.device)
         _capi.check(_lib.pccnn_pccnn_conv_weight_var(d, pts.shape[0], _p(pts), _p(feats), cin, _p(pdf), m, _p(samples),
                                                      _p(neighbors), _p(start_ids), _p(radii), _p(kernel_pts), k,
                                                      float(sigma), out.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
@@ -760,7 +770,7 @@ def sph_conv(pts, feats, samples, neighbors, start_ids, radii, radial_bins, azim
         raise RuntimeError("weights must be [(R * A * P + 1) * Cin, Cout]")
     out = torch.empty((m, cout), dtype=torch.float32, device=pts.device)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, k, cout), pts.device)
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(feats.shape[0], m, cin, k, cout), pts.device)
         _capi.check(_lib.pccnn_sph_conv(3, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors), _p(start_ids),
                                         _p(radii), *_bins_c(bins), _p(weights), cout, _p(out), ws.data_ptr(), ws.numel(),
                                         _stream()), "sph_conv")
@@ -779,7 +789,7 @@ def sph_conv_grads(pts, feats, samples, neighbors, start_ids, radii, radial_bins
         raise RuntimeError("weights must be [(R * A * P + 1) * Cin, Cout] and in_grads [M, Cout]")
     d_w, d_f = torch.empty_like(weights), torch.empty_like(feats)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, k, cout), pts.device)
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(feats.shape[0], m, cin, k, cout), pts.device)
         _capi.check(_lib.pccnn_sph_conv_grads(3, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
                                               _p(start_ids), _p(radii), *_bins_c(bins), _p(weights), cout, _p(in_grads),
                                               d_w.data_ptr(), d_f.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
@@ -794,7 +804,7 @@ def sph_conv_weight_var(pts, feats, samples, neighbors, start_ids, radii, radial
     cin, m = feats.shape[1], samples.shape[0]
     out = _variance_out(pts.device)
     with _on(pts.device):
-        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, k), pts.device)
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(feats.shape[0], m, cin, k), pts.device)
         _capi.check(_lib.pccnn_sph_conv_weight_var(3, pts.shape[0], _p(pts), _p(feats), cin, m, _p(samples), _p(neighbors),
                                                    _p(start_ids), _p(radii), *_bins_c(bins), out.data_ptr(), ws.data_ptr(),
                                                    ws.numel(), _stream()), "sph_conv_weight_var")
@@ -864,7 +874,7 @@ def point_conv(basis, feats, neighbors, start_ids, weights):
         raise RuntimeError("weights must be [H * Cin, Cout]")
     out = torch.empty((m, cout), dtype=torch.float32, device=feats.device)
     with _on(feats.device):
-        ws = _workspace(_lib.pccnn_conv_workspace_bytes(m, cin, hidden, cout), feats.device)
+        ws = _workspace(_lib.pccnn_conv_workspace_bytes(feats.shape[0], m, cin, hidden, cout), feats.device)
         _capi.check(_lib.pccnn_point_conv(feats.shape[0], _p(basis), hidden, _p(feats), cin, m, _p(neighbors), _p(start_ids),
                                           _p(weights), cout, _p(out), ws.data_ptr(), ws.numel(), _stream()), "point_conv")
     return out
@@ -880,7 +890,7 @@ def point_conv_grads(basis, feats, neighbors, start_ids, weights, in_grads):
         raise RuntimeError("weights must be [H * Cin, Cout] and in_grads [M, Cout]")
     d_w, d_f, d_b = torch.empty_like(weights), torch.empty_like(feats), torch.empty_like(basis)
     with _on(feats.device):
-        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(m, cin, hidden, cout), feats.device)
+        ws = _workspace(_lib.pccnn_conv_grads_workspace_bytes(feats.shape[0], m, cin, hidden, cout), feats.device)
         _capi.check(_lib.pccnn_point_conv_grads(feats.shape[0], _p(basis), hidden, _p(feats), cin, m, basis.shape[0],
                                                 _p(neighbors), _p(start_ids), _p(weights), cout, _p(in_grads),
                                                 d_w.data_ptr(), d_f.data_ptr(), d_b.data_ptr(), ws.data_ptr(), ws.numel(),
@@ -894,7 +904,7 @@ def point_conv_weight_var(basis, feats, neighbors, start_ids):
     hidden, cin, m = basis.shape[1], feats.shape[1], start_ids.shape[0]
     out = _variance_out(feats.device)
     with _on(feats.device):
-        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(m, cin, hidden), feats.device)
+        ws = _workspace(_lib.pccnn_conv_weight_var_workspace_bytes(feats.shape[0], m, cin, hidden), feats.device)
         _capi.check(_lib.pccnn_point_conv_weight_var(feats.shape[0], _p(basis), hidden, _p(feats), cin, m, _p(neighbors),
                                                      _p(start_ids), out.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
                     "point_conv_weight_var")

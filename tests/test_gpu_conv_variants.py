@@ -94,7 +94,7 @@ def test_warmup_initialisation_of_the_layers(ref_clouds):
         layer.set_init_warmup_state(True)
         out, nb = layer(pc, pc, feats, radius)
         assert layer.accum_weight_var_ > 0.0
-        assert 0.5 < float(out.var()) < 2.0
+        assert 0.5 < float(out.detach().var()) < 2.0
         layer.set_init_warmup_state(False)
         w = layer.conv_weights_.detach().clone()
         layer(pc, pc, feats, radius, nb)

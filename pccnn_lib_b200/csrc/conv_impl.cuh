@@ -941,14 +941,17 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
     const FeaturePlanes planes{(const __nv_bfloat16*)(ws + L.f_hi_off), (const __nv_bfloat16*)(ws + L.f_lo_off), L.ld_f};
     if (tc)
         if (int rc = split_features(num_pts, cin, feats, ws + L.f_hi_off, ws + L.f_lo_off, s)) return rc;
+    // The tensor-core pair kernel also produces the projected features of its samples when one pass covers all
+    // channels (the gathered tile is the same); then the weight-gradient contraction follows it.
+    const bool fused_p = tc && cin <= kTcChan;
     for (int64_t m0 = 0; m0 < num_samples; m0 += L.chunk) {
         const int64_t m1 = (m0 + L.chunk < num_samples) ? m0 + L.chunk : num_samples;
         const int64_t rows = m1 - m0;
         int rc = PCCNN_OK;
-        if (tc)
+        if (tc && !fused_p)
             rc = launch_project_tc<ARGS, BASIS, true>(K, args, pts, planes, cin, samples, neighbors, start_ids, radii, (int)m0,
                                                       (int)m1, ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, status, s);
-        else
+        else if (!tc)
             rc = dispatch_dims<BasisTraits<BASIS>::kOnly3D>(D, [&](auto dim) {
                 constexpr int DIM = decltype(dim)::value;
                 return launch_project<DIM, ARGS, BASIS>(K, args, pts, feats, cin, samples, neighbors, start_ids, radii,
@@ -957,36 +960,50 @@ static int conv_backward(const char* who, int D, int K, const ARGS& args, int64_
         if (rc) return rc;
         if ((rc = split_bf16(rows, cout, in_grads + (size_t)m0 * cout, cout, L.ld_g, ws + L.g_hi_off, ws + L.g_lo_off, s)))
             return rc;
+        auto operands = [&](int j, GemmOperand& p, GemmOperand& g, GemmOperand& w) {
+            p = GemmOperand{ws + L.p_hi_off + (size_t)j * inner_j * 2, ws + L.p_lo_off + (size_t)j * inner_j * 2, L.ld_p,
+                            L.ld_p - (int64_t)j * inner_j};
+            g = GemmOperand{ws + L.g_hi_off + (size_t)j * cout_j * 2, ws + L.g_lo_off + (size_t)j * cout_j * 2, L.ld_g,
+                            L.ld_g - (int64_t)j * cout_j};
+            w = GemmOperand{ws + L.w_hi_off + (size_t)j * inner_j * L.ld_g * 2, ws + L.w_lo_off + (size_t)j * inner_j * L.ld_g * 2,
+                            L.ld_g};
+        };
+        auto weight_grads = [&]() -> int {  // dW_j += P_j^T g_j
+            for (int j = 0; j < num_mlps; ++j) {
+                GemmOperand p, g, w;
+                operands(j, p, g, w);
+                if (int rc2 = gemm_bf16_tn_accumulate(p, g, d_weights + (size_t)j * inner_j * cout_j, rows, inner_j, cout_j,
+                                                      cout_j, status, s))
+                    return rc2;
+            }
+            if (m1 == num_samples && weight_grads_event) PCCNN_CUDA(cudaEventRecord(weight_grads_event, s));  // dW is final
+            return PCCNN_OK;
+        };
+        if (!fused_p)
+            if ((rc = weight_grads())) return rc;
         for (int j = 0; j < num_mlps; ++j) {
-            GemmOperand p{ws + L.p_hi_off + (size_t)j * inner_j * 2, ws + L.p_lo_off + (size_t)j * inner_j * 2, L.ld_p,
-                          L.ld_p - (int64_t)j * inner_j};
-            GemmOperand g{ws + L.g_hi_off + (size_t)j * cout_j * 2, ws + L.g_lo_off + (size_t)j * cout_j * 2, L.ld_g,
-                          L.ld_g - (int64_t)j * cout_j};
-            GemmOperand w{ws + L.w_hi_off + (size_t)j * inner_j * L.ld_g * 2,
-                          ws + L.w_lo_off + (size_t)j * inner_j * L.ld_g * 2, L.ld_g};
-            // dW_j += P_j^T g_j
-            if ((rc = gemm_bf16_tn_accumulate(p, g, d_weights + (size_t)j * inner_j * cout_j, rows, inner_j, cout_j,
-                                              cout_j, status, s)))
-                return rc;
+            GemmOperand p, g, w;
+            operands(j, p, g, w);
             // dP_j = g_j W_j^T  ->  columns [j * inner_j, (j + 1) * inner_j) of the dP rows
             // (reduction over the MLP's outputs rounded up to 64: the surplus columns of g meet zero weights)
             const int kp = num_mlps == 1 ? L.ld_g : (cout_j + 63) / 64 * 64;
-            if (j == num_mlps - 1 && m1 == num_samples && weight_grads_event)
-                PCCNN_CUDA(cudaEventRecord(weight_grads_event, s));  // dW is final from here on
             if ((rc = gemm_bf16_nt(g, w, d_proj + (size_t)j * inner_j, rows, inner_j, kp, inner, status, s))) return rc;
         }
         if (tc)
             rc = launch_backward_tc<ARGS, BASIS>(K, args, pts, planes, cin, samples, neighbors, start_ids, radii, (int)m0,
-                                                 (int)m1, d_proj, d_feat, d_pts, d_samples, d_param0, d_param1, d_pdf, status,
-                                                 s);
+                                                 (int)m1, d_proj, d_feat, d_pts, d_samples, d_param0, d_param1, d_pdf,
+                                                 fused_p ? ws + L.p_hi_off : nullptr, fused_p ? ws + L.p_lo_off : nullptr, L.ld_p,
+                                                 status, s);
         else
             rc = dispatch_dims<BasisTraits<BASIS>::kOnly3D>(D, [&](auto dim) {
                 constexpr int DIM = decltype(dim)::value;
-                return launch_backward_pairs<DIM, ARGS, BASIS>(
-                                       K, args, pts, feats, cin, samples, neighbors, start_ids, radii, (int)m0, (int)m1,
-                                       d_proj, d_feat, d_pts, d_samples, d_param0, d_param1, d_pdf, s);
+                return launch_backward_pairs<DIM, ARGS, BASIS>(K, args, pts, feats, cin, samples, neighbors, start_ids, radii,
+                                                               (int)m0, (int)m1, d_proj, d_feat, d_pts, d_samples, d_param0,
+                                                               d_param1, d_pdf, s);
             });
         if (rc) return rc;
+        if (fused_p)
+            if ((rc = weight_grads())) return rc;
     }
     return publish_status(status, kOriginConvBackward, s);
 }

@@ -127,6 +127,39 @@ static int split_features(int64_t rows, int cin, const float* src, void* hi, voi
     return PCCNN_OK;
 }
 
+// K entries of channel c of a P row (bf16 hi [+ lo] planes): 128-bit stores when the K values of a channel are
+// 16-byte aligned, element stores otherwise.
+template <int NB>
+__device__ __forceinline__ void store_p_row(const float (&acc)[NB], int c, int cin, int K, __nv_bfloat16* __restrict__ p_hi,
+                                            __nv_bfloat16* __restrict__ p_lo, size_t row) {
+    if (c >= cin) return;
+    if (K == NB) {
+#pragma unroll
+        for (int k = 0; k < NB; k += 8) {
+            uint32_t hw[4], lw[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float v0 = acc[k + 2 * q], v1 = acc[k + 2 * q + 1];
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+                const __nv_bfloat162 l2 = __floats2bfloat162_rn(v0 - __low2float(h2), v1 - __high2float(h2));
+                hw[q] = *reinterpret_cast<const uint32_t*>(&h2);
+                lw[q] = *reinterpret_cast<const uint32_t*>(&l2);
+            }
+            *reinterpret_cast<uint4*>(p_hi + row + (size_t)c * K + k) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            if (p_lo) *reinterpret_cast<uint4*>(p_lo + row + (size_t)c * K + k) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < NB; ++k) {
+            if (k < K) {
+                const __nv_bfloat16 h = __float2bfloat16_rn(acc[k]);
+                p_hi[row + (size_t)c * K + k] = h;
+                if (p_lo) p_lo[row + (size_t)c * K + k] = __float2bfloat16_rn(acc[k] - __bfloat162float(h));
+            }
+        }
+    }
+}
+
 template <int NB>
 struct TcForwardSmem {
     static constexpr int kF = 2 * kTcRows * 128;  // one plane of the F tile: 32 KB
@@ -279,33 +312,7 @@ project_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes
                     for (int k = 0; k < 16; ++k) acc[k0 + k] = __uint_as_float(r[k]);
                 }
             }
-            if (c < cin) {
-                if (K == NB) {
-#pragma unroll
-                    for (int k = 0; k < NB; k += 8) {
-                        uint32_t hw[4], lw[4];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const float v0 = acc[k + 2 * q], v1 = acc[k + 2 * q + 1];
-                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
-                            const __nv_bfloat162 l2 = __floats2bfloat162_rn(v0 - __low2float(h2), v1 - __high2float(h2));
-                            hw[q] = *reinterpret_cast<const uint32_t*>(&h2);
-                            lw[q] = *reinterpret_cast<const uint32_t*>(&l2);
-                        }
-                        *reinterpret_cast<uint4*>(p_hi + row + (size_t)c * K + k) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-                        if (p_lo) *reinterpret_cast<uint4*>(p_lo + row + (size_t)c * K + k) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
-                    }
-                } else {
-#pragma unroll
-                    for (int k = 0; k < NB; ++k) {
-                        if (k < K) {
-                            const __nv_bfloat16 h = __float2bfloat16_rn(acc[k]);
-                            p_hi[row + (size_t)c * K + k] = h;
-                            if (p_lo) p_lo[row + (size_t)c * K + k] = __float2bfloat16_rn(acc[k] - __bfloat162float(h));
-                        }
-                    }
-                }
-            }
+            store_p_row<NB>(acc, c, cin, K, p_hi, p_lo, row);
             tc_fence_before();
             __syncthreads();  // the accumulator is free for the next channel block / sample
         }
@@ -328,25 +335,25 @@ project_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes
 
 template <int NB>
 struct TcBackwardSmem {
-    static constexpr int kF = 2 * kTcRows * 128;   // F plane: 32 KB
-    static constexpr int kBM = kTcRows * 128;      // BM plane: 16 KB (rows padded to 128 bytes)
-    static constexpr int kGP = 2 * NB * 128;       // GP plane: two 64-channel blocks of [NB x 128 B]
-    static constexpr int kGQ = kTcChan * 128;      // GQ plane: 16 KB
-    static constexpr int kFHi = 0, kFLo = kF, kBMHi = 2 * kF, kBMLo = kBMHi + kBM, kGPHi = kBMLo + kBM,
-                         kGPLo = kGPHi + kGP, kGQHi = kGPLo + kGP, kGQLo = kGQHi + kGQ;
-    static constexpr int kTiles = kGQLo + kGQ;
+    static constexpr int kF = 2 * kTcRows * 128;  // F plane: 32 KB
+    static constexpr int kBT = 2 * NB * 128;      // BT plane: two 64-neighbor blocks of [NB x 128 B]
+    static constexpr int kGP = 2 * NB * 128;      // GP plane: two 64-channel blocks of [NB x 128 B]
+    static constexpr int kFHi = 0, kFLo = kF, kBTHi = 2 * kF, kBTLo = kBTHi + kBT, kGPHi = kBTLo + kBT, kGPLo = kGPHi + kGP;
+    static constexpr int kTiles = kGPLo + kGP;
     static constexpr int kMisc = 4096;  // barrier, tensor-memory slot, neighbor ids, basis parameters, parameter gradients
     static constexpr int kBytes = kTiles + kMisc;
 };
 
-__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
 // Everything of the backward pass that runs per neighbor pair, given dP = g W^T (rows of `inner` floats) for the
-// samples [m_begin, m_end): dF (reduced into d_feat), db -> basis / offset / point / parameter gradients.
-// Thread r of the CTA owns neighbor r of the current pass in the "lanes as neighbors" stages and channel cb + r in
-// the "lanes as channels" stage that lays out the sample's dP row.
+// samples [m_begin, m_end): dF (reduced into d_feat), db -> basis / offset / point / parameter gradients, and, when
+// p_hi is given (Cin <= 128), the projected features P of the samples for the weight-gradient contraction, which
+// share the gathered tile.  Three products per pass, all from the tiles F, BT (basis, [k][neighbor]) and GP (the
+// sample's dP row, [k][channel]):
+//     P^T [channel, k]          = F^T  * BT^T     A = F  MN-major, B = BT K-major      (accumulated over the passes)
+//     db  [neighbor, k]         = F    * GP^T     A = F  K-major,  B = GP K-major      (accumulated over channel blocks)
+//     dF^T[channel, neighbor]   = GP^T * BT       A = GP MN-major, B = BT MN-major     (one 16-deep step per 16 basis functions)
+// Thread r of the CTA owns neighbor r in the "lanes as neighbors" stages and channel cb + r in the "lanes as
+// channels" stages.
 template <int NB, class BASIS, class ARGS>
 __global__ void __launch_bounds__(128)
 backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes feats, int cin,
@@ -354,7 +361,8 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
                    const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
                    const float* __restrict__ d_proj, float* __restrict__ d_feat, float* __restrict__ d_pts,
                    float* __restrict__ d_samples, float* __restrict__ d_param0, float* __restrict__ d_param1,
-                   float* __restrict__ d_pdf, uint32_t poll_limit, int* __restrict__ status) {
+                   float* __restrict__ d_pdf, __nv_bfloat16* __restrict__ p_hi, __nv_bfloat16* __restrict__ p_lo, int ld_p,
+                   uint32_t poll_limit, int* __restrict__ status) {
     using SM = TcBackwardSmem<NB>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];  // the swizzled tiles need 1024-byte alignment
     uint8_t* smem = smem_raw;
@@ -365,7 +373,8 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
     float* s_params = (float*)(misc + 64 + 512);       // up to 256 floats
     float* s_grad = (float*)(misc + 64 + 512 + 1024);  // up to 256 floats
     static_assert(BASIS::kParamFloats <= 256 && BASIS::kGradFloats <= 256, "basis parameters do not fit their slots");
-    constexpr uint32_t kTmemCols = 256;  // db in columns [0, NB), dF in columns [128, 256)
+    constexpr uint32_t kTmemCols = 256;  // db in columns [0, NB), P^T in [64, 64 + NB), dF^T in [128, 256)
+    constexpr uint32_t kColP = 64, kColF = 128;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
@@ -389,14 +398,14 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
 #pragma unroll
     for (int d = 0; d < 3; ++d) inv[d] = BASIS::kUsesOffset ? __frcp_rn(__ldg(radii + d)) : 0.f;
     const int inner = cin * K;
-    const bool vec = (cin & 3) == 0;
+    const bool with_p = p_hi != nullptr;
     const uint32_t f_hi = smem_u32(smem + SM::kFHi), f_lo = smem_u32(smem + SM::kFLo);
-    const uint32_t bm_hi = smem_u32(smem + SM::kBMHi), bm_lo = smem_u32(smem + SM::kBMLo);
+    const uint32_t bt_hi = smem_u32(smem + SM::kBTHi), bt_lo = smem_u32(smem + SM::kBTLo);
     const uint32_t gp_hi = smem_u32(smem + SM::kGPHi), gp_lo = smem_u32(smem + SM::kGPLo);
-    const uint32_t gq_hi = smem_u32(smem + SM::kGQHi), gq_lo = smem_u32(smem + SM::kGQLo);
-    // fp32 accumulate, bf16 x bf16, both operands K-major, M = 128
-    constexpr uint32_t idesc_db = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-    constexpr uint32_t idesc_df = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    constexpr uint32_t kBase = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 4) << 24);  // fp32 += bf16 x bf16, M = 128
+    constexpr uint32_t idesc_p = kBase | (1u << 15) | ((uint32_t)(NB >> 3) << 17);                  // A MN-major, N = NB
+    constexpr uint32_t idesc_db = kBase | ((uint32_t)(NB >> 3) << 17);                              // K-major, N = NB
+    constexpr uint32_t idesc_df = kBase | (1u << 15) | (1u << 16) | ((uint32_t)(128 >> 3) << 17);   // both MN-major, N = 128
     uint32_t parity = 0;
     bool failed = false;
     // Parameter gradients: with a small basis every thread keeps its own partial sums in registers and the block
@@ -414,48 +423,47 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
 #pragma unroll
         for (int d = 0; d < 3; ++d) s[d] = BASIS::kUsesOffset ? __ldg(samples + (int64_t)m * 3 + d) : 0.f;
         const float* grow = d_proj + (size_t)(m - m_begin) * inner;
+        const size_t prow = (size_t)(m - m_begin) * ld_p;
+        bool first = true;
 
         for (int t0 = lo; t0 < hi && !failed; t0 += kTcRows) {
             const int cnt = min(kTcRows, hi - t0);
-            // ---- lanes as neighbors: offset and basis of pair t0 + tid, BM row tid
+            const int rows = (cnt + 15) & ~15;
+            // ---- the neighbor of this thread
             const int t = t0 + tid;
             const bool active = tid < cnt;
-            int n0 = -1;
-            float d[3] = {0.f, 0.f, 0.f};
-            {
-                float b[NB];
-                if (active) {
-                    n0 = __ldg(&neighbors[t]).x;
-#pragma unroll
-                    for (int x = 0; x < 3; ++x)
-                        d[x] = BASIS::kUsesOffset ? (__ldg(pts + (int64_t)n0 * 3 + x) - s[x]) * inv[x] : 0.f;
-                    BASIS::eval(s_params, args, K, d, n0, t, m, b);
-                } else {
-#pragma unroll
-                    for (int k = 0; k < NB; ++k) b[k] = 0.f;
-                }
-                s_n0[tid] = n0;
-#pragma unroll
-                for (int j = 0; j < NB / 8; ++j) {
-                    uint32_t hw[4], lw[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const float v0 = b[8 * j + 2 * q], v1 = b[8 * j + 2 * q + 1];
-                        const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
-                        const __nv_bfloat162 l2 = __floats2bfloat162_rn(v0 - __low2float(h2), v1 - __high2float(h2));
-                        hw[q] = *reinterpret_cast<const uint32_t*>(&h2);
-                        lw[q] = *reinterpret_cast<const uint32_t*>(&l2);
-                    }
-                    const uint32_t off = sw128_offset(tid, j);
-                    *reinterpret_cast<uint4*>(smem + SM::kBMHi + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-                    *reinterpret_cast<uint4*>(smem + SM::kBMLo + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
-                }
-            }
+            const int n0 = active ? __ldg(&neighbors[t]).x : -1;
+            s_n0[tid] = n0;
             __syncthreads();
+            float d[3] = {0.f, 0.f, 0.f};
 
             for (int cb = 0; cb < cin; cb += kTcChan) {
-                gather_features_async<true>(f_hi, f_lo, s_n0, cnt, feats, cb);
-                // ---- lanes as channels: the dP entries of channel cb + tid -> GQ row tid and GP column tid
+                gather_features_async<true>(f_hi, f_lo, s_n0, rows, feats, cb);
+                if (cb == 0) {
+                    // ---- lanes as neighbors, while the copies are in flight: offset, basis, BT column of this pair
+                    float b[NB];
+                    if (active) {
+#pragma unroll
+                        for (int x = 0; x < 3; ++x)
+                            d[x] = BASIS::kUsesOffset ? (__ldg(pts + (int64_t)n0 * 3 + x) - s[x]) * inv[x] : 0.f;
+                        BASIS::eval(s_params, args, K, d, n0, t, m, b);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < NB; ++k) b[k] = 0.f;
+                    }
+                    // all 128 columns are written: dF^T is computed for every column of the tile
+                    uint8_t* base_hi = smem + SM::kBTHi + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                    uint8_t* base_lo = smem + SM::kBTLo + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                    const int chunk = (tid & 63) >> 3;
+#pragma unroll
+                    for (int k = 0; k < NB; ++k) {
+                        const __nv_bfloat16 h = __float2bfloat16_rn(b[k]);
+                        const uint32_t off = sw128_offset(k, chunk);
+                        *reinterpret_cast<__nv_bfloat16*>(base_hi + off) = h;
+                        *reinterpret_cast<__nv_bfloat16*>(base_lo + off) = __float2bfloat16_rn(b[k] - __bfloat162float(h));
+                    }
+                }
+                // ---- lanes as channels: the dP entries of channel cb + tid -> GP column tid
                 {
                     const int c = cb + tid;
                     float g[NB];
@@ -474,31 +482,15 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
 #pragma unroll
                         for (int k = 0; k < NB; ++k) g[k] = 0.f;
                     }
-                    uint8_t* gp_base_hi = smem + SM::kGPHi + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
-                    uint8_t* gp_base_lo = smem + SM::kGPLo + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                    uint8_t* base_hi = smem + SM::kGPHi + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                    uint8_t* base_lo = smem + SM::kGPLo + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
                     const int chunk = (tid & 63) >> 3;
 #pragma unroll
-                    for (int j = 0; j < NB / 8; ++j) {
-                        uint32_t hw[4], lw[4];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const float v0 = g[8 * j + 2 * q], v1 = g[8 * j + 2 * q + 1];
-                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
-                            const __nv_bfloat162 l2 = __floats2bfloat162_rn(v0 - __low2float(h2), v1 - __high2float(h2));
-                            hw[q] = *reinterpret_cast<const uint32_t*>(&h2);
-                            lw[q] = *reinterpret_cast<const uint32_t*>(&l2);
-                            // the same values, transposed: (row k, column = this channel) of GP
-#pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-                                const int k = 8 * j + 2 * q + e;
-                                const uint32_t off = sw128_offset(k, chunk);
-                                *reinterpret_cast<__nv_bfloat16*>(gp_base_hi + off) = e ? __high2bfloat16(h2) : __low2bfloat16(h2);
-                                *reinterpret_cast<__nv_bfloat16*>(gp_base_lo + off) = e ? __high2bfloat16(l2) : __low2bfloat16(l2);
-                            }
-                        }
-                        const uint32_t off = sw128_offset(tid, j);
-                        *reinterpret_cast<uint4*>(smem + SM::kGQHi + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-                        *reinterpret_cast<uint4*>(smem + SM::kGQLo + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+                    for (int k = 0; k < NB; ++k) {
+                        const __nv_bfloat16 h = __float2bfloat16_rn(g[k]);
+                        const uint32_t off = sw128_offset(k, chunk);
+                        *reinterpret_cast<__nv_bfloat16*>(base_hi + off) = h;
+                        *reinterpret_cast<__nv_bfloat16*>(base_lo + off) = __float2bfloat16_rn(g[k] - __bfloat162float(h));
                     }
                 }
                 cp_async_wait_all();
@@ -517,14 +509,29 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
                         tc_mma_bf16(tmem_base, a_lo, b_hi, idesc_db, 1u);
                         tc_mma_bf16(tmem_base, a_hi, b_lo, idesc_db, 1u);
                     }
-                    // dF[neighbor, c] = b[neighbor, k] * dP[c, k]: NB / 16 steps
+                    // dF^T[c, neighbor] = dP[c, k] * b[neighbor, k]: both operands MN-major (16 basis rows = 2048 bytes
+                    // = +128 per step; 64-channel / 64-neighbor groups are one block of NB rows apart)
 #pragma unroll
                     for (int ks = 0; ks < NB / 16; ++ks) {
-                        const uint64_t a_hi = umma_desc_k_sw128(bm_hi) + 2ull * ks, a_lo = umma_desc_k_sw128(bm_lo) + 2ull * ks;
-                        const uint64_t b_hi = umma_desc_k_sw128(gq_hi) + 2ull * ks, b_lo = umma_desc_k_sw128(gq_lo) + 2ull * ks;
-                        tc_mma_bf16(tmem_base + 128, a_hi, b_hi, idesc_df, ks > 0 ? 1u : 0u);
-                        tc_mma_bf16(tmem_base + 128, a_lo, b_hi, idesc_df, 1u);
-                        tc_mma_bf16(tmem_base + 128, a_hi, b_lo, idesc_df, 1u);
+                        const uint64_t a_hi = umma_desc_mn_sw128(gp_hi, NB * 128) + 128ull * ks;
+                        const uint64_t a_lo = umma_desc_mn_sw128(gp_lo, NB * 128) + 128ull * ks;
+                        const uint64_t b_hi = umma_desc_mn_sw128(bt_hi, NB * 128) + 128ull * ks;
+                        const uint64_t b_lo = umma_desc_mn_sw128(bt_lo, NB * 128) + 128ull * ks;
+                        tc_mma_bf16(tmem_base + kColF, a_hi, b_hi, idesc_df, ks > 0 ? 1u : 0u);
+                        tc_mma_bf16(tmem_base + kColF, a_lo, b_hi, idesc_df, 1u);
+                        tc_mma_bf16(tmem_base + kColF, a_hi, b_lo, idesc_df, 1u);
+                    }
+                    if (with_p) {
+                        // P^T[c, k] (+)= F[neighbor, c] * b[neighbor, k] over the neighbors of this pass
+                        for (int kb = 0; kb < rows / 16; ++kb) {
+                            const uint64_t a_hi = umma_desc_mn_sw128(f_hi, kTcRows * 128) + 128ull * kb;
+                            const uint64_t a_lo = umma_desc_mn_sw128(f_lo, kTcRows * 128) + 128ull * kb;
+                            const uint64_t b_off = (uint64_t)(kb >> 2) * ((NB * 128) >> 4) + 2ull * (kb & 3);
+                            const uint64_t b_hi = umma_desc_k_sw128(bt_hi) + b_off, b_lo = umma_desc_k_sw128(bt_lo) + b_off;
+                            tc_mma_bf16(tmem_base + kColP, a_hi, b_hi, idesc_p, (!first || kb > 0) ? 1u : 0u);
+                            tc_mma_bf16(tmem_base + kColP, a_hi, b_lo, idesc_p, 1u);
+                            tc_mma_bf16(tmem_base + kColP, a_lo, b_hi, idesc_p, 1u);
+                        }
                     }
                     tc_commit(bar);
                 }
@@ -535,30 +542,27 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
                     break;
                 }
                 tc_fence_after();
-                // ---- dF row of this neighbor, 32 channels at a time, reduced into the feature gradient
+                // ---- dF^T row of channel cb + tid: one column per neighbor, 32 at a time; the lanes of a warp hold 32
+                // consecutive channels of the same neighbor row, so every reduction below is one 128-byte line
+                {
+                    const int c = cb + tid;
 #pragma unroll 1
-                for (int c0 = 0; c0 < kTcChan && cb + c0 < cin; c0 += 32) {
-                    uint32_t r[32];
-                    tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + 128u + (uint32_t)c0, r);
-                    if (active) {
-                        float* dst = d_feat + (int64_t)n0 * cin + cb + c0;
+                    for (int j0 = 0; j0 < cnt; j0 += 32) {
+                        uint32_t r[32];
+                        tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + kColF + (uint32_t)j0, r);
+                        if (c < cin) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            if (vec && cb + c0 + j + 3 < cin) {
-                                red_add_f32x4(dst + j, __uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    if (cb + c0 + j + e < cin) atomicAdd(dst + j + e, __uint_as_float(r[j + e]));
+                            for (int j = 0; j < 32; ++j) {
+                                if (j0 + j < cnt) atomicAdd(d_feat + (int64_t)s_n0[j0 + j] * cin + c, __uint_as_float(r[j]));
                             }
                         }
                     }
                 }
                 tc_fence_before();
-                __syncthreads();  // the tiles and the dF accumulator are free for the next channel block
+                __syncthreads();  // the tiles and the dF^T accumulator are free for the next channel block
             }
             if (failed) break;
+            first = false;
 
             // ---- lanes as neighbors again: db row -> basis gradient, offset gradient, point gradients
             float db[NB];
@@ -585,7 +589,32 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
                 if (d_pdf && dpdf != 0.f) atomicAdd(d_pdf + n0, dpdf);
             }
             tc_fence_before();
-            __syncthreads();  // db accumulator and BM tile are free for the next pass
+            __syncthreads();  // db accumulator, BT tile and neighbor ids are free for the next pass
+        }
+        if (failed) break;
+        if (with_p) {
+            // ---- P row of the sample: thread = channel, NB accumulator columns -> K entries (zeros without neighbors)
+            tc_fence_after();
+            float acc[NB];
+            if (first) {
+#pragma unroll
+                for (int k = 0; k < NB; ++k) acc[k] = 0.f;
+            } else {
+#pragma unroll
+                for (int k0 = 0; k0 < NB; k0 += 16) {
+                    uint32_t r[16];
+                    tc_ld_32x16(tmem_base + ((uint32_t)(warp * 32) << 16) + kColP + (uint32_t)k0, r);
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) acc[k0 + k] = __uint_as_float(r[k]);
+                }
+            }
+            store_p_row<NB>(acc, tid, cin, K, p_hi, p_lo, prow);
+            for (int c = inner + tid; c < ld_p; c += 128) {
+                p_hi[prow + c] = __float2bfloat16_rn(0.f);
+                p_lo[prow + c] = __float2bfloat16_rn(0.f);
+            }
+            tc_fence_before();
+            __syncthreads();
         }
         if (d_samples) {
 #pragma unroll
@@ -662,7 +691,7 @@ static int launch_backward_tc_nb(int K, const ARGS& args, const float* pts, cons
                                  const float* samples, const int32_t* neighbors, const int32_t* start_ids,
                                  const float* radii, int m_begin, int m_end, const float* d_proj, float* d_feat,
                                  float* d_pts, float* d_samples, float* d_param0, float* d_param1, float* d_pdf,
-                                 int* status, cudaStream_t s) {
+                                 void* p_hi, void* p_lo, int ld_p, int* status, cudaStream_t s) {
     auto kernel = backward_tc_kernel<NB, BASIS, ARGS>;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
@@ -671,10 +700,14 @@ static int launch_backward_tc_nb(int K, const ARGS& args, const float* pts, cons
     });
     PCCNN_CUDA(attr_err);
     const int count = m_end - m_begin;
-    const unsigned grid = (unsigned)(count < sm_count() ? count : sm_count());
+    // two CTAs per SM: 2 x 256 tensor-memory columns and 2 x (tiles + 1 KB) of shared memory
+    const int per_sm = (227 * 1024) / (TcBackwardSmem<NB>::kBytes + 1024) >= 2 ? 2 : 1;
+    const int64_t cap = (int64_t)sm_count() * per_sm;
+    const unsigned grid = (unsigned)(count < cap ? count : cap);
     kernel<<<grid, 128, TcBackwardSmem<NB>::kBytes, s>>>(args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids,
                                                          radii, m_begin, m_end, d_proj, d_feat, d_pts, d_samples, d_param0,
-                                                         d_param1, d_pdf, tensor_core_poll_limit(), status);
+                                                         d_param1, d_pdf, (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo, ld_p,
+                                                         tensor_core_poll_limit(), status);
     PCCNN_LAUNCH_CHECK();
     return PCCNN_OK;
 }
@@ -683,19 +716,20 @@ template <class ARGS, template <int, int> class BASIS>
 static int launch_backward_tc(int K, const ARGS& args, const float* pts, const FeaturePlanes& feats, int cin, const float* samples,
                               const int32_t* neighbors, const int32_t* start_ids, const float* radii, int m_begin,
                               int m_end, const float* d_proj, float* d_feat, float* d_pts, float* d_samples,
-                              float* d_param0, float* d_param1, float* d_pdf, int* status, cudaStream_t s) {
+                              float* d_param0, float* d_param1, float* d_pdf, void* p_hi, void* p_lo, int ld_p, int* status,
+                              cudaStream_t s) {
     if (m_end <= m_begin) return PCCNN_OK;
     if (K <= 16)
         return launch_backward_tc_nb<16, BASIS<3, 16>, ARGS>(K, args, pts, feats, cin, samples, neighbors, start_ids, radii,
                                                              m_begin, m_end, d_proj, d_feat, d_pts, d_samples, d_param0,
-                                                             d_param1, d_pdf, status, s);
+                                                             d_param1, d_pdf, p_hi, p_lo, ld_p, status, s);
     if (K <= 32)
         return launch_backward_tc_nb<32, BASIS<3, 32>, ARGS>(K, args, pts, feats, cin, samples, neighbors, start_ids, radii,
                                                              m_begin, m_end, d_proj, d_feat, d_pts, d_samples, d_param0,
-                                                             d_param1, d_pdf, status, s);
+                                                             d_param1, d_pdf, p_hi, p_lo, ld_p, status, s);
     return launch_backward_tc_nb<64, BASIS<3, 64>, ARGS>(K, args, pts, feats, cin, samples, neighbors, start_ids, radii,
                                                          m_begin, m_end, d_proj, d_feat, d_pts, d_samples, d_param0,
-                                                         d_param1, d_pdf, status, s);
+                                                         d_param1, d_pdf, p_hi, p_lo, ld_p, status, s);
 }
 
 }  // namespace pccnn

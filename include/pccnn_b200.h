@@ -301,6 +301,23 @@ int pccnn_kp_conv_bf16(int D, int64_t num_pts, const float* pts, const void* fea
                        int num_kernel_pts, float sigma, const void* weights_bf16, int cout, void* out_bf16,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* KPConv forward WITHOUT a neighbor list (3-D points): the projection kernel finds the neighbors of every sample on
+ * the grid itself -- the 27-cell stencil and the exact radius predicate of the search -- so the [T, 2] list of
+ * find_neighbors is neither written nor read.  Same result as pccnn_find_neighbors_* followed by pccnn_kp_conv(_bf16)
+ * (rows in the same ascending order).  Replaces the sequence __create_neighborhood__ + kp_conv of
+ * pccnn_lib/pc/layers/KPConv.py:127-146,118-123 of the reference for inference.
+ * sorted_pts / sorted_keys [num_pts]: the points in grid order with their keys (pccnn_sort_keys); grid_ds, grid_size,
+ * radii (= cell size) as for the search; samples [num_samples, 3] with their keys on the same grid, any order.
+ * feats [num_pts, cin] are in the CALLER's order: pt_index_map[j] (the sort permutation; NULL = identity) is the
+ * feature row of sorted position j.  feats_are_bf16 != 0: features, weights and output are bf16 (one tensor-core
+ * pass, as pccnn_kp_conv_bf16), otherwise fp32.  Scratch: pccnn_kp_conv_grid_workspace_bytes. */
+size_t pccnn_kp_conv_grid_workspace_bytes(int64_t num_pts, int64_t num_samples, int cin, int num_kernel_pts, int cout);
+int pccnn_kp_conv_grid(int64_t num_pts, const float* sorted_pts, const int64_t* sorted_keys, const int64_t* pt_index_map,
+                       const void* feats, int feats_are_bf16, int cin, int64_t num_samples, const float* samples,
+                       const int64_t* sample_keys, const int32_t* grid_ds, const int32_t* grid_size, const float* radii,
+                       const float* kernel_pts, int num_kernel_pts, float sigma, const void* weights, int cout, void* out,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* MCConv forward: basis b[t,:] = leaky_relu_{0.2}(d_t . axis + bias) / pdf[n0(t)], axis [D, hidden],
  * bias [hidden], weights [num_mlps, hidden / num_mlps * cin, cout / num_mlps] (hidden counts the
  * units of all MLPs together, as the reference's proj_axis_ does).

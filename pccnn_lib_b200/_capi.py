@@ -53,6 +53,9 @@ SIGNATURES = {
     "pccnn_conv_workspace_bytes": (_size, [_c_i64, _c_i64, _c_int, _c_int, _c_int]),
     "pccnn_kp_conv": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
                                ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
+    "pccnn_kp_conv_grid_workspace_bytes": (_size, [_c_i64, _c_i64, _c_int, _c_int, _c_int]),
+    "pccnn_kp_conv_grid": (_c_int, [_c_i64, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+                                    _c_int, ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
     "pccnn_kp_conv_bf16": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int,
                                     ctypes.c_float, _ptr, _c_int, _ptr, _ptr, _size, _ptr]),
     "pccnn_mc_conv": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,

@@ -45,6 +45,23 @@ int pccnn_kp_conv(int D, int64_t num_pts, const float* pts, const float* feats, 
                                               workspace_bytes, (cudaStream_t)stream);
 }
 
+size_t pccnn_kp_conv_grid_workspace_bytes(int64_t num_pts, int64_t num_samples, int cin, int num_kernel_pts, int cout) {
+    return conv_grid_layout(num_pts < 0 ? 0 : num_pts, num_samples < 0 ? 0 : num_samples, cin, num_kernel_pts, cout).total;
+}
+
+int pccnn_kp_conv_grid(int64_t num_pts, const float* sorted_pts, const int64_t* sorted_keys, const int64_t* pt_index_map,
+                       const void* feats, int feats_are_bf16, int cin, int64_t num_samples, const float* samples,
+                       const int64_t* sample_keys, const int32_t* grid_ds, const int32_t* grid_size, const float* radii,
+                       const float* kernel_pts, int num_kernel_pts, float sigma, const void* weights, int cout, void* out,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+    PCCNN_CHECK_ARG(kernel_pts && sigma > 0.f, "kp_conv_grid: kernel points missing or sigma <= 0");
+    KPBasisArgs args{kernel_pts, 1.0f / sigma};
+    return conv_forward_grid<KPBasisArgs, KPBasis>("kp_conv_grid", num_kernel_pts, args, num_pts, sorted_pts, sorted_keys,
+                                                   pt_index_map, feats, feats_are_bf16, cin, num_samples, samples, sample_keys,
+                                                   grid_ds, grid_size, radii, weights, cout, out, workspace, workspace_bytes,
+                                                   (cudaStream_t)stream);
+}
+
 int pccnn_kp_conv_bf16(int D, int64_t num_pts, const float* pts, const void* feats_bf16, int cin, int64_t num_samples,
                        const float* samples, const int32_t* neighbors, const int32_t* start_ids, const float* radii,
                        const float* kernel_pts, int num_kernel_pts, float sigma, const void* weights_bf16, int cout,
@@ -67,6 +84,14 @@ int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, co
                                                 samples, neighbors, start_ids, radii, num_mlps, weights, cout, out,
                                                 workspace, workspace_bytes, (cudaStream_t)stream);
 }
+
+#ifdef PCCNN_TC_PROFILE
+int pccnn_debug_tc_profile(long long* out16) {
+    PCCNN_CUDA(cudaDeviceSynchronize());
+    PCCNN_CUDA(cudaMemcpyFromSymbol(out16, g_tc_prof, sizeof(long long) * 16));
+    return PCCNN_OK;
+}
+#endif
 
 int pccnn_conv_set_path(int path) {
     PCCNN_CHECK_ARG(path == 0 || path == 1, "conv_set_path: 0 (tensor-core pair kernels where they apply) or 1 (CUDA cores)");

@@ -853,6 +853,88 @@ static int conv_forward(const char* who, int D, int K, const ARGS& args, int64_t
     return publish_status(status, kOriginConvForward, s);
 }
 
+// ---- forward without a neighbor list ------------------------------------------------------------------------
+struct ConvGridLayout {
+    ConvLayout base;
+    size_t f_hi_off, f_lo_off, total;
+};
+
+static ConvGridLayout conv_grid_layout(int64_t num_pts, int64_t num_samples, int cin, int K, int cout) {
+    ConvGridLayout G;
+    G.base = conv_layout(0, num_samples, cin, K, cout);  // the planes of the list-based path are not needed
+    const size_t plane = align_up((size_t)(num_pts > 0 ? num_pts : 1) * ((cin + 7) / 8 * 8) * 2);
+    G.f_hi_off = G.base.f_hi_off;
+    G.f_lo_off = G.f_hi_off + plane;
+    G.total = G.f_lo_off + plane;
+    return G;
+}
+
+// out = P W with P from project_tc_grid_kernel: the neighbors are found on the grid inside the projection, no list.
+// Points, keys and table as the search takes them (grid order); `pt_index_map` (may be null = identity) maps a sorted
+// position to the row of `feats`, which are in the caller's order.  3-D points.
+template <class ARGS, template <int, int> class BASIS>
+static int conv_forward_grid(const char* who, int K, const ARGS& args, int64_t num_pts, const float* sorted_pts,
+                             const int64_t* sorted_keys, const int64_t* pt_index_map, const void* feats_any, int io_bf16,
+                             int cin, int64_t num_samples, const float* samples, const int64_t* sample_keys,
+                             const int32_t* grid_ds, const int32_t* grid_size, const float* radii, const void* weights_any,
+                             int cout, void* out_any, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+    if (int rc = take_sticky_status(who)) return rc;
+    PCCNN_CHECK_ARG(K >= 1 && K <= 64, "%s: basis size %d outside [1, 64]", who, K);
+    PCCNN_CHECK_ARG(cin >= 1 && cout >= 1, "%s: bad channel counts (cin %d, cout %d)", who, cin, cout);
+    PCCNN_CHECK_ARG(num_samples >= 0 && num_samples < 0x7fffffffLL && num_pts >= 0 && num_pts < 0x7fffffffLL, "%s: bad sizes", who);
+    if (num_samples == 0) return PCCNN_OK;
+    PCCNN_CHECK_ARG(samples && sample_keys && grid_ds && grid_size && radii && weights_any && out_any, "%s: null pointer", who);
+    PCCNN_CHECK_ARG(num_pts == 0 || (sorted_pts && sorted_keys && feats_any), "%s: null points", who);
+    const ConvGridLayout G = conv_grid_layout(num_pts, num_samples, cin, K, cout);
+    const ConvLayout& L = G.base;
+    if (!workspace || workspace_bytes < G.total) {
+        set_error("%s: workspace of %zu bytes, need %zu", who, workspace_bytes, G.total);
+        return PCCNN_ERR_WORKSPACE;
+    }
+    char* ws = (char*)workspace;
+    int* status = (int*)(ws + L.status_off);
+    PCCNN_CUDA(cudaMemsetAsync(status, 0, 4, s));
+    PCCNN_CUDA(cudaMemsetAsync(ws + L.w_hi_off, 0, L.status_off - L.w_hi_off, s));
+    const int inner = cin * K;
+    int rc;
+    if (io_bf16)
+        rc = transpose_bf16(inner, cout, weights_any, cout, L.ld_p, ws + L.w_hi_off, s);
+    else
+        rc = split_bf16_transpose(inner, cout, (const float*)weights_any, cout, L.ld_p, ws + L.w_hi_off, ws + L.w_lo_off, s);
+    if (rc) return rc;
+    // feature planes in grid order
+    __nv_bfloat16* f_hi = (__nv_bfloat16*)(ws + G.f_hi_off);
+    __nv_bfloat16* f_lo = io_bf16 ? nullptr : (__nv_bfloat16*)(ws + G.f_lo_off);
+    if (num_pts > 0) {
+        const unsigned grid = grid_for(num_pts * (L.ld_f / 8), 256, 8);
+        if (io_bf16)
+            permute_features_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(num_pts, cin, L.ld_f, (const __nv_bfloat16*)feats_any,
+                                                                         pt_index_map, f_hi, f_lo);
+        else
+            permute_features_kernel<float><<<grid, 256, 0, s>>>(num_pts, cin, L.ld_f, (const float*)feats_any, pt_index_map,
+                                                                f_hi, f_lo);
+        PCCNN_LAUNCH_CHECK();
+    }
+    const FeaturePlanes planes{f_hi, f_lo, L.ld_f};
+    for (int64_t m0 = 0; m0 < num_samples; m0 += L.chunk) {
+        const int64_t m1 = (m0 + L.chunk < num_samples) ? m0 + L.chunk : num_samples;
+        if (io_bf16)
+            rc = launch_project_tc_grid<ARGS, BASIS, false>(K, args, (int)num_pts, sorted_pts, sorted_keys, planes, cin,
+                                                            (int)num_samples, samples, sample_keys, grid_ds, grid_size, radii,
+                                                            (int)m0, (int)m1, ws + L.p_hi_off, nullptr, L.ld_p, status, s);
+        else
+            rc = launch_project_tc_grid<ARGS, BASIS, true>(K, args, (int)num_pts, sorted_pts, sorted_keys, planes, cin,
+                                                           (int)num_samples, samples, sample_keys, grid_ds, grid_size, radii,
+                                                           (int)m0, (int)m1, ws + L.p_hi_off, ws + L.p_lo_off, L.ld_p, status, s);
+        if (rc) return rc;
+        GemmOperand a{ws + L.p_hi_off, io_bf16 ? nullptr : ws + L.p_lo_off, L.ld_p};
+        GemmOperand b{ws + L.w_hi_off, io_bf16 ? nullptr : ws + L.w_lo_off, L.ld_p};
+        float* c_ptr = io_bf16 ? (float*)((__nv_bfloat16*)out_any + (size_t)m0 * cout) : (float*)out_any + (size_t)m0 * cout;
+        if ((rc = gemm_bf16_nt(a, b, c_ptr, m1 - m0, cout, L.ld_p, cout, status, s, io_bf16 ? 1 : 0))) return rc;
+    }
+    return publish_status(status, kOriginConvForward, s);
+}
+
 struct ConvBackwardLayout {
     int ld_p, ld_g;
     int64_t chunk;

@@ -26,6 +26,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "stencil.cuh"
 #include "tc_ptx.cuh"
 
 namespace pccnn {
@@ -168,7 +169,15 @@ struct TcForwardSmem {
     static constexpr int kTiles = 2 * kF + 2 * kBT;
     static constexpr int kMisc = 2048;  // barrier, tensor-memory slot, neighbor ids, basis parameters
     static constexpr int kBytes = kTiles + kMisc;
+    static constexpr int kGridBytes = kTiles + 2688;  // list-free variant: + candidate ranges and the hit queue
 };
+
+#ifdef PCCNN_TC_PROFILE
+static __device__ long long g_tc_prof[16];
+#define TC_PROF(i) do { if (blockIdx.x == 0 && tid == 0) { long long now_ = clock64(); prof_[i] += now_ - last_; last_ = now_; } } while (0)
+#else
+#define TC_PROF(i) do {} while (0)
+#endif
 
 // P rows (bf16 hi [+ lo]) of the samples [m_begin, m_end).  One CTA = one sample at a time.
 template <int NB, class BASIS, class ARGS, bool SPLIT_F>
@@ -220,87 +229,64 @@ project_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes
     uint32_t parity = 0;
     bool failed = false;
 
-    for (int m = m_begin + blockIdx.x; m < m_end && !failed; m += gridDim.x) {
-        const int lo = (m > 0) ? __ldg(start_ids + m - 1) : 0;
-        const int hi = __ldg(start_ids + m);
+    // The work of this CTA is a flat sequence of passes (sample, channel block, 128 neighbors), run as a software
+    // pipeline: the loads a pass depends on (the sample's range, the neighbor ids, the neighbors' coordinates) are
+    // issued one pass ahead, and the epilogue of a finished (sample, channel block) runs while the feature rows of
+    // the next pass are being copied.
+    struct Sample {
+        int m, lo, hi;
         float s[3];
+    };
+    auto load_sample = [&](int m) {
+        Sample q;
+        q.m = m;
+        q.lo = q.hi = 0;
+        q.s[0] = q.s[1] = q.s[2] = 0.f;
+        if (m < m_end) {
+            q.lo = (m > 0) ? __ldg(start_ids + m - 1) : 0;
+            q.hi = __ldg(start_ids + m);
 #pragma unroll
-        for (int d = 0; d < 3; ++d) s[d] = BASIS::kUsesOffset ? __ldg(samples + (int64_t)m * 3 + d) : 0.f;
-        const size_t row = (size_t)(m - m_begin) * ld_p;
+            for (int d = 0; d < 3; ++d) q.s[d] = BASIS::kUsesOffset ? __ldg(samples + (int64_t)m * 3 + d) : 0.f;
+        }
+        return q;
+    };
+    auto load_id = [&](bool valid, int t0, int hi) {
+        return (valid && t0 + tid < hi) ? __ldg(&neighbors[t0 + tid]).x : -1;
+    };
+    auto load_point = [&](int n0, float (&q)[3]) {
+#pragma unroll
+        for (int x = 0; x < 3; ++x) q[x] = (BASIS::kUsesOffset && n0 >= 0) ? __ldg(pts + (int64_t)n0 * 3 + x) : 0.f;
+    };
 
-        for (int cb = 0; cb < cin && !failed; cb += kTcChan) {
-            bool first = true;
-            for (int t0 = lo; t0 < hi; t0 += kTcRows) {
-                const int cnt = min(kTcRows, hi - t0);
-                const int rows = (cnt + 15) & ~15;
-                // ---- the neighbor of this thread; the copies of all feature rows start as soon as the ids are staged
-                const int t = t0 + tid;
-                const int n0 = (tid < cnt) ? __ldg(&neighbors[t]).x : -1;
-                s_n0[tid] = n0;
-                __syncthreads();
-                gather_features_async<SPLIT_F>(f_hi, f_lo, s_n0, rows, feats, cb);
-                // ---- lanes as neighbors, while the copies are in flight: offset, basis, BT column of pair t0 + tid
-                {
-                    float b[NB];
-                    if (tid < cnt) {
-                        float d[3];
-#pragma unroll
-                        for (int x = 0; x < 3; ++x)
-                            d[x] = BASIS::kUsesOffset ? (__ldg(pts + (int64_t)n0 * 3 + x) - s[x]) * inv[x] : 0.f;
-                        BASIS::eval(s_params, args, K, d, n0, t, m, b);
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < NB; ++k) b[k] = 0.f;
-                    }
-                    if (tid < rows) {
-                        uint8_t* base_hi = smem + SM::kBTHi + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
-                        uint8_t* base_lo = smem + SM::kBTLo + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
-                        const int chunk = (tid & 63) >> 3;
-#pragma unroll
-                        for (int k = 0; k < NB; ++k) {
-                            const __nv_bfloat16 h = __float2bfloat16_rn(b[k]);
-                            const uint32_t off = sw128_offset(k, chunk);
-                            *reinterpret_cast<__nv_bfloat16*>(base_hi + off) = h;
-                            *reinterpret_cast<__nv_bfloat16*>(base_lo + off) = __float2bfloat16_rn(b[k] - __bfloat162float(h));
-                        }
-                    }
-                }
-                cp_async_wait_all();
-                fence_smem_to_async_proxy();
-                __syncthreads();
-                if (tid == 0) {
-                    tc_fence_after();
-                    for (int kb = 0; kb < rows / 16; ++kb) {
-                        // A: 16 neighbor rows further = 2048 bytes = +128 in 16-byte units; the two 64-channel blocks
-                        // are 16 KB apart (leading byte offset).  B: 64-neighbor block kb / 4, 16 neighbors = +2.
-                        const uint64_t a_hi = umma_desc_mn_sw128(f_hi, kTcRows * 128) + 128ull * kb;
-                        const uint64_t b_off = (uint64_t)(kb >> 2) * ((NB * 128) >> 4) + 2ull * (kb & 3);
-                        const uint64_t b_hi = umma_desc_k_sw128(bt_hi) + b_off, b_lo = umma_desc_k_sw128(bt_lo) + b_off;
-                        tc_mma_bf16(tmem_base, a_hi, b_hi, idesc, (!first || kb > 0) ? 1u : 0u);
-                        tc_mma_bf16(tmem_base, a_hi, b_lo, idesc, 1u);
-                        if (SPLIT_F) {
-                            const uint64_t a_lo = umma_desc_mn_sw128(f_lo, kTcRows * 128) + 128ull * kb;
-                            tc_mma_bf16(tmem_base, a_lo, b_hi, idesc, 1u);
-                        }
-                    }
-                    tc_commit(bar);
-                }
-                // one thread polls for the MMAs (they have read the tiles, which the next pass overwrites); the others
-                // wait at the block barrier, which costs no issue slots
-                const bool ok = (tid != 0) || mbar_wait(bar, parity, poll_limit);
-                parity ^= 1u;
-                if (__syncthreads_or(ok ? 0 : 1)) {
-                    failed = true;
-                    break;
-                }
-                first = false;
-            }
-            if (failed) break;
-            // ---- epilogue: thread = channel cb + tid, NB accumulator columns -> K entries of the P row
+    Sample cur = load_sample(m_begin + blockIdx.x);
+    Sample ahead = load_sample(cur.m + gridDim.x);  // its loads are in flight while `cur` is processed
+    int cb = 0, t0 = cur.lo;
+    bool cur_valid = cur.m < m_end;
+    int n0 = load_id(cur_valid, t0, cur.hi);
+    float pt[3];
+    load_point(n0, pt);
+    // the (sample, channel block) whose accumulator waits for its epilogue
+    bool epi = false, epi_nonempty = false;
+    int epi_m = 0, epi_cb = 0;
+
+#ifdef PCCNN_TC_PROFILE
+    long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}, last_ = clock64();
+#endif
+    while ((cur_valid || epi) && !failed) {
+        const int cnt = cur_valid ? min(kTcRows, cur.hi - t0) : 0;
+        const int rows = (cnt + 15) & ~15;
+        s_n0[tid] = n0;
+        __syncthreads();
+        TC_PROF(0);
+        if (cnt > 0) gather_features_async<SPLIT_F>(f_hi, f_lo, s_n0, rows, feats, cb);
+        TC_PROF(1);
+
+        // ---- epilogue of the previous (sample, channel block): thread = channel, NB columns -> K entries of the P row
+        if (epi) {
             tc_fence_after();
-            const int c = cb + tid;
+            const size_t row = (size_t)(epi_m - m_begin) * ld_p;
             float acc[NB];
-            if (first) {  // no neighbor at all: the accumulator was never written
+            if (!epi_nonempty) {  // no neighbor at all: the accumulator was never written
 #pragma unroll
                 for (int k = 0; k < NB; ++k) acc[k] = 0.f;
             } else {
@@ -312,16 +298,114 @@ project_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes
                     for (int k = 0; k < 16; ++k) acc[k0 + k] = __uint_as_float(r[k]);
                 }
             }
-            store_p_row<NB>(acc, c, cin, K, p_hi, p_lo, row);
-            tc_fence_before();
-            __syncthreads();  // the accumulator is free for the next channel block / sample
+            store_p_row<NB>(acc, epi_cb + tid, cin, K, p_hi, p_lo, row);
+            if (epi_cb + kTcChan >= cin) {  // last channel block: the padding columns feed the contraction too
+                for (int c = inner + tid; c < ld_p; c += 128) {
+                    p_hi[row + c] = __float2bfloat16_rn(0.f);
+                    if (p_lo) p_lo[row + c] = __float2bfloat16_rn(0.f);
+                }
+            }
+            epi = false;
         }
-        // padding columns feed the contraction too: keep them zero
-        for (int c = inner + tid; c < ld_p; c += 128) {
-            p_hi[row + c] = __float2bfloat16_rn(0.f);
-            if (p_lo) p_lo[row + c] = __float2bfloat16_rn(0.f);
+        TC_PROF(2);
+
+        // ---- the pass after this one, and its first loads
+        Sample nxt = cur;
+        int nxt_cb = cb, nxt_t0 = t0 + kTcRows;
+        bool nxt_valid = cur_valid;
+        const bool last_of_block = cur_valid && nxt_t0 >= cur.hi;
+        if (last_of_block) {
+            nxt_cb = cb + kTcChan;
+            nxt_t0 = cur.lo;
+            if (nxt_cb >= cin) {
+                nxt = ahead;
+                nxt_cb = 0;
+                nxt_t0 = nxt.lo;
+                nxt_valid = nxt.m < m_end;
+                ahead = load_sample(nxt.m + gridDim.x);
+            }
         }
+        const int n0_next = load_id(nxt_valid, nxt_t0, nxt.hi);
+
+        // ---- lanes as neighbors, while the copies are in flight: offset, basis, BT column of pair t0 + tid
+        if (cnt > 0) {
+            float b[NB];
+            if (tid < cnt) {
+                float d[3];
+#pragma unroll
+                for (int x = 0; x < 3; ++x) d[x] = (pt[x] - cur.s[x]) * inv[x];
+                BASIS::eval(s_params, args, K, d, n0, t0 + tid, cur.m, b);
+            } else {
+#pragma unroll
+                for (int k = 0; k < NB; ++k) b[k] = 0.f;
+            }
+            if (tid < rows) {
+                uint8_t* base_hi = smem + SM::kBTHi + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                uint8_t* base_lo = smem + SM::kBTLo + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                const int chunk = (tid & 63) >> 3;
+#pragma unroll
+                for (int k = 0; k < NB; ++k) {
+                    const __nv_bfloat16 h = __float2bfloat16_rn(b[k]);
+                    const uint32_t off = sw128_offset(k, chunk);
+                    *reinterpret_cast<__nv_bfloat16*>(base_hi + off) = h;
+                    *reinterpret_cast<__nv_bfloat16*>(base_lo + off) = __float2bfloat16_rn(b[k] - __bfloat162float(h));
+                }
+            }
+        }
+        TC_PROF(3);
+        cp_async_wait_all();
+        fence_smem_to_async_proxy();
+        tc_fence_before();
+        __syncthreads();
+        TC_PROF(4);
+        if (cnt > 0 && tid == 0) {
+            tc_fence_after();
+            const bool first = t0 == cur.lo;
+            for (int kb = 0; kb < rows / 16; ++kb) {
+                // A: 16 neighbor rows further = 2048 bytes = +128 in 16-byte units; the two 64-channel blocks
+                // are 16 KB apart (leading byte offset).  B: 64-neighbor block kb / 4, 16 neighbors = +2.
+                const uint64_t a_hi = umma_desc_mn_sw128(f_hi, kTcRows * 128) + 128ull * kb;
+                const uint64_t b_off = (uint64_t)(kb >> 2) * ((NB * 128) >> 4) + 2ull * (kb & 3);
+                const uint64_t b_hi = umma_desc_k_sw128(bt_hi) + b_off, b_lo = umma_desc_k_sw128(bt_lo) + b_off;
+                tc_mma_bf16(tmem_base, a_hi, b_hi, idesc, (!first || kb > 0) ? 1u : 0u);
+                tc_mma_bf16(tmem_base, a_hi, b_lo, idesc, 1u);
+                if (SPLIT_F) {
+                    const uint64_t a_lo = umma_desc_mn_sw128(f_lo, kTcRows * 128) + 128ull * kb;
+                    tc_mma_bf16(tmem_base, a_lo, b_hi, idesc, 1u);
+                }
+            }
+            tc_commit(bar);
+        }
+        TC_PROF(5);
+        // the coordinates of the next pass's neighbors travel while the MMAs run
+        float pt_next[3];
+        load_point(n0_next, pt_next);
+        if (cnt > 0) {
+            // one thread polls for the MMAs (they have read the tiles, which the next pass overwrites); the others
+            // wait at the block barrier, which costs no issue slots
+            const bool ok = (tid != 0) || mbar_wait(bar, parity, poll_limit);
+            parity ^= 1u;
+            if (__syncthreads_or(ok ? 0 : 1)) failed = true;
+        }
+        TC_PROF(6);
+        if (last_of_block) {
+            epi = true;
+            epi_nonempty = cur.hi > cur.lo;
+            epi_m = cur.m;
+            epi_cb = cb;
+        }
+        cur = nxt;
+        cb = nxt_cb;
+        t0 = nxt_t0;
+        cur_valid = nxt_valid;
+        n0 = n0_next;
+#pragma unroll
+        for (int x = 0; x < 3; ++x) pt[x] = pt_next[x];
     }
+#ifdef PCCNN_TC_PROFILE
+    if (blockIdx.x == 0 && tid == 0)
+        for (int i = 0; i < 8; ++i) g_tc_prof[i] = prof_[i];
+#endif
     if (failed && tid == 0) {
         atomicExch(status, 5);
         mbar_wait(bar, parity ^ 1u, poll_limit);  // once more, bounded: MMAs still in flight must not outlive tensor memory
@@ -730,6 +814,278 @@ static int launch_backward_tc(int K, const ARGS& args, const float* pts, const F
     return launch_backward_tc_nb<64, BASIS<3, 64>, ARGS>(K, args, pts, feats, cin, samples, neighbors, start_ids, radii,
                                                          m_begin, m_end, d_proj, d_feat, d_pts, d_samples, d_param0,
                                                          d_param1, d_pdf, p_hi, p_lo, ld_p, status, s);
+}
+
+// ---- projection without a neighbor list -----------------------------------------------------------------------
+// The same P rows as project_tc_kernel, for callers that hold the grid instead of a neighbor list: the CTA finds the
+// neighbors of its sample itself -- the candidate ranges of the sample's 27-cell stencil (find_ranges_grid_ds.cu:
+// 65-166 of the reference, resolved as the search kernel does), the radius predicate of count_neighbors.cu:87 with its
+// exact operation order -- compacts the hits in ascending position and runs the tensor-core pass on every 128 of
+// them.  The list [T, 2] is never written or read.  Points and feature planes are in grid order (sorted position =
+// row), samples in any order.
+template <int NB, class BASIS, class ARGS, bool SPLIT_F>
+__global__ void __launch_bounds__(128)
+project_tc_grid_kernel(ARGS args, int K, int num_pts, const float* __restrict__ sorted_pts,
+                       const int64_t* __restrict__ sorted_keys, FeaturePlanes feats, int cin, int num_samples,
+                       const float* __restrict__ samples, const int64_t* __restrict__ sample_keys,
+                       const int2* __restrict__ grid_ds, const int32_t* __restrict__ grid_size,
+                       const float* __restrict__ radii, int m_begin, int m_end, __nv_bfloat16* __restrict__ p_hi,
+                       __nv_bfloat16* __restrict__ p_lo, int ld_p, uint32_t poll_limit, int* __restrict__ status) {
+    using SM = TcForwardSmem<NB>;
+    using S = Stencil<3>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    uint8_t* misc = smem + SM::kTiles;
+    uint64_t* bar = (uint64_t*)misc;
+    uint32_t* tmem_slot = (uint32_t*)(misc + 8);
+    int* s_warp_hits = (int*)(misc + 16);          // [4]
+    int* s_lo = (int*)(misc + 32);                 // [9]
+    int* s_pref = (int*)(misc + 32 + 40);          // [10]
+    int* s_n0 = (int*)(misc + 128);                // [128] ids of the pass being run
+    float* s_params = (float*)(misc + 128 + 512);  // up to 256 floats
+    int* s_q_id = (int*)(misc + 128 + 512 + 1024); // [256] hits waiting for a pass: up to 127 left over + 128 new ones
+    static_assert(BASIS::kParamFloats <= 256, "basis parameters do not fit the shared-memory slot");
+    constexpr uint32_t kTmemCols = NB < 32 ? 32 : NB;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    BASIS::load_params(s_params, args, K);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const GridDesc<3> g = load_grid<3>(grid_size);
+    float inv[3];
+#pragma unroll
+    for (int d = 0; d < 3; ++d) inv[d] = __frcp_rn(__ldg(radii + d));
+    const int inner = cin * K;
+    const uint32_t f_hi = smem_u32(smem + SM::kFHi), f_lo = smem_u32(smem + SM::kFLo);
+    const uint32_t bt_hi = smem_u32(smem + SM::kBTHi), bt_lo = smem_u32(smem + SM::kBTLo);
+    constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)(NB >> 3) << 17) |
+                               ((uint32_t)(128 >> 4) << 24);
+    uint32_t parity = 0;
+    bool failed = false;
+
+    for (int m = m_begin + blockIdx.x; m < m_end && !failed; m += gridDim.x) {
+        float s[3];
+#pragma unroll
+        for (int d = 0; d < 3; ++d) s[d] = __ldg(samples + (int64_t)m * 3 + d);
+        const size_t row = (size_t)(m - m_begin) * ld_p;
+        int num_cand = 0;
+        if (warp == 0) num_cand = resolve_ranges<3>(__ldg(sample_keys + m), g, grid_ds, sorted_keys, num_pts, s_lo, s_pref);
+        __syncthreads();
+        num_cand = s_pref[S::kRanges];
+
+        for (int cb = 0; cb < cin && !failed; cb += kTcChan) {
+            bool first = true;
+            int queued = 0;  // hits waiting in s_q_id
+            int base = 0;    // candidates tested so far
+            while (true) {
+                // ---- 128 candidates: exact radius test, hits appended to the queue in ascending position
+                if (base < num_cand) {
+                    const int gidx = base + tid;
+                    bool hit = false;
+                    int j = 0;
+                    if (gidx < num_cand) {
+                        int r = 0;
+                        while (gidx >= s_pref[r + 1]) ++r;
+                        j = s_lo[r] + gidx - s_pref[r];
+                        float acc = 0.f;
+#pragma unroll
+                        for (int d = 0; d < 3; ++d) {
+                            const float v = __fmul_rn(__fsub_rn(s[d], __ldg(sorted_pts + (int64_t)j * 3 + d)), inv[d]);
+                            acc = (d == 0) ? __fmul_rn(v, v) : __fmaf_rn(v, v, acc);
+                        }
+                        hit = acc < 1.0f;
+                    }
+                    const unsigned bal = __ballot_sync(kFullMask, hit);
+                    if (lane == 0) s_warp_hits[warp] = __popc(bal);
+                    __syncthreads();
+                    int before = queued;
+                    for (int w = 0; w < warp; ++w) before += s_warp_hits[w];
+                    if (hit) s_q_id[before + __popc(bal & ((1u << lane) - 1u))] = j;
+                    queued += s_warp_hits[0] + s_warp_hits[1] + s_warp_hits[2] + s_warp_hits[3];
+                    base += 128;
+                    __syncthreads();
+                }
+                const bool all_tested = base >= num_cand;
+                if (queued < kTcRows && !all_tested) continue;
+                if (queued == 0) break;
+
+                // ---- one pass over the first min(128, queued) hits
+                const int cnt = min(kTcRows, queued);
+                const int rows = (cnt + 15) & ~15;
+                const int n0 = tid < cnt ? s_q_id[tid] : -1;
+                const int moved = tid + kTcRows < queued ? s_q_id[tid + kTcRows] : -1;  // does not fit this pass
+                s_n0[tid] = n0;
+                __syncthreads();
+                if (moved >= 0) s_q_id[tid] = moved;  // the queue's tail moves to its front
+                queued -= cnt;
+                gather_features_async<SPLIT_F>(f_hi, f_lo, s_n0, rows, feats, cb);
+                {
+                    float b[NB];
+                    if (tid < cnt) {
+                        float d[3];
+#pragma unroll
+                        for (int x = 0; x < 3; ++x) d[x] = (__ldg(sorted_pts + (int64_t)n0 * 3 + x) - s[x]) * inv[x];
+                        BASIS::eval(s_params, args, K, d, n0, 0, m, b);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < NB; ++k) b[k] = 0.f;
+                    }
+                    if (tid < rows) {
+                        uint8_t* base_hi = smem + SM::kBTHi + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                        uint8_t* base_lo = smem + SM::kBTLo + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
+                        const int chunk = (tid & 63) >> 3;
+#pragma unroll
+                        for (int k = 0; k < NB; ++k) {
+                            const __nv_bfloat16 h = __float2bfloat16_rn(b[k]);
+                            const uint32_t off = sw128_offset(k, chunk);
+                            *reinterpret_cast<__nv_bfloat16*>(base_hi + off) = h;
+                            *reinterpret_cast<__nv_bfloat16*>(base_lo + off) = __float2bfloat16_rn(b[k] - __bfloat162float(h));
+                        }
+                    }
+                }
+                cp_async_wait_all();
+                fence_smem_to_async_proxy();
+                __syncthreads();
+                if (tid == 0) {
+                    tc_fence_after();
+                    for (int kb = 0; kb < rows / 16; ++kb) {
+                        const uint64_t a_hi = umma_desc_mn_sw128(f_hi, kTcRows * 128) + 128ull * kb;
+                        const uint64_t b_off = (uint64_t)(kb >> 2) * ((NB * 128) >> 4) + 2ull * (kb & 3);
+                        const uint64_t b_hi = umma_desc_k_sw128(bt_hi) + b_off, b_lo = umma_desc_k_sw128(bt_lo) + b_off;
+                        tc_mma_bf16(tmem_base, a_hi, b_hi, idesc, (!first || kb > 0) ? 1u : 0u);
+                        tc_mma_bf16(tmem_base, a_hi, b_lo, idesc, 1u);
+                        if (SPLIT_F) {
+                            const uint64_t a_lo = umma_desc_mn_sw128(f_lo, kTcRows * 128) + 128ull * kb;
+                            tc_mma_bf16(tmem_base, a_lo, b_hi, idesc, 1u);
+                        }
+                    }
+                    tc_commit(bar);
+                }
+                const bool ok = (tid != 0) || mbar_wait(bar, parity, poll_limit);
+                parity ^= 1u;
+                if (__syncthreads_or(ok ? 0 : 1)) {
+                    failed = true;
+                    break;
+                }
+                first = false;
+            }
+            if (failed) break;
+            // ---- epilogue: thread = channel cb + tid
+            tc_fence_after();
+            float acc[NB];
+            if (first) {
+#pragma unroll
+                for (int k = 0; k < NB; ++k) acc[k] = 0.f;
+            } else {
+#pragma unroll
+                for (int k0 = 0; k0 < NB; k0 += 16) {
+                    uint32_t r[16];
+                    tc_ld_32x16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)k0, r);
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) acc[k0 + k] = __uint_as_float(r[k]);
+                }
+            }
+            store_p_row<NB>(acc, cb + tid, cin, K, p_hi, p_lo, row);
+            tc_fence_before();
+            __syncthreads();
+        }
+        for (int c = inner + tid; c < ld_p; c += 128) {
+            p_hi[row + c] = __float2bfloat16_rn(0.f);
+            if (p_lo) p_lo[row + c] = __float2bfloat16_rn(0.f);
+        }
+    }
+    if (failed && tid == 0) {
+        atomicExch(status, 7);
+        mbar_wait(bar, parity ^ 1u, poll_limit);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// fp32 or bf16 rows src[map[r]] -> bf16 planes in row order r (hi, and lo for fp32 input): the feature planes in grid
+// order for the list-free projection, where a neighbor is named by its sorted position.
+template <class FT>
+static __global__ void __launch_bounds__(256)
+permute_features_kernel(int64_t rows, int cin, int ld, const FT* __restrict__ src, const int64_t* __restrict__ map,
+                        __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
+    const int64_t total = rows * (ld / 8);
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t r = i / (ld / 8);
+        const int c = (int)(i - r * (ld / 8)) * 8;
+        const int64_t from = map ? __ldg(map + r) : r;
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = (c + e < cin) ? (float)src[from * cin + c + e] : 0.f;
+        uint32_t hw[4], lw[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+            const __nv_bfloat162 l2 = __floats2bfloat162_rn(v[2 * q] - __low2float(h2), v[2 * q + 1] - __high2float(h2));
+            hw[q] = *reinterpret_cast<const uint32_t*>(&h2);
+            lw[q] = *reinterpret_cast<const uint32_t*>(&l2);
+        }
+        *reinterpret_cast<uint4*>(hi + r * ld + c) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        if (lo) *reinterpret_cast<uint4*>(lo + r * ld + c) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+    }
+}
+
+template <int NB, class BASIS, class ARGS, bool SPLIT_F>
+static int launch_project_tc_grid_nb(int K, const ARGS& args, int num_pts, const float* sorted_pts, const int64_t* sorted_keys,
+                                     const FeaturePlanes& feats, int cin, int num_samples, const float* samples,
+                                     const int64_t* sample_keys, const int32_t* grid_ds, const int32_t* grid_size,
+                                     const float* radii, int m_begin, int m_end, void* p_hi, void* p_lo, int ld_p,
+                                     int* status, cudaStream_t s) {
+    auto kernel = project_tc_grid_kernel<NB, BASIS, ARGS, SPLIT_F>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcForwardSmem<NB>::kGridBytes);
+    });
+    PCCNN_CUDA(attr_err);
+    const int per_sm = (227 * 1024) / (TcForwardSmem<NB>::kGridBytes + 1024);
+    const int64_t cap = (int64_t)sm_count() * (per_sm < 1 ? 1 : per_sm);
+    const int count = m_end - m_begin;
+    const unsigned grid = (unsigned)(count < cap ? count : cap);
+    kernel<<<grid, 128, TcForwardSmem<NB>::kGridBytes, s>>>(args, K, num_pts, sorted_pts, sorted_keys, feats, cin, num_samples, samples,
+                                                        sample_keys, (const int2*)grid_ds, grid_size, radii, m_begin, m_end,
+                                                        (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo, ld_p,
+                                                        tensor_core_poll_limit(), status);
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
+template <class ARGS, template <int, int> class BASIS, bool SPLIT_F>
+static int launch_project_tc_grid(int K, const ARGS& args, int num_pts, const float* sorted_pts, const int64_t* sorted_keys,
+                                  const FeaturePlanes& feats, int cin, int num_samples, const float* samples,
+                                  const int64_t* sample_keys, const int32_t* grid_ds, const int32_t* grid_size,
+                                  const float* radii, int m_begin, int m_end, void* p_hi, void* p_lo, int ld_p, int* status,
+                                  cudaStream_t s) {
+    if (m_end <= m_begin) return PCCNN_OK;
+#define PCCNN_GRID_NB(NBV)                                                                                              \
+    return launch_project_tc_grid_nb<NBV, BASIS<3, NBV>, ARGS, SPLIT_F>(K, args, num_pts, sorted_pts, sorted_keys, feats, cin, \
+                                                                        num_samples, samples, sample_keys, grid_ds, grid_size, \
+                                                                        radii, m_begin, m_end, p_hi, p_lo, ld_p, status, s)
+    if (K <= 16) PCCNN_GRID_NB(16);
+    if (K <= 32) PCCNN_GRID_NB(32);
+    PCCNN_GRID_NB(64);
+#undef PCCNN_GRID_NB
 }
 
 }  // namespace pccnn

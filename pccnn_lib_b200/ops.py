@@ -447,6 +447,41 @@ def kp_conv(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma,
     return out
 
 
+def kp_conv_grid(sorted_pts, sorted_keys, sorted_ids, feats, samples, sample_keys, grid_ds, grid_size, radii, kernel_pts,
+                 sigma, weights):
+    """KPConv forward without a neighbor list -> [M, Cout]: the kernel searches the grid itself (3-D points, radius =
+    cell size).  `sorted_pts` / `sorted_keys` / `sorted_ids` / `grid_ds` / `grid_size` as a Grid holds them, `feats` in
+    the original point order, `samples` with their keys on the same grid.  Same result as find_neighbors + kp_conv;
+    float32 or bfloat16 features (with weights of the same dtype).  No counterpart in the reference, where every
+    convolution reads a materialised list (pccnn_lib/pc/layers/KPConv.py:127-146)."""
+    sorted_pts = _need(sorted_pts, "sorted_pts", torch.float32, 2)
+    sorted_keys = _need(sorted_keys, "sorted_keys", torch.int64, 1)
+    if sorted_ids is not None:
+        sorted_ids = _need(sorted_ids, "sorted_ids", torch.int64, 1)
+    samples = _need(samples, "samples", torch.float32, 2)
+    sample_keys = _need(sample_keys, "sample_keys", torch.int64, 1)
+    grid_ds = _need(grid_ds, "grid_ds", torch.int32)
+    grid_size = _need(grid_size, "grid_size", torch.int32, 1)
+    radii = _need(radii, "radii", torch.float32, 1)
+    kernel_pts = _need(kernel_pts, "kernel_pts", torch.float32, 2)
+    bf16 = isinstance(feats, torch.Tensor) and feats.dtype == torch.bfloat16
+    feats = _need(feats, "features", torch.bfloat16 if bf16 else torch.float32, 2)
+    weights = _need(weights, "weights", torch.bfloat16 if bf16 else torch.float32, 2)
+    if sorted_pts.shape[1] != 3 or samples.shape[1] != 3 or kernel_pts.shape[1] != 3:
+        raise RuntimeError("kp_conv_grid is defined for 3-D points")
+    n, m, cin, k, cout = sorted_pts.shape[0], samples.shape[0], feats.shape[1], kernel_pts.shape[0], weights.shape[1]
+    if feats.shape[0] != n or sorted_keys.shape[0] != n or sample_keys.shape[0] != m or weights.shape[0] != k * cin:
+        raise RuntimeError("kp_conv_grid: sizes of points / keys / features / weights do not match")
+    out = torch.empty((m, cout), dtype=feats.dtype, device=feats.device)
+    with _on(feats.device):
+        ws = _workspace(_lib.pccnn_kp_conv_grid_workspace_bytes(n, m, cin, k, cout), feats.device)
+        _capi.check(_lib.pccnn_kp_conv_grid(n, _p(sorted_pts), _p(sorted_keys), _p(sorted_ids), _p(feats), 1 if bf16 else 0,
+                                            cin, m, _p(samples), _p(sample_keys), _p(grid_ds), _p(grid_size), _p(radii),
+                                            _p(kernel_pts), k, float(sigma), _p(weights), cout, _p(out), ws.data_ptr(),
+                                            ws.numel(), _stream()), "kp_conv_grid")
+    return out
+
+
 def _kp_conv_bf16(pts, feats, samples, neighbors, start_ids, radii, kernel_pts, sigma, weights):
     pts, feats, samples, neighbors, start_ids, radii, d = _conv_common(pts, feats, samples, neighbors, start_ids, radii,
                                                                         torch.bfloat16)

@@ -31,3 +31,24 @@ class Neighborhood(object):
 
     def __repr__(self):
         return "### Neighbors:\n{}\n### Start indices:\n{}".format(self.neighbors_, self.start_ids_)
+
+
+class GridNeighborhood(object):
+    """The neighborhood of every sample in the points of a grid, WITHOUT the list: it holds the grid and the samples'
+    cell keys, and the convolution that receives it searches the grid inside its own kernel (ops.kp_conv_grid).
+    No counterpart in the reference, whose Neighborhood always materialises ``neighbors_`` [T, 2].  Inference only
+    (the gradient operators read a list): KPConv accepts it when no gradient is required; 3-D points, search radius
+    = the grid's cell size."""
+
+    def __init__(self, p_grid, p_samples):
+        self.grid_ = p_grid
+        self.samples_ = p_samples
+        self.neighbors_ = None
+        self.start_ids_ = None
+        with torch.no_grad():
+            grid = self.grid_
+            if grid.grid_ds_ is None:
+                grid.compute_cell_ids()
+                grid.build_ds()
+            self.sample_cell_ids_ = ops.compute_keys(self.samples_.pts_.detach(), self.samples_.batch_ids_,
+                                                     grid.bounding_box_.min_, grid.num_cells_, grid.cell_size_)

@@ -3,6 +3,6 @@ pccnn_lib/pc package (phermosilla/pccnn_lib); they orchestrate the operators of 
 from .Pointcloud import Pointcloud
 from .BoundingBox import BoundingBox
 from .Grid import Grid
-from .Neighborhood import Neighborhood
+from .Neighborhood import GridNeighborhood, Neighborhood
 from .PointPooling import PointPooling
 from .layers import *  # noqa: F401,F403

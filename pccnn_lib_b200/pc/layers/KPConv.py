@@ -3,6 +3,7 @@ import math
 import numpy as np
 import torch
 
+from ... import ops
 from ...op_wrappers import ComputeKPConv, ComputeKPConvWeightVar
 from ...py_utils.pc_utils import rotate_pc_3d
 from .IConvLayer import IConvLayer, IConvLayerFactory
@@ -52,6 +53,15 @@ class KPConv(IConvLayer):
     def __compute_convolution__(self, p_pc_in, p_pc_out, p_in_features, p_radius, p_neighborhood):
         if self.sigma_cpu_ is None:
             self.sigma_cpu_ = self.sigma_.item()
+        if getattr(p_neighborhood, "neighbors_", 0) is None:
+            # a GridNeighborhood: no list exists, the convolution searches the grid in its own kernel (inference only)
+            if torch.is_grad_enabled() and (p_in_features.requires_grad or self.conv_weights_.requires_grad):
+                raise RuntimeError("a GridNeighborhood carries no neighbor list, which the gradient operators need: "
+                                   "use a Neighborhood for training, or run the layer under torch.no_grad()")
+            grid = p_neighborhood.grid_
+            return ops.kp_conv_grid(grid.sorted_pts_, grid.sorted_cell_ids_, grid.sorted_ids_, p_in_features,
+                                    p_pc_out.pts_, p_neighborhood.sample_cell_ids_, grid.grid_ds_, grid.num_cells_,
+                                    grid.cell_size_, self.kernel_pts_, self.sigma_cpu_, self.conv_weights_.to(p_in_features.dtype))
         if self.wamup_state_ and self.use_const_variance_init_:
             self.__warmup_weights__(ComputeKPConvWeightVar.apply(
                 p_pc_in.pts_, p_in_features, p_pc_out.pts_, p_neighborhood.neighbors_, p_neighborhood.start_ids_, p_radius,

@@ -38,7 +38,8 @@ def base_case(clouds, c, normal_feats=False):
         pick = np.sort(rs.permutation(pts.shape[0])[: pts.shape[0] // 3])
         samples, sample_b = pts[pick], batch_ids[pick]
     neigh, start_ids, _ = oracle_neighborhood(pts, batch_ids, c["batch"], c["radius"], 0, samples, sample_b)
-    out = dict(pts=pts, batch_ids=batch_ids, samples=samples, feats=feats, neighbors=neigh, start_ids=start_ids,
+    out = dict(pts=pts, batch_ids=batch_ids, samples=samples, sample_batch_ids=sample_b, feats=feats, neighbors=neigh,
+               start_ids=start_ids,
                radii=np.full((c["dims"],), c["radius"], np.float32), rs=rs)
     return out
 

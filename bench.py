@@ -761,6 +761,7 @@ CONV_WORKLOADS = {
                             layers=[("kp", 128, 128), ("mc", 128, 128)], clouds=1, pts=2000000, gen="scene", radius=0.1,
                             k=16, backward=True, pool=None, bw=0.02, shard="scenes"),
 }
+LIST_FREE_MAX_SAMPLES = 65536  # encoder levels up to this many output points use the list-free convolution
 SECONDARY = ["kpconv_cfg0", "mcconv_cfg2", "kpconv_encoder_cfg3", "scene_pair_cfg4"]
 
 
@@ -1162,7 +1163,7 @@ def encoder_entry(args, R):
     d_pts, d_ids, feats0 = h_pts.to(device), h_ids.to(device), h_feats.to(device)
     stats = {}
 
-    def step(p_d=None, i_d=None, f_d=None, record=False):
+    def step(p_d=None, i_d=None, f_d=None, record=False, list_free=True):
         pc = lib.pc.Pointcloud(d_pts if p_d is None else p_d, d_ids if i_d is None else i_d)
         pc._batch_size_host = clouds
         feats = feats0 if f_d is None else f_d
@@ -1179,13 +1180,21 @@ def encoder_entry(args, R):
             grid = lib.pc.Grid(pc, lib.pc.BoundingBox(pc), radius)
             grid.compute_cell_ids()
             grid.build_ds()
-            nb = lib.pc.Neighborhood(grid, pc_out, 0)
+            # inference needs no neighbor list: at the small levels, where a level costs what its launches and host
+            # round trips cost, the convolution searches the grid in its own kernel instead
+            free = list_free and not record and pc_out.pts_.shape[0] <= LIST_FREE_MAX_SAMPLES
+            nb = lib.pc.GridNeighborhood(grid, pc_out) if free else lib.pc.Neighborhood(grid, pc_out, 0)
             ev[2].record()
             geo.append(ev)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            feats = ops.kp_conv(pc.pts_, feats, pc_out.pts_, nb.neighbors_, nb.start_ids_, radius, kpts, sigma,
-                                weights[level])
+            if nb.neighbors_ is None:
+                feats = ops.kp_conv_grid(grid.sorted_pts_, grid.sorted_cell_ids_, grid.sorted_ids_, feats, pc_out.pts_,
+                                         nb.sample_cell_ids_, grid.grid_ds_, grid.num_cells_, grid.cell_size_, kpts, sigma,
+                                         weights[level])
+            else:
+                feats = ops.kp_conv(pc.pts_, feats, pc_out.pts_, nb.neighbors_, nb.start_ids_, radius, kpts, sigma,
+                                    weights[level])
             e1.record()
             if record:
                 stats.setdefault("levels", []).append(dict(points=int(pc.pts_.shape[0]), samples=int(pc_out.pts_.shape[0]),
@@ -1194,8 +1203,11 @@ def encoder_entry(args, R):
             pc = pc_out
         return feats, (conv_ms, geo)
 
-    out, _ = step(record=True)
+    out_listed, _ = step(record=True)
+    out, _ = step()
+    same = float((out.float() - out_listed.float()).abs().max() / out_listed.float().abs().max())
     steps, warm = max(args.steps, 10), max(args.warmup, 3)
+    listed_ms, _ = device_timed(lambda: step(list_free=False), max(3, steps // 2), 2, R)
     marks = []
 
     def timed_step():
@@ -1229,6 +1241,10 @@ def encoder_entry(args, R):
                    "geometry_ms": ms - conv_total, "pooling_ms_per_level": pooling,
                    "neighborhood_ms_per_level": neighborhoods,
                    "finite_output": bool(torch.isfinite(out.float()).all()),
+                   "route": "levels with at most %d output points run without a neighbor list (the convolution searches the "
+                            "grid in its own kernel, ops.kp_conv_grid); larger levels build the list" % LIST_FREE_MAX_SAMPLES,
+                   "with_neighbor_lists_ms_per_step": listed_ms,
+                   "max_rel_difference_between_the_two_routes": same,
                    "sharding": "clouds split over the ranks (parallel.shard_clouds)"},
         "clocks": clocks,
         "e2e": {"value": total_pts / (e2e_ms * 1e-3), "unit": "points/s", "ms_per_step": e2e_ms,

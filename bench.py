@@ -854,8 +854,8 @@ def conv_entry(name, args, R, steps=None, with_gemm_alone=True):
     if w["shard"] == "none" and R.world > 1:
         return {"workload": name, "skipped": "a single cloud does not shard; measured at 1 GPU"}
     device = R.device
-    steps = steps or max(args.steps, 10)
-    warm = max(args.warmup, 3)
+    steps = steps or (args.steps if args.exact_steps else max(args.steps, 10))
+    warm = args.warmup if args.exact_steps else max(args.warmup, 3)
     rs = np.random.RandomState(77 + R.rank)
     pts, ids, clouds = _conv_host_data(w, R)
     radius = np.full((3,), w["radius"], np.float32)
@@ -1206,7 +1206,7 @@ def encoder_entry(args, R):
     out_listed, _ = step(record=True)
     out, _ = step()
     same = float((out.float() - out_listed.float()).abs().max() / out_listed.float().abs().max())
-    steps, warm = max(args.steps, 10), max(args.warmup, 3)
+    steps, warm = (args.steps, args.warmup) if args.exact_steps else (max(args.steps, 10), max(args.warmup, 3))
     listed_ms, _ = device_timed(lambda: step(list_free=False), max(3, steps // 2), 2, R)
     marks = []
 
@@ -1513,6 +1513,8 @@ def main():
                     help="clouds per GPU (default: the full workload; smaller values are for profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs (profiler captures)")
     ap.add_argument("--no-secondary", action="store_true", help="headline workload only (profiler captures)")
+    ap.add_argument("--exact-steps", action="store_true",
+                    help="convolution workloads: run exactly --steps / --warmup instead of at least 10 / 3 (profiler captures)")
     ap.add_argument("--points", type=int, default=0,
                     help="convolution workloads: points per cloud (default: the workload's own size)")
     ap.add_argument("--presort", action="store_true",

@@ -68,9 +68,9 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // Starts the copies of the feature rows of the staged neighbors (s_n0[0 .. rows), -1 = no neighbor) for the channels
 // [cb, cb + 128) into the F tile: warp w takes rows w, w + 4, ...; with two planes lanes 0-15 copy the 16 chunks of
 // the hi plane and lanes 16-31 those of the lo plane (one warp instruction per row); with one plane the two half
-// warps take two rows.  Chunks past the row's end and rows without a neighbor are zero-filled.  Asynchronous: the
+// warps take two rows (NW = warps of the CTA).  Chunks past the row's end and rows without a neighbor are zero-filled.  Asynchronous: the
 // caller waits (cp_async_wait_all) before the tile is used.
-template <bool SPLIT_F>
+template <bool SPLIT_F, int NW = 4>
 __device__ __forceinline__ void gather_features_async(uint32_t f_hi, uint32_t f_lo, const int* s_n0, int rows,
                                                       const FeaturePlanes& f, int cb) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,13 +80,13 @@ __device__ __forceinline__ void gather_features_async(uint32_t f_hi, uint32_t f_
     if (SPLIT_F) {
         const __nv_bfloat16* plane = (lane < 16) ? f.hi : f.lo;
         const uint32_t tile = (lane < 16) ? f_hi : f_lo;
-        for (int r = warp; r < rows; r += 4) {
+        for (int r = warp; r < rows; r += NW) {
             const int n0 = s_n0[r];
             const bool valid = n0 >= 0 && c < f.ld;
             cp_async_16(tile + in_tile + sw128_offset(r, chunk & 7), plane + (valid ? (int64_t)n0 * f.ld + c : 0), valid);
         }
     } else {
-        for (int r = 2 * warp + (lane >> 4); r < rows; r += 8) {
+        for (int r = 2 * warp + (lane >> 4); r < rows; r += 2 * NW) {
             const int n0 = s_n0[r];
             const bool valid = n0 >= 0 && c < f.ld;
             cp_async_16(f_hi + in_tile + sw128_offset(r, chunk & 7), f.hi + (valid ? (int64_t)n0 * f.ld + c : 0), valid);
@@ -436,10 +436,14 @@ struct TcBackwardSmem {
 //     P^T [channel, k]          = F^T  * BT^T     A = F  MN-major, B = BT K-major      (accumulated over the passes)
 //     db  [neighbor, k]         = F    * GP^T     A = F  K-major,  B = GP K-major      (accumulated over channel blocks)
 //     dF^T[channel, neighbor]   = GP^T * BT       A = GP MN-major, B = BT MN-major     (one 16-deep step per 16 basis functions)
-// Thread r of the CTA owns neighbor r in the "lanes as neighbors" stages and channel cb + r in the "lanes as
-// channels" stages.
+// A pass of this kernel is a chain of dependent phases, and with the few warps that fit an SM beside the tiles its
+// duration is the number of instructions one warp has to run.  So the CTA has two groups of four warps that split
+// every phase: threads 0-127 own one neighbor each (offset, basis, BT column, later the db row with the basis,
+// offset, point and parameter gradients), threads 128-255 one channel each (GP column, most of the dF^T reduction,
+// the P row); all eight warps copy feature rows.  The ids, coordinates and dP entries of the next pass are loaded
+// while the products of this one run.
 template <int NB, class BASIS, class ARGS>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256, 2)
 backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes feats, int cin,
                    const float* __restrict__ samples, const int2* __restrict__ neighbors,
                    const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
@@ -453,14 +457,18 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
     uint8_t* misc = smem + SM::kTiles;
     uint64_t* bar = (uint64_t*)misc;
     uint32_t* tmem_slot = (uint32_t*)(misc + 8);
-    int* s_n0 = (int*)(misc + 64);                     // [128]
-    float* s_params = (float*)(misc + 64 + 512);       // up to 256 floats
-    float* s_grad = (float*)(misc + 64 + 512 + 1024);  // up to 256 floats
+    int* s_n0 = (int*)(misc + 64);                      // [2][128]: the ids of this pass and of the next one
+    float* s_params = (float*)(misc + 64 + 1024);       // up to 256 floats
+    float* s_grad = (float*)(misc + 64 + 1024 + 1024);  // up to 256 floats
     static_assert(BASIS::kParamFloats <= 256 && BASIS::kGradFloats <= 256, "basis parameters do not fit their slots");
+    static_assert(64 + 3 * 1024 <= SM::kMisc, "the small buffers do not fit");
     constexpr uint32_t kTmemCols = 256;  // db in columns [0, NB), P^T in [64, 64 + NB), dF^T in [128, 256)
     constexpr uint32_t kColP = 64, kColF = 128;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int grp = tid >> 7;   // 0: one neighbor per thread, 1: one channel per thread
+    const int r = tid & 127;    // that neighbor / channel; also this thread's tensor-memory lane
+    const int quad = warp & 3;  // the 32 tensor-memory lanes this warp may read
     if (tid == 0) {
         mbar_init(bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -472,11 +480,12 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     BASIS::load_params(s_params, args, K);
-    for (int i = tid; i < BASIS::kGradFloats; i += 128) s_grad[i] = 0.f;
+    for (int i = tid; i < BASIS::kGradFloats; i += 256) s_grad[i] = 0.f;
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_lanes = tmem_base + ((uint32_t)(quad * 32) << 16);
 
     float inv[3];
 #pragma unroll
@@ -492,231 +501,318 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
     constexpr uint32_t idesc_df = kBase | (1u << 15) | (1u << 16) | ((uint32_t)(128 >> 3) << 17);   // both MN-major, N = 128
     uint32_t parity = 0;
     bool failed = false;
-    // Parameter gradients: with a small basis every thread keeps its own partial sums in registers and the block
-    // reduces them once at the end; a chain of warp reductions per pass would dominate a kernel that has only
-    // four warps to hide it.  Larger bases reduce per pass in shared memory.
+    // Parameter gradients: with a small basis every neighbor thread keeps its own partial sums in registers and the
+    // block reduces them once at the end; a chain of warp reductions per pass would dominate a kernel that has
+    // few warps to hide it.  Larger bases reduce per pass in shared memory.
     constexpr bool kLocalGrads = NB <= 16;
     float g_acc[kLocalGrads ? BASIS::kGradFloats : 1];
 #pragma unroll
     for (int i = 0; i < (kLocalGrads ? BASIS::kGradFloats : 1); ++i) g_acc[i] = 0.f;
+    // the dP entries of the next pass travel in registers while a small basis leaves room for them
+    constexpr bool kPrefetchGP = NB <= 32;
 
-    for (int m = m_begin + blockIdx.x; m < m_end && !failed; m += gridDim.x) {
-        const int lo = (m > 0) ? __ldg(start_ids + m - 1) : 0;
-        const int hi = __ldg(start_ids + m);
-        float s[3], ds_acc[3] = {0.f, 0.f, 0.f};
+    struct Sample {
+        int m, lo, hi;
+        float s[3];
+    };
+    auto load_sample = [&](int m) {
+        Sample q;
+        q.m = m;
+        q.lo = q.hi = 0;
+        q.s[0] = q.s[1] = q.s[2] = 0.f;
+        if (m < m_end) {
+            q.lo = (m > 0) ? __ldg(start_ids + m - 1) : 0;
+            q.hi = __ldg(start_ids + m);
 #pragma unroll
-        for (int d = 0; d < 3; ++d) s[d] = BASIS::kUsesOffset ? __ldg(samples + (int64_t)m * 3 + d) : 0.f;
-        const float* grow = d_proj + (size_t)(m - m_begin) * inner;
-        const size_t prow = (size_t)(m - m_begin) * ld_p;
-        bool first = true;
-
-        for (int t0 = lo; t0 < hi && !failed; t0 += kTcRows) {
-            const int cnt = min(kTcRows, hi - t0);
-            const int rows = (cnt + 15) & ~15;
-            // ---- the neighbor of this thread
-            const int t = t0 + tid;
-            const bool active = tid < cnt;
-            const int n0 = active ? __ldg(&neighbors[t]).x : -1;
-            s_n0[tid] = n0;
-            __syncthreads();
-            float d[3] = {0.f, 0.f, 0.f};
-
-            for (int cb = 0; cb < cin; cb += kTcChan) {
-                gather_features_async<true>(f_hi, f_lo, s_n0, rows, feats, cb);
-                if (cb == 0) {
-                    // ---- lanes as neighbors, while the copies are in flight: offset, basis, BT column of this pair
-                    float b[NB];
-                    if (active) {
-#pragma unroll
-                        for (int x = 0; x < 3; ++x)
-                            d[x] = BASIS::kUsesOffset ? (__ldg(pts + (int64_t)n0 * 3 + x) - s[x]) * inv[x] : 0.f;
-                        BASIS::eval(s_params, args, K, d, n0, t, m, b);
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < NB; ++k) b[k] = 0.f;
-                    }
-                    // all 128 columns are written: dF^T is computed for every column of the tile
-                    uint8_t* base_hi = smem + SM::kBTHi + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
-                    uint8_t* base_lo = smem + SM::kBTLo + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
-                    const int chunk = (tid & 63) >> 3;
-#pragma unroll
-                    for (int k = 0; k < NB; ++k) {
-                        const __nv_bfloat16 h = __float2bfloat16_rn(b[k]);
-                        const uint32_t off = sw128_offset(k, chunk);
-                        *reinterpret_cast<__nv_bfloat16*>(base_hi + off) = h;
-                        *reinterpret_cast<__nv_bfloat16*>(base_lo + off) = __float2bfloat16_rn(b[k] - __bfloat162float(h));
-                    }
-                }
-                // ---- lanes as channels: the dP entries of channel cb + tid -> GP column tid
-                {
-                    const int c = cb + tid;
-                    float g[NB];
-                    if (c < cin) {
-                        if (K == NB) {
-#pragma unroll
-                            for (int k = 0; k < NB; k += 4) {
-                                const float4 v = __ldg(reinterpret_cast<const float4*>(grow + (size_t)c * K + k));
-                                g[k] = v.x; g[k + 1] = v.y; g[k + 2] = v.z; g[k + 3] = v.w;
-                            }
-                        } else {
-#pragma unroll
-                            for (int k = 0; k < NB; ++k) g[k] = (k < K) ? __ldg(grow + (size_t)c * K + k) : 0.f;
-                        }
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < NB; ++k) g[k] = 0.f;
-                    }
-                    uint8_t* base_hi = smem + SM::kGPHi + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
-                    uint8_t* base_lo = smem + SM::kGPLo + (tid >> 6) * (NB * 128) + (tid & 7) * 2;
-                    const int chunk = (tid & 63) >> 3;
-#pragma unroll
-                    for (int k = 0; k < NB; ++k) {
-                        const __nv_bfloat16 h = __float2bfloat16_rn(g[k]);
-                        const uint32_t off = sw128_offset(k, chunk);
-                        *reinterpret_cast<__nv_bfloat16*>(base_hi + off) = h;
-                        *reinterpret_cast<__nv_bfloat16*>(base_lo + off) = __float2bfloat16_rn(g[k] - __bfloat162float(h));
-                    }
-                }
-                cp_async_wait_all();
-                fence_smem_to_async_proxy();
-                __syncthreads();
-                if (tid == 0) {
-                    tc_fence_after();
-                    // db[neighbor, k] (+)= F[neighbor, c] * dP[c, k]: 8 steps of 16 channels, accumulated over the blocks
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        const uint64_t a_off = (uint64_t)(ks >> 2) * ((kTcRows * 128) >> 4) + 2ull * (ks & 3);
-                        const uint64_t b_off = (uint64_t)(ks >> 2) * ((NB * 128) >> 4) + 2ull * (ks & 3);
-                        const uint64_t a_hi = umma_desc_k_sw128(f_hi) + a_off, a_lo = umma_desc_k_sw128(f_lo) + a_off;
-                        const uint64_t b_hi = umma_desc_k_sw128(gp_hi) + b_off, b_lo = umma_desc_k_sw128(gp_lo) + b_off;
-                        tc_mma_bf16(tmem_base, a_hi, b_hi, idesc_db, (cb > 0 || ks > 0) ? 1u : 0u);
-                        tc_mma_bf16(tmem_base, a_lo, b_hi, idesc_db, 1u);
-                        tc_mma_bf16(tmem_base, a_hi, b_lo, idesc_db, 1u);
-                    }
-                    // dF^T[c, neighbor] = dP[c, k] * b[neighbor, k]: both operands MN-major (16 basis rows = 2048 bytes
-                    // = +128 per step; 64-channel / 64-neighbor groups are one block of NB rows apart)
-#pragma unroll
-                    for (int ks = 0; ks < NB / 16; ++ks) {
-                        const uint64_t a_hi = umma_desc_mn_sw128(gp_hi, NB * 128) + 128ull * ks;
-                        const uint64_t a_lo = umma_desc_mn_sw128(gp_lo, NB * 128) + 128ull * ks;
-                        const uint64_t b_hi = umma_desc_mn_sw128(bt_hi, NB * 128) + 128ull * ks;
-                        const uint64_t b_lo = umma_desc_mn_sw128(bt_lo, NB * 128) + 128ull * ks;
-                        tc_mma_bf16(tmem_base + kColF, a_hi, b_hi, idesc_df, ks > 0 ? 1u : 0u);
-                        tc_mma_bf16(tmem_base + kColF, a_lo, b_hi, idesc_df, 1u);
-                        tc_mma_bf16(tmem_base + kColF, a_hi, b_lo, idesc_df, 1u);
-                    }
-                    if (with_p) {
-                        // P^T[c, k] (+)= F[neighbor, c] * b[neighbor, k] over the neighbors of this pass
-                        for (int kb = 0; kb < rows / 16; ++kb) {
-                            const uint64_t a_hi = umma_desc_mn_sw128(f_hi, kTcRows * 128) + 128ull * kb;
-                            const uint64_t a_lo = umma_desc_mn_sw128(f_lo, kTcRows * 128) + 128ull * kb;
-                            const uint64_t b_off = (uint64_t)(kb >> 2) * ((NB * 128) >> 4) + 2ull * (kb & 3);
-                            const uint64_t b_hi = umma_desc_k_sw128(bt_hi) + b_off, b_lo = umma_desc_k_sw128(bt_lo) + b_off;
-                            tc_mma_bf16(tmem_base + kColP, a_hi, b_hi, idesc_p, (!first || kb > 0) ? 1u : 0u);
-                            tc_mma_bf16(tmem_base + kColP, a_hi, b_lo, idesc_p, 1u);
-                            tc_mma_bf16(tmem_base + kColP, a_lo, b_hi, idesc_p, 1u);
-                        }
-                    }
-                    tc_commit(bar);
-                }
-                const bool ok = (tid != 0) || mbar_wait(bar, parity, poll_limit);
-                parity ^= 1u;
-                if (__syncthreads_or(ok ? 0 : 1)) {
-                    failed = true;
-                    break;
-                }
-                tc_fence_after();
-                // ---- dF^T row of channel cb + tid: one column per neighbor, 32 at a time; the lanes of a warp hold 32
-                // consecutive channels of the same neighbor row, so every reduction below is one 128-byte line
-                {
-                    const int c = cb + tid;
-#pragma unroll 1
-                    for (int j0 = 0; j0 < cnt; j0 += 32) {
-                        uint32_t r[32];
-                        tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + kColF + (uint32_t)j0, r);
-                        if (c < cin) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                if (j0 + j < cnt) atomicAdd(d_feat + (int64_t)s_n0[j0 + j] * cin + c, __uint_as_float(r[j]));
-                            }
-                        }
-                    }
-                }
-                tc_fence_before();
-                __syncthreads();  // the tiles and the dF^T accumulator are free for the next channel block
-            }
-            if (failed) break;
-            first = false;
-
-            // ---- lanes as neighbors again: db row -> basis gradient, offset gradient, point gradients
-            float db[NB];
-            tc_fence_after();
-#pragma unroll
-            for (int k0 = 0; k0 < NB; k0 += 16) {
-                uint32_t r[16];
-                tc_ld_32x16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)k0, r);
-#pragma unroll
-                for (int k = 0; k < 16; ++k) db[k0 + k] = active ? __uint_as_float(r[k]) : 0.f;
-            }
-            float d_off[3] = {0.f, 0.f, 0.f}, dpdf = 0.f;
-            if constexpr (kLocalGrads)
-                BASIS::grad_local(s_params, args, K, d, max(n0, 0), t, m, active, db, d_off, g_acc, dpdf);
-            else
-                BASIS::grad(s_params, args, K, d, max(n0, 0), t, m, active, db, d_off, s_grad, dpdf);
-            if (active) {
-#pragma unroll
-                for (int x = 0; x < 3; ++x) {
-                    const float gx = d_off[x] * inv[x];
-                    if (d_pts && gx != 0.f) atomicAdd(d_pts + (int64_t)n0 * 3 + x, gx);
-                    ds_acc[x] += gx;
-                }
-                if (d_pdf && dpdf != 0.f) atomicAdd(d_pdf + n0, dpdf);
-            }
-            tc_fence_before();
-            __syncthreads();  // db accumulator, BT tile and neighbor ids are free for the next pass
+            for (int d = 0; d < 3; ++d) q.s[d] = BASIS::kUsesOffset ? __ldg(samples + (int64_t)m * 3 + d) : 0.f;
         }
-        if (failed) break;
-        if (with_p) {
-            // ---- P row of the sample: thread = channel, NB accumulator columns -> K entries (zeros without neighbors)
-            tc_fence_after();
-            float acc[NB];
-            if (first) {
+        return q;
+    };
+    // `cur` becomes the next sample that has neighbors; a sample without any gets its row of zeros in P here
+    Sample cur, ahead;
+    auto open_sample = [&]() {
+        while (cur.m < m_end && cur.hi == cur.lo) {
+            if (with_p && grp == 1) {
+                const size_t prow = (size_t)(cur.m - m_begin) * ld_p;
+                for (int c = r; c < ld_p; c += 128) {
+                    p_hi[prow + c] = __float2bfloat16_rn(0.f);
+                    p_lo[prow + c] = __float2bfloat16_rn(0.f);
+                }
+            }
+            cur = ahead;
+            ahead = load_sample(cur.m + gridDim.x);
+        }
+    };
+    auto load_id = [&](const Sample& q, int t0) { return (q.m < m_end && t0 + r < q.hi) ? __ldg(&neighbors[t0 + r]).x : -1; };
+    auto load_point = [&](int n0, float (&q)[3]) {
 #pragma unroll
-                for (int k = 0; k < NB; ++k) acc[k] = 0.f;
+        for (int x = 0; x < 3; ++x) q[x] = (BASIS::kUsesOffset && n0 >= 0) ? __ldg(pts + (int64_t)n0 * 3 + x) : 0.f;
+    };
+    // dP entries [k] of channel c of a sample
+    auto load_gp = [&](const Sample& q, int c, float (&g)[NB]) {
+        const float* grow = d_proj + (size_t)(q.m - m_begin) * inner;
+        if (q.m < m_end && c < cin) {
+            if (K == NB) {
+#pragma unroll
+                for (int k = 0; k < NB; k += 4) {
+                    const float4 v = __ldg(reinterpret_cast<const float4*>(grow + (size_t)c * K + k));
+                    g[k] = v.x; g[k + 1] = v.y; g[k + 2] = v.z; g[k + 3] = v.w;
+                }
             } else {
 #pragma unroll
-                for (int k0 = 0; k0 < NB; k0 += 16) {
-                    uint32_t r[16];
-                    tc_ld_32x16(tmem_base + ((uint32_t)(warp * 32) << 16) + kColP + (uint32_t)k0, r);
+                for (int k = 0; k < NB; ++k) g[k] = (k < K) ? __ldg(grow + (size_t)c * K + k) : 0.f;
+            }
+        } else {
 #pragma unroll
-                    for (int k = 0; k < 16; ++k) acc[k0 + k] = __uint_as_float(r[k]);
+            for (int k = 0; k < NB; ++k) g[k] = 0.f;
+        }
+    };
+
+    cur = load_sample(m_begin + blockIdx.x);
+    ahead = load_sample(cur.m + gridDim.x);
+    open_sample();
+    int t0 = cur.lo, cb = 0, buf = 0;
+    int n0 = -1;
+    float pt[3] = {0.f, 0.f, 0.f}, d[3] = {0.f, 0.f, 0.f}, ds_acc[3] = {0.f, 0.f, 0.f};
+    float gp[kPrefetchGP ? NB : 1];
+    if (grp == 0) {
+        n0 = load_id(cur, t0);
+        s_n0[r] = n0;
+        load_point(n0, pt);
+    } else if constexpr (kPrefetchGP) {
+        load_gp(cur, r, gp);
+    }
+    __syncthreads();
+
+    while (cur.m < m_end && !failed) {
+        const int cnt = min(kTcRows, cur.hi - t0);
+        const int rows = (cnt + 15) & ~15;
+        const int* ids = s_n0 + buf * kTcRows;
+        const int t = t0 + r;
+        const bool active = grp == 0 && r < cnt;
+        const bool last_cb = cb + kTcChan >= cin;
+        const bool last_pass = last_cb && t0 + kTcRows >= cur.hi;
+
+        // ---- the pass after this one
+        Sample nxt = cur;
+        int nxt_t0 = t0, nxt_cb = cb + kTcChan;
+        if (last_cb) {
+            nxt_cb = 0;
+            nxt_t0 = t0 + kTcRows;
+        }
+        gather_features_async<true, 8>(f_hi, f_lo, ids, rows, feats, cb);
+        if (last_pass) {
+            const Sample done = cur;
+            cur = ahead;
+            ahead = load_sample(cur.m + gridDim.x);
+            open_sample();
+            nxt = cur;
+            nxt_t0 = nxt.lo;
+            cur = done;
+        }
+        int n0_next = n0;
+        if (grp == 0 && last_cb) n0_next = load_id(nxt, nxt_t0);
+
+        if (grp == 0) {
+            if (cb == 0) {
+                // ---- offset, basis, BT column of this thread's pair, while the copies are in flight
+                float b[NB];
+                if (active) {
+#pragma unroll
+                    for (int x = 0; x < 3; ++x) d[x] = BASIS::kUsesOffset ? (pt[x] - cur.s[x]) * inv[x] : 0.f;
+                    BASIS::eval(s_params, args, K, d, n0, t, cur.m, b);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < NB; ++k) b[k] = 0.f;
+                }
+                // all 128 columns are written: dF^T is computed for every column of the tile
+                uint8_t* base_hi = smem + SM::kBTHi + (r >> 6) * (NB * 128) + (r & 7) * 2;
+                uint8_t* base_lo = smem + SM::kBTLo + (r >> 6) * (NB * 128) + (r & 7) * 2;
+                const int chunk = (r & 63) >> 3;
+#pragma unroll
+                for (int k = 0; k < NB; ++k) {
+                    const __nv_bfloat16 h = __float2bfloat16_rn(b[k]);
+                    const uint32_t off = sw128_offset(k, chunk);
+                    *reinterpret_cast<__nv_bfloat16*>(base_hi + off) = h;
+                    *reinterpret_cast<__nv_bfloat16*>(base_lo + off) = __float2bfloat16_rn(b[k] - __bfloat162float(h));
                 }
             }
-            store_p_row<NB>(acc, tid, cin, K, p_hi, p_lo, prow);
-            for (int c = inner + tid; c < ld_p; c += 128) {
-                p_hi[prow + c] = __float2bfloat16_rn(0.f);
-                p_lo[prow + c] = __float2bfloat16_rn(0.f);
-            }
-            tc_fence_before();
-            __syncthreads();
-        }
-        if (d_samples) {
+        } else {
+            // ---- the dP entries of channel cb + r -> GP column r
+            float g[NB];
+            if constexpr (kPrefetchGP) {
 #pragma unroll
-            for (int x = 0; x < 3; ++x) {
-                const float tot = warp_sum(ds_acc[x]);
-                if (lane == 0 && tot != 0.f) atomicAdd(d_samples + (int64_t)m * 3 + x, -tot);
+                for (int k = 0; k < NB; ++k) g[k] = gp[k];
+            } else {
+                load_gp(cur, cb + r, g);
+            }
+            uint8_t* base_hi = smem + SM::kGPHi + (r >> 6) * (NB * 128) + (r & 7) * 2;
+            uint8_t* base_lo = smem + SM::kGPLo + (r >> 6) * (NB * 128) + (r & 7) * 2;
+            const int chunk = (r & 63) >> 3;
+#pragma unroll
+            for (int k = 0; k < NB; ++k) {
+                const __nv_bfloat16 h = __float2bfloat16_rn(g[k]);
+                const uint32_t off = sw128_offset(k, chunk);
+                *reinterpret_cast<__nv_bfloat16*>(base_hi + off) = h;
+                *reinterpret_cast<__nv_bfloat16*>(base_lo + off) = __float2bfloat16_rn(g[k] - __bfloat162float(h));
             }
         }
+        cp_async_wait_all();
+        fence_smem_to_async_proxy();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            // db[neighbor, k] (+)= F[neighbor, c] * dP[c, k]: 8 steps of 16 channels, accumulated over the blocks
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint64_t a_off = (uint64_t)(ks >> 2) * ((kTcRows * 128) >> 4) + 2ull * (ks & 3);
+                const uint64_t b_off = (uint64_t)(ks >> 2) * ((NB * 128) >> 4) + 2ull * (ks & 3);
+                const uint64_t a_hi = umma_desc_k_sw128(f_hi) + a_off, a_lo = umma_desc_k_sw128(f_lo) + a_off;
+                const uint64_t b_hi = umma_desc_k_sw128(gp_hi) + b_off, b_lo = umma_desc_k_sw128(gp_lo) + b_off;
+                tc_mma_bf16(tmem_base, a_hi, b_hi, idesc_db, (cb > 0 || ks > 0) ? 1u : 0u);
+                tc_mma_bf16(tmem_base, a_lo, b_hi, idesc_db, 1u);
+                tc_mma_bf16(tmem_base, a_hi, b_lo, idesc_db, 1u);
+            }
+            // dF^T[c, neighbor] = dP[c, k] * b[neighbor, k]: both operands MN-major (16 basis rows = 2048 bytes
+            // = +128 per step; 64-channel / 64-neighbor groups are one block of NB rows apart)
+#pragma unroll
+            for (int ks = 0; ks < NB / 16; ++ks) {
+                const uint64_t a_hi = umma_desc_mn_sw128(gp_hi, NB * 128) + 128ull * ks;
+                const uint64_t a_lo = umma_desc_mn_sw128(gp_lo, NB * 128) + 128ull * ks;
+                const uint64_t b_hi = umma_desc_mn_sw128(bt_hi, NB * 128) + 128ull * ks;
+                const uint64_t b_lo = umma_desc_mn_sw128(bt_lo, NB * 128) + 128ull * ks;
+                tc_mma_bf16(tmem_base + kColF, a_hi, b_hi, idesc_df, ks > 0 ? 1u : 0u);
+                tc_mma_bf16(tmem_base + kColF, a_lo, b_hi, idesc_df, 1u);
+                tc_mma_bf16(tmem_base + kColF, a_hi, b_lo, idesc_df, 1u);
+            }
+            if (with_p) {
+                // P^T[c, k] (+)= F[neighbor, c] * b[neighbor, k] over the neighbors of this pass
+                const bool first = t0 == cur.lo;
+                // not unrolled: with this kernel's register budget the compiler's four-fold unrolled body issued
+                // products with wrong operands (caught by the parity tests on samples of 49 - 64 neighbors)
+#pragma unroll 1
+                for (int kb = 0; kb < rows / 16; ++kb) {
+                    const uint64_t a_hi = umma_desc_mn_sw128(f_hi, kTcRows * 128) + 128ull * kb;
+                    const uint64_t a_lo = umma_desc_mn_sw128(f_lo, kTcRows * 128) + 128ull * kb;
+                    const uint64_t b_off = (uint64_t)(kb >> 2) * ((NB * 128) >> 4) + 2ull * (kb & 3);
+                    const uint64_t b_hi = umma_desc_k_sw128(bt_hi) + b_off, b_lo = umma_desc_k_sw128(bt_lo) + b_off;
+                    tc_mma_bf16(tmem_base + kColP, a_hi, b_hi, idesc_p, (!first || kb > 0) ? 1u : 0u);
+                    tc_mma_bf16(tmem_base + kColP, a_hi, b_lo, idesc_p, 1u);
+                    tc_mma_bf16(tmem_base + kColP, a_lo, b_hi, idesc_p, 1u);
+                }
+            }
+            tc_commit(bar);
+        }
+        // ---- loads of the next pass travel while the products run
+        float pt_next[3] = {pt[0], pt[1], pt[2]};
+        if (grp == 0) {
+            if (last_cb) load_point(n0_next, pt_next);
+        } else if constexpr (kPrefetchGP) {
+            load_gp(nxt, nxt_cb + r, gp);
+        }
+        const bool ok = (tid != 0) || mbar_wait(bar, parity, poll_limit);
+        parity ^= 1u;
+        if (__syncthreads_or(ok ? 0 : 1)) {
+            failed = true;
+            break;
+        }
+        tc_fence_after();
+
+        // ---- dF^T rows: a warp holds 32 consecutive channels as lanes, one column per neighbor, 32 columns at a
+        // time; every reduction below is one 128-byte line of a neighbor's feature-gradient row
+        auto reduce_df = [&](int j0) {
+            if (j0 >= cnt) return;
+            uint32_t v[32];
+            tc_ld_32x32(tmem_lanes + kColF + (uint32_t)j0, v);
+            const int c = cb + r;
+            if (c < cin) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (j0 + j < cnt) atomicAdd(d_feat + (int64_t)ids[j0 + j] * cin + c, __uint_as_float(v[j]));
+                }
+            }
+        };
+        if (grp == 1) {
+            reduce_df(0);
+            reduce_df(32);
+            reduce_df(64);
+            if (last_pass && with_p) {
+                // ---- P row of the sample: thread = channel, NB accumulator columns -> K entries
+                float acc[NB];
+#pragma unroll
+                for (int k0 = 0; k0 < NB; k0 += 16) {
+                    uint32_t v[16];
+                    tc_ld_32x16(tmem_lanes + kColP + (uint32_t)k0, v);
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) acc[k0 + k] = __uint_as_float(v[k]);
+                }
+                const size_t prow = (size_t)(cur.m - m_begin) * ld_p;
+                store_p_row<NB>(acc, r, cin, K, p_hi, p_lo, prow);
+                for (int c = inner + r; c < ld_p; c += 128) {
+                    p_hi[prow + c] = __float2bfloat16_rn(0.f);
+                    p_lo[prow + c] = __float2bfloat16_rn(0.f);
+                }
+            }
+        } else {
+            if (last_cb) {
+                // ---- db row of this thread's pair -> basis gradient, offset gradient, point gradients
+                float db[NB];
+#pragma unroll
+                for (int k0 = 0; k0 < NB; k0 += 16) {
+                    uint32_t v[16];
+                    tc_ld_32x16(tmem_lanes + (uint32_t)k0, v);
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) db[k0 + k] = active ? __uint_as_float(v[k]) : 0.f;
+                }
+                float d_off[3] = {0.f, 0.f, 0.f}, dpdf = 0.f;
+                if constexpr (kLocalGrads)
+                    BASIS::grad_local(s_params, args, K, d, max(n0, 0), t, cur.m, active, db, d_off, g_acc, dpdf);
+                else
+                    BASIS::grad(s_params, args, K, d, max(n0, 0), t, cur.m, active, db, d_off, s_grad, dpdf);
+                if (active) {
+#pragma unroll
+                    for (int x = 0; x < 3; ++x) {
+                        const float gx = d_off[x] * inv[x];
+                        if (d_pts && gx != 0.f) atomicAdd(d_pts + (int64_t)n0 * 3 + x, gx);
+                        ds_acc[x] += gx;
+                    }
+                    if (d_pdf && dpdf != 0.f) atomicAdd(d_pdf + n0, dpdf);
+                }
+            }
+            reduce_df(96);
+            if (last_pass) {
+                if (d_samples) {
+#pragma unroll
+                    for (int x = 0; x < 3; ++x) {
+                        const float tot = warp_sum(ds_acc[x]);
+                        if (lane == 0 && tot != 0.f) atomicAdd(d_samples + (int64_t)cur.m * 3 + x, -tot);
+                    }
+                }
+                ds_acc[0] = ds_acc[1] = ds_acc[2] = 0.f;
+            }
+            s_n0[(buf ^ 1) * kTcRows + r] = n0_next;
+        }
+        tc_fence_before();
+        __syncthreads();  // tiles, accumulators and the other id buffer are free; the next ids are staged
+        if (last_cb) buf ^= 1;
+        cur = nxt;
+        t0 = nxt_t0;
+        cb = nxt_cb;
+        n0 = n0_next;
+#pragma unroll
+        for (int x = 0; x < 3; ++x) pt[x] = pt_next[x];
     }
     if (failed && tid == 0) {
         atomicExch(status, 6);
         mbar_wait(bar, parity ^ 1u, poll_limit);
     }
     if constexpr (kLocalGrads) {
+        if (grp == 0) {
 #pragma unroll
-        for (int i = 0; i < BASIS::kGradFloats; ++i) {
-            const float tot = warp_sum(g_acc[i]);
-            if (lane == 0 && tot != 0.f) atomicAdd(s_grad + i, tot);
+            for (int i = 0; i < BASIS::kGradFloats; ++i) {
+                const float tot = warp_sum(g_acc[i]);
+                if (lane == 0 && tot != 0.f) atomicAdd(s_grad + i, tot);
+            }
         }
     }
     __syncthreads();
@@ -788,7 +884,7 @@ static int launch_backward_tc_nb(int K, const ARGS& args, const float* pts, cons
     const int per_sm = (227 * 1024) / (TcBackwardSmem<NB>::kBytes + 1024) >= 2 ? 2 : 1;
     const int64_t cap = (int64_t)sm_count() * per_sm;
     const unsigned grid = (unsigned)(count < cap ? count : cap);
-    kernel<<<grid, 128, TcBackwardSmem<NB>::kBytes, s>>>(args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids,
+    kernel<<<grid, 256, TcBackwardSmem<NB>::kBytes, s>>>(args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids,
                                                          radii, m_begin, m_end, d_proj, d_feat, d_pts, d_samples, d_param0,
                                                          d_param1, d_pdf, (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo, ld_p,
                                                          tensor_core_poll_limit(), status);

@@ -529,7 +529,8 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
         return q;
     };
     // `cur` becomes the next sample that has neighbors; a sample without any gets its row of zeros in P here
-    Sample cur, ahead;
+    Sample cur = load_sample(m_begin + blockIdx.x);
+    Sample ahead = load_sample(cur.m + gridDim.x);
     auto open_sample = [&]() {
         while (cur.m < m_end && cur.hi == cur.lo) {
             if (with_p && grp == 1) {
@@ -568,8 +569,6 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
         }
     };
 
-    cur = load_sample(m_begin + blockIdx.x);
-    ahead = load_sample(cur.m + gridDim.x);
     open_sample();
     int t0 = cur.lo, cb = 0, buf = 0;
     int n0 = -1;

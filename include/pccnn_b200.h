@@ -205,6 +205,17 @@ int pccnn_compute_pdf_grads(int D, int manifold_dims, const float* bandwidth, in
                             const int32_t* neighbors, const int32_t* start_ids, const float* in_grads,
                             float* out_pt_grads, void* stream);
 
+/* The same gradient for a list that is the FULL self-neighborhood of the points: samples = points, no cap on the
+ * neighbor count, so that every pair (i, j) sits in the row of i and in the row of j (what pccnn_lib/pc/Pointcloud.py:88-97
+ * builds when its cap of 300 does not bite).  One pass over the row of each point, no reductions into other rows:
+ *     grad_i = scale * sum_{j in row(i)} (in_grads[i] + in_grads[j]) * w_ij * (p_j - p_i) / bw^2.
+ * The caller vouches for the symmetry; on any other list the result is wrong, not undefined.  No counterpart in the
+ * reference, whose one operator serves both cases.  out_pt_grads: [n, D], written, not accumulated.  The workspace is
+ * optional as for pccnn_compute_pdf (same size). */
+int pccnn_compute_pdf_grads_symmetric(int D, int manifold_dims, const float* bandwidth, int64_t n, const float* pts,
+                                      const int32_t* neighbors, const int32_t* start_ids, const float* in_grads,
+                                      float* out_pt_grads, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------- */
 /* Poisson-disk sampling                                                      */
 /* ------------------------------------------------------------------------- */

@@ -40,6 +40,8 @@ SIGNATURES = {
     "pccnn_compute_pdf_workspace_bytes": (_size, [_c_int, _c_i64]),
     "pccnn_compute_pdf": (_c_int, [_c_int, _c_int, _ptr, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _size, _ptr]),
     "pccnn_compute_pdf_grads": (_c_int, [_c_int, _c_int, _ptr, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),
+    "pccnn_compute_pdf_grads_symmetric": (_c_int, [_c_int, _c_int, _ptr, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _size,
+                                                    _ptr]),
     "pccnn_poisson_disk_sampling_workspace_bytes": (_size, [_c_i64]),
     "pccnn_poisson_disk_sampling": (_c_int, [_c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr,
                                              ctypes.POINTER(_c_i64), _ptr, _size, _ptr]),

@@ -165,6 +165,108 @@ pdf_grads_kernel(int manifold_dims, const float* __restrict__ bandwidth, int n, 
     }
 }
 
+// Gradient of the density for a list that is the FULL self-neighborhood of the points (every pair (i, j) sits in the
+// row of i and in the row of j, which is what the search returns for samples = points with no cap on the count).
+// Then the term that sample m's density contributes to point i is the mirror image of a pair in i's own row, and
+//     grad_i = scale * sum_{j in N(i)} (g_i + g_j) w_ij (x_j - x_i) / bw^2 ,
+// one pass over the row of i with one more gathered value per pair (g_j) and no reduction into other rows at all
+// (the general kernel above makes three float reductions per pair into random rows).  The 3-D form gathers
+// (x, y, z, g) as one 128-bit load from a padded copy.
+template <int D>
+__global__ void __launch_bounds__(kPdfWarps * 32)
+pdf_grads_symmetric_kernel(int manifold_dims, const float* __restrict__ bandwidth, int n, const float* __restrict__ pts,
+                           const int2* __restrict__ neighbors, const int32_t* __restrict__ start_ids,
+                           const float* __restrict__ in_grads, float* __restrict__ out_grads) {
+    float ibw[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) ibw[d] = __frcp_rn(__ldg(bandwidth + d));
+    const float scale = pdf_scale<D>(ibw, manifold_dims);
+    const int lane = lane_id();
+    const int warps_total = gridDim.x * kPdfWarps;
+    for (int i = blockIdx.x * kPdfWarps + (threadIdx.x >> 5); i < n; i += warps_total) {
+        float p[D], acc[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            p[d] = __ldg(pts + (int64_t)i * D + d);
+            acc[d] = 0.f;
+        }
+        const int lo = (i > 0) ? __ldg(start_ids + i - 1) : 0;
+        const int hi = __ldg(start_ids + i);
+        const float gi = __ldg(in_grads + i);
+        for (int t = lo + lane; t < hi; t += 32) {
+            const int j = __ldcs(&neighbors[t]).x;
+            float v[D], dot = 0.f;
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                v[d] = (__ldg(pts + (int64_t)j * D + d) - p[d]) * ibw[d];
+                dot = fmaf(v[d], v[d], dot);
+            }
+            const float w = expf(dot * -0.5f) * (gi + __ldg(in_grads + j));  // j == i: v is zero
+#pragma unroll
+            for (int d = 0; d < D; ++d) acc[d] = fmaf(v[d] * ibw[d], w, acc[d]);
+        }
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            const float total = warp_sum(acc[d]);
+            if (lane == 0) out_grads[(int64_t)i * D + d] = total * scale;
+        }
+    }
+}
+
+__global__ void pad_points_grads_kernel(int n, const float* __restrict__ pts, const float* __restrict__ in_grads,
+                                        float4* __restrict__ out) {
+    const int stride = gridDim.x * blockDim.x;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = make_float4(pts[3 * (int64_t)i], pts[3 * (int64_t)i + 1], pts[3 * (int64_t)i + 2], in_grads[i]);
+}
+
+__global__ void __launch_bounds__(kPdfWarps * 32)
+pdf_grads_symmetric_padded(int manifold_dims, const float* __restrict__ bandwidth, int n, const float4* __restrict__ pg,
+                           const int2* __restrict__ neighbors, const int32_t* __restrict__ start_ids,
+                           float* __restrict__ out_grads) {
+    float ibw[3];
+#pragma unroll
+    for (int d = 0; d < 3; ++d) ibw[d] = __frcp_rn(__ldg(bandwidth + d));
+    const float scale = pdf_scale<3>(ibw, manifold_dims);
+    const int lane = lane_id();
+    const int warps_total = gridDim.x * kPdfWarps;
+    for (int i = blockIdx.x * kPdfWarps + (threadIdx.x >> 5); i < n; i += warps_total) {
+        const float4 p = __ldg(pg + i);
+        const int lo = (i > 0) ? __ldg(start_ids + i - 1) : 0;
+        const int hi = __ldg(start_ids + i);
+        float ax = 0.f, ay = 0.f, az = 0.f;
+        auto term = [&](int j) {
+            const float4 q = __ldg(pg + j);
+            const float vx = (q.x - p.x) * ibw[0], vy = (q.y - p.y) * ibw[1], vz = (q.z - p.z) * ibw[2];
+            const float w = expf(fmaf(vz, vz, fmaf(vy, vy, fmaf(vx, vx, 0.f))) * -0.5f) * (p.w + q.w);
+            ax = fmaf(vx * ibw[0], w, ax);
+            ay = fmaf(vy * ibw[1], w, ay);
+            az = fmaf(vz * ibw[2], w, az);
+        };
+        // as in the density kernel: four row loads per lane in flight before their gathers
+        int t = lo + lane;
+        for (; t + 96 < hi; t += 128) {
+            const int j0 = __ldcs(&neighbors[t]).x;
+            const int j1 = __ldcs(&neighbors[t + 32]).x;
+            const int j2 = __ldcs(&neighbors[t + 64]).x;
+            const int j3 = __ldcs(&neighbors[t + 96]).x;
+            term(j0);
+            term(j1);
+            term(j2);
+            term(j3);
+        }
+        for (; t < hi; t += 32) term(__ldcs(&neighbors[t]).x);
+        ax = warp_sum(ax);
+        ay = warp_sum(ay);
+        az = warp_sum(az);
+        if (lane == 0) {
+            out_grads[3 * (int64_t)i] = ax * scale;
+            out_grads[3 * (int64_t)i + 1] = ay * scale;
+            out_grads[3 * (int64_t)i + 2] = az * scale;
+        }
+    }
+}
+
 }  // namespace pccnn
 
 using namespace pccnn;
@@ -208,6 +310,30 @@ int pccnn_compute_pdf_grads(int D, int manifold_dims, const float* bandwidth, in
     PCCNN_CUDA(cudaMemsetAsync(out_pt_grads, 0, (size_t)n * D * sizeof(float), s));
     const unsigned grid = grid_for(n * 32, kPdfWarps * 32, 8);
     PCCNN_DISPATCH_DIM(D, (pdf_grads_kernel<DIM><<<grid, kPdfWarps * 32, 0, s>>>(
+                              manifold_dims, bandwidth, (int)n, pts, (const int2*)neighbors, start_ids, in_grads,
+                              out_pt_grads)));
+    PCCNN_LAUNCH_CHECK();
+    return PCCNN_OK;
+}
+
+int pccnn_compute_pdf_grads_symmetric(int D, int manifold_dims, const float* bandwidth, int64_t n, const float* pts,
+                                      const int32_t* neighbors, const int32_t* start_ids, const float* in_grads,
+                                      float* out_pt_grads, void* workspace, size_t workspace_bytes, void* stream) {
+    PCCNN_CHECK_ARG(n >= 0 && n < 0x7fffffffLL, "compute_pdf_grads_symmetric: %lld points outside [0, 2^31)", (long long)n);
+    if (n == 0) return PCCNN_OK;
+    PCCNN_CHECK_ARG(bandwidth && pts && start_ids && in_grads && out_pt_grads, "compute_pdf_grads_symmetric: null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    const unsigned grid = grid_for(n * 32, kPdfWarps * 32, 8);
+    if (D == 3 && workspace && workspace_bytes >= (size_t)n * 16 && reinterpret_cast<uintptr_t>(workspace) % 16 == 0) {
+        float4* padded = (float4*)workspace;
+        pad_points_grads_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>((int)n, pts, in_grads, padded);
+        PCCNN_LAUNCH_CHECK();
+        pdf_grads_symmetric_padded<<<grid, kPdfWarps * 32, 0, s>>>(manifold_dims, bandwidth, (int)n, padded,
+                                                                  (const int2*)neighbors, start_ids, out_pt_grads);
+        PCCNN_LAUNCH_CHECK();
+        return PCCNN_OK;
+    }
+    PCCNN_DISPATCH_DIM(D, (pdf_grads_symmetric_kernel<DIM><<<grid, kPdfWarps * 32, 0, s>>>(
                               manifold_dims, bandwidth, (int)n, pts, (const int2*)neighbors, start_ids, in_grads,
                               out_pt_grads)));
     PCCNN_LAUNCH_CHECK();

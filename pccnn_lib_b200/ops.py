@@ -325,15 +325,28 @@ def compute_pdf(manifold_dims, bandwidth, pts, neighbors, start_ids):
     return out
 
 
-def compute_pdf_grads(manifold_dims, bandwidth, pts, neighbors, start_ids, in_grads):
-    """Point gradients of the KDE; compute_pdf_grads() of compute_pdf/compute_pdf.cu:206-257."""
+def compute_pdf_grads(manifold_dims, bandwidth, pts, neighbors, start_ids, in_grads, full_self_neighborhood=False):
+    """Point gradients of the KDE; compute_pdf_grads() of compute_pdf/compute_pdf.cu:206-257.
+
+    `full_self_neighborhood` (an extension): the caller vouches that the list is the uncapped neighborhood of the
+    points in themselves, so that every pair appears in both rows; the gradient is then one pass over each point's
+    own row without reductions into other rows."""
     bandwidth, pts, neighbors, start_ids, d = _pdf_args(bandwidth, pts, neighbors, start_ids)
     in_grads = _need(in_grads, "in_grads", torch.float32, 1)
+    if in_grads.shape[0] != pts.shape[0]:
+        raise RuntimeError("in_grads must have one entry per point")
     out = torch.empty_like(pts)
     with _on(pts.device):
-        _capi.check(_lib.pccnn_compute_pdf_grads(d, int(manifold_dims), _p(bandwidth), pts.shape[0], _p(pts),
-                                                 _p(neighbors), _p(start_ids), _p(in_grads), _p(out), _stream()),
-                    "compute_pdf_grads")
+        if full_self_neighborhood:
+            ws = _workspace(_lib.pccnn_compute_pdf_workspace_bytes(d, pts.shape[0]), pts.device)
+            _capi.check(_lib.pccnn_compute_pdf_grads_symmetric(d, int(manifold_dims), _p(bandwidth), pts.shape[0],
+                                                               _p(pts), _p(neighbors), _p(start_ids), _p(in_grads),
+                                                               _p(out), ws.data_ptr(), ws.numel(), _stream()),
+                        "compute_pdf_grads (full self-neighborhood)")
+        else:
+            _capi.check(_lib.pccnn_compute_pdf_grads(d, int(manifold_dims), _p(bandwidth), pts.shape[0], _p(pts),
+                                                     _p(neighbors), _p(start_ids), _p(in_grads), _p(out), _stream()),
+                        "compute_pdf_grads")
     return out
 
 

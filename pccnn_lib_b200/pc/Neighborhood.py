@@ -28,6 +28,10 @@ class Neighborhood(object):
                 grid.sorted_pts_, grid.sorted_cell_ids_, self.samples_.pts_.detach(), sample_cell_ids,
                 grid.grid_ds_, grid.num_cells_, grid.cell_size_, p_max_neighbors, pt_index_map=grid.sorted_ids_,
                 key_bits=grid.key_bits())
+            # The uncapped neighborhood of a point cloud in itself holds every pair in both rows; operators that can use
+            # that (the gradient of the density) read the mark from the list.
+            self.full_self_ = self.samples_ is grid.pointcloud_ and not p_max_neighbors
+            self.neighbors_._pccnn_full_self = self.full_self_
 
     def __repr__(self):
         return "### Neighbors:\n{}\n### Start indices:\n{}".format(self.neighbors_, self.start_ids_)

@@ -141,6 +141,28 @@ def test_pdf_and_grads_match_oracle(ref_clouds, batch_size, num_pts, num_dims, b
     assert np.abs(gg - eg).max() <= 2e-5 * scale  # float atomics vs a double-precision sum
 
 
+@pytest.mark.parametrize("batch_size,num_pts,num_dims,bandwidth", PDF_CASES)
+def test_pdf_grads_on_the_full_self_neighborhood(ref_clouds, batch_size, num_pts, num_dims, bandwidth):
+    # The uncapped neighborhood of the points in themselves holds every pair in both rows; the one-pass gradient
+    # for such lists against the oracle's general double-precision sum and against the general kernel.
+    from pccnn_lib_b200 import ops
+    pts, batch_ids = ref_case(ref_clouds, batch_size, num_pts, num_dims)
+    radius = float(np.float32(bandwidth) * np.float32(4.0))
+    _, _, _, _, _, o = both_neighborhoods(pts, batch_ids, batch_size, radius, 0)
+    spts = o["sorted_pts"]
+    gn, gs, on, os_, _, _ = both_neighborhoods(spts, batch_ids[o["sorted_ids"]], batch_size, radius, 0)
+    rows = gn.cpu().numpy()
+    assert {(int(a), int(b)) for a, b in rows} == {(int(b), int(a)) for a, b in rows}  # the premise
+    bw = np.full((num_dims,), bandwidth, np.float32)
+    w = np.random.RandomState(6).randn(spts.shape[0]).astype(np.float32)
+    one_pass = ops.compute_pdf_grads(num_dims, dev(bw), dev(spts), gn, gs, dev(w), full_self_neighborhood=True).cpu().numpy()
+    general = ops.compute_pdf_grads(num_dims, dev(bw), dev(spts), gn, gs, dev(w)).cpu().numpy()
+    expect = oracle.compute_pdf_grads(num_dims, bw, spts, on, os_, w)
+    scale = np.abs(expect).max() + 1e-30
+    assert np.abs(one_pass - expect).max() <= 2e-5 * scale
+    assert np.abs(one_pass - general).max() <= 2e-5 * scale
+
+
 PDS_CASES = [(4, 1000, 2, 0.1), (4, 1000, 3, 0.1), (4, 1000, 6, 0.1), (32, 100, 2, 3.0), (32, 100, 3, 3.0),
              (21, 100, 6, 3.0), (16, 1000, 3, 0.03), (8, 1000, 3, 0.3),
              # crowded cells (block per cell), cells beyond the block kernel's 512 points, thinned (one-sided) lists

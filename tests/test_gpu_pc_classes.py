@@ -65,6 +65,33 @@ def test_pointcloud_pdf_matches_oracle_and_backpropagates(ref_clouds, batch_size
     assert tuple(pc.global_pooling(pc.pts_.detach(), "max").shape) == (batch_size, num_dims)
 
 
+def test_density_gradient_through_the_classes_uses_the_full_self_neighborhood(ref_clouds):
+    # Neighborhood marks the uncapped neighborhood of a cloud in itself; ComputePDF hands the mark to the gradient
+    # operator.  Same gradient as with the mark removed (general kernel).
+    import pccnn_lib_b200 as lib
+    from pccnn_lib_b200.op_wrappers import ComputePDF
+    pts, batch_ids = ref_case(ref_clouds, 4, 800, 3)
+    bw = torch.full((3,), 0.03, dtype=torch.float32, device="cuda:0")
+    grads = []
+    for keep_mark in (True, False):
+        pc = lib.pc.Pointcloud(torch.as_tensor(pts, device="cuda:0").requires_grad_(True),
+                               torch.as_tensor(batch_ids, device="cuda:0"))
+        grid = lib.pc.Grid(pc, lib.pc.BoundingBox(pc), bw * 4.0)
+        grid.compute_cell_ids()
+        grid.build_ds()
+        nb = lib.pc.Neighborhood(grid, pc, 0)
+        assert nb.full_self_ and nb.neighbors_._pccnn_full_self
+        capped = lib.pc.Neighborhood(grid, pc, 300)
+        assert not capped.full_self_
+        if not keep_mark:
+            nb.neighbors_._pccnn_full_self = False
+        pdf = ComputePDF.apply(pc.pts_, nb.neighbors_, nb.start_ids_, bw, 3)
+        (pdf * torch.linspace(0.5, 1.5, pdf.shape[0], device="cuda:0")).sum().backward()
+        grads.append(pc.pts_.grad.detach().cpu().numpy())
+    assert np.abs(grads[0]).max() > 0
+    assert np.abs(grads[0] - grads[1]).max() <= 2e-5 * np.abs(grads[1]).max()
+
+
 def test_reference_module_names_resolve_to_this_package():
     import sys
     import pccnn_lib_b200

@@ -436,33 +436,18 @@ project_narrow_kernel(ARGS args, int K, const float* __restrict__ pts, const FT*
         float acc[64];
 #pragma unroll
         for (int e = 0; e < 64; ++e) acc[e] = 0.f;
-        // The loop waits on the gathers (ids -> coordinates and features), not on arithmetic: the loads of two pairs
-        // per lane are issued before the first basis is evaluated.
-        auto fetch = [&](int t, int& n0, float (&d)[D], float (&f)[CS]) {
-            const bool live = t < hi;
-            n0 = live ? __ldg(&neighbors[t]).x : -1;
+        for (int t = lo + lane; t < hi; t += 32) {
+            const int n0 = __ldg(&neighbors[t]).x;
+            float d[D], b[KP], f[CS];
 #pragma unroll
-            for (int c = 0; c < CS; ++c) f[c] = (live && c < cin) ? load_feat(feats + (int64_t)n0 * cin + c) : 0.f;
+            for (int c = 0; c < CS; ++c) f[c] = (c < cin) ? load_feat(feats + (int64_t)n0 * cin + c) : 0.f;
 #pragma unroll
-            for (int x = 0; x < D; ++x)
-                d[x] = (live && BASIS::kUsesOffset) ? (__ldg(pts + (int64_t)n0 * D + x) - s[x]) * inv[x] : 0.f;
-        };
-        auto add = [&](int t, int n0, const float (&d)[D], const float (&f)[CS]) {
-            if (t >= hi) return;
-            float b[KP];
+            for (int x = 0; x < D; ++x) d[x] = BASIS::kUsesOffset ? (__ldg(pts + (int64_t)n0 * D + x) - s[x]) * inv[x] : 0.f;
             BASIS::eval(s_params, args, K, d, n0, t, m, b);
 #pragma unroll
             for (int c = 0; c < CS; ++c)
 #pragma unroll
                 for (int k = 0; k < KP; ++k) acc[c * KP + k] = fmaf(f[c], b[k], acc[c * KP + k]);
-        };
-        for (int t = lo + lane; t < hi; t += 64) {
-            int n0a, n0b;
-            float da[D], db[D], fa[CS], fb[CS];
-            fetch(t, n0a, da, fa);
-            fetch(t + 32, n0b, db, fb);
-            add(t, n0a, da, fa);
-            add(t + 32, n0b, db, fb);
         }
         int e0, n;
         warp_reduce_scatter<64>(acc, lane, e0, n);  // n == 2: this lane owns entries e0 and e0 + 1 (c = e / KP, k = e % KP)

@@ -235,6 +235,9 @@ class Ranks(object):
         self.numa_cpus = bind_to_gpu_numa_node(self.local_rank) if self.world > 1 else None
         if self.world > 1:
             import torch.distributed as dist
+            # whatever NCCL logs (its version line where NCCL_DEBUG asks for one) goes to stderr: stdout carries
+            # the one JSON line and nothing else
+            os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
             dist.init_process_group("nccl", device_id=self.device)
 
     def barrier(self):

@@ -721,13 +721,21 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
         // time; every reduction below is one 128-byte line of a neighbor's feature-gradient row
         auto reduce_df = [&](int j0) {
             if (j0 >= cnt) return;
+            // the ids first: a reduction orders memory operations, so a shared-memory read per column inside the loop
+            // below could not be moved ahead of the previous column's reduction
+            int idr[32];
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const int4 q = *reinterpret_cast<const int4*>(ids + j0 + j);
+                idr[j] = q.x; idr[j + 1] = q.y; idr[j + 2] = q.z; idr[j + 3] = q.w;
+            }
             uint32_t v[32];
             tc_ld_32x32(tmem_lanes + kColF + (uint32_t)j0, v);
             const int c = cb + r;
             if (c < cin) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    if (j0 + j < cnt) atomicAdd(d_feat + (int64_t)ids[j0 + j] * cin + c, __uint_as_float(v[j]));
+                    if (j0 + j < cnt) atomicAdd(d_feat + (int64_t)idr[j] * cin + c, __uint_as_float(v[j]));
                 }
             }
         };

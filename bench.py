@@ -235,9 +235,6 @@ class Ranks(object):
         self.numa_cpus = bind_to_gpu_numa_node(self.local_rank) if self.world > 1 else None
         if self.world > 1:
             import torch.distributed as dist
-            # whatever NCCL logs (its version line where NCCL_DEBUG asks for one) goes to stderr: stdout carries
-            # the one JSON line and nothing else
-            os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
             dist.init_process_group("nccl", device_id=self.device)
 
     def barrier(self):
@@ -753,7 +750,7 @@ def run_reference(args):
                          "sample": "%d clouds x %d points per step, %d steps" % (num_clouds, POINTS_PER_CLOUD, steps)},
         "e2e": {"value": value, "unit": "pairs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(json.dumps(line))
 
 
 # ---- convolution configurations ------------------------------------------------------------------
@@ -1359,7 +1356,7 @@ def run_pooling_workload(args):
             rows.append([m[j].elapsed_time(m[j + 1]) for j in range(4)])
     same = bool(torch.equal(by_list, by_grid))
     front, search, listed, gridded = [float(np.mean([r[j] for r in rows])) for j in range(4)]
-    print(json.dumps({
+    emit(json.dumps({
         "metric": "pooled points/s (Poisson-disk pooling, list-free route)", "value": pts.shape[0] / ((front + gridded) * 1e-3),
         "unit": "points/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": front + gridded,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32+i32/i64", "data": "synthetic",
@@ -1378,7 +1375,7 @@ def run_reference_gpu(args):
     import torch
     so = os.path.join(ROOT, "oracle", "_ref", "pccnn_lib_ops.so")
     if not os.path.exists(so):
-        print(json.dumps({"impl": "reference_gpu", "unavailable": "oracle/_ref/pccnn_lib_ops.so has not been built"}))
+        emit(json.dumps({"impl": "reference_gpu", "unavailable": "oracle/_ref/pccnn_lib_ops.so has not been built"}))
         return
     spec = importlib.util.spec_from_file_location("pccnn_lib_ops", so)
     ref = importlib.util.module_from_spec(spec)
@@ -1415,7 +1412,7 @@ def run_reference_gpu(args):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
-    print(json.dumps({"impl": "reference_gpu", "metric": "neighbor pairs/s (radius search + KDE)",
+    emit(json.dumps({"impl": "reference_gpu", "metric": "neighbor pairs/s (radius search + KDE)",
                       "value": pairs / (ms * 1e-3), "unit": "pairs/s", "n_gpus": 1, "steps": args.steps,
                       "ms_per_step": ms / args.steps, "higher_is_better": True,
                       "config": {"workload": "neighbor search + KDE: %d clouds x 100k surface points, radius 0.05"
@@ -1432,14 +1429,14 @@ def run_reference_gpu_conv(args):
     from pccnn_lib_b200.pc.layers import prepare_kernel_points
     so = os.path.join(ROOT, "oracle", "_ref", "pccnn_lib_ops.so")
     if not os.path.exists(so):
-        print(json.dumps({"impl": "reference_gpu", "unavailable": "oracle/_ref/pccnn_lib_ops.so has not been built"}))
+        emit(json.dumps({"impl": "reference_gpu", "unavailable": "oracle/_ref/pccnn_lib_ops.so has not been built"}))
         return
     spec = importlib.util.spec_from_file_location("pccnn_lib_ops", so)
     ref = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(ref)
     w = dict(CONV_WORKLOADS[args.workload])
     if len(w["layers"]) != 1:
-        print(json.dumps({"impl": "reference_gpu", "unavailable": "single-layer workloads only"}))
+        emit(json.dumps({"impl": "reference_gpu", "unavailable": "single-layer workloads only"}))
         return
     if args.points:
         w["pts"] = args.points
@@ -1483,7 +1480,7 @@ def run_reference_gpu_conv(args):
     fwd_ms, _ = device_timed(fwd, args.steps, max(args.warmup, 1))
     bwd_ms = device_timed(bwd, args.steps, max(args.warmup, 1))[0] if w["backward"] else 0.0
     step_ms = fwd_ms + bwd_ms
-    print(json.dumps({"impl": "reference_gpu", "metric": "conv-layer points/s", "value": m / (step_ms * 1e-3),
+    emit(json.dumps({"impl": "reference_gpu", "metric": "conv-layer points/s", "value": m / (step_ms * 1e-3),
                       "unit": "points/s", "ms_per_step": step_ms,
                       "config": {"workload": w["desc"], "forward_ms": fwd_ms, "backward_ms": bwd_ms, "samples": m,
                                  "pairs": int(nb.neighbors_.shape[0]),
@@ -1498,7 +1495,7 @@ def run_b200(args):
         entry = encoder_entry(args, R) if args.workload == "kpconv_encoder_cfg3" else conv_entry(args.workload, args, R)
         if R.rank == 0:
             entry.update({"higher_is_better": True, "scaling": "weak", "vs_baseline": None})
-            print(json.dumps(entry))
+            emit(json.dumps(entry))
         R.close()
         return
     line = run_neighbors_kde(args, R)
@@ -1514,11 +1511,32 @@ def run_b200(args):
             secondary.append(entry)
     if R.rank == 0:
         line["secondary"] = secondary
-        print(json.dumps(line))
+        emit(json.dumps(line))
     R.close()
 
 
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """From here on everything any library writes to file descriptor 1 (NCCL's version line, for one) goes to stderr;
+    the result line alone is written to what stdout was."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(text):
+    if _RESULT_FD is None:
+        print(text)
+        return
+    sys.stdout.flush()
+    os.write(_RESULT_FD, (text + "\n").encode())
+
+
 def main():
+    keep_stdout_for_the_result()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

@@ -332,7 +332,10 @@ int pccnn_kp_conv_grid(int64_t num_pts, const float* sorted_pts, const int64_t* 
 /* MCConv forward: basis b[t,:] = leaky_relu_{0.2}(d_t . axis + bias) / pdf[n0(t)], axis [D, hidden],
  * bias [hidden], weights [num_mlps, hidden / num_mlps * cin, cout / num_mlps] (hidden counts the
  * units of all MLPs together, as the reference's proj_axis_ does).
- * Replaces mcconv()  pccnn_lib_ops/pcconvs/mcconv.cu:32-71 (stages shared/mlp_basis.cu:27-48). */
+ * Replaces mcconv()  pccnn_lib_ops/pcconvs/mcconv.cu:32-71 (stages shared/mlp_basis.cu:27-48).
+ * With num_mlps > 1 the slices of the operands must start on 16-byte boundaries: hidden / num_mlps * cin a multiple
+ * of 8 here, and cout / num_mlps a multiple of 8 as well in pccnn_mc_conv_grads; other shapes are refused with
+ * PCCNN_ERR_INVALID before anything is launched.  num_mlps == 1 has no such restriction. */
 int pccnn_mc_conv(int D, int64_t num_pts, const float* pts, const float* pdf, const float* feats, int cin,
                   int64_t num_samples, const float* samples, const int32_t* neighbors,
                   const int32_t* start_ids, const float* radii, const float* axis, const float* bias,

@@ -84,7 +84,8 @@ neighbors_kernel(int num_pts, const float* __restrict__ pts, const int64_t* __re
                  const float* __restrict__ radii, int max_neighbors,
                  int32_t* __restrict__ counts,             // kCount: out; kStoreLimited: raw counts in
                  const int32_t* __restrict__ start_ids,    // stores: inclusive ends
-                 const int64_t* __restrict__ pt_index_map, int2* __restrict__ out, MaskCache cache) {
+                 const int64_t* __restrict__ pt_index_map, int2* __restrict__ out, MaskCache cache,
+                 const int32_t* __restrict__ tile_order, int num_tiles) {
     using S = Stencil<D>;
     constexpr int kChunks = S::kSlots / 32;
     __shared__ float4 s_slots[kWarpsPerBlock][S::kPlanes * S::kSlots];
@@ -97,7 +98,11 @@ neighbors_kernel(int num_pts, const float* __restrict__ pts, const int64_t* __re
     int* lo = s_lo[warp];
     int* pref = s_pref[warp];
 
-    const int i0 = (blockIdx.x * kWarpsPerBlock + warp) * 32;
+    // Tiles of 32 samples; with tile_order the heaviest come first, so that no SM is left alone with one of them
+    // at the end of the launch.
+    const int slot = blockIdx.x * kWarpsPerBlock + warp;
+    if (slot >= num_tiles) return;
+    const int i0 = (tile_order ? __ldg(tile_order + slot) : slot) * 32;
     if (i0 >= num_samples) return;
     const int n_here = min(32, num_samples - i0);
     const GridDesc<D> g = load_grid<D>(grid_size);
@@ -338,14 +343,45 @@ __global__ void clamp_counts_kernel(int n, const int32_t* __restrict__ counts, i
     if (lane_id() == 0 && local) atomicAdd(total, local);
 }
 
+// Work estimates per tile of 32 samples (in the order the search visits them), for the heaviest-first order.
+// Before anything is counted: the points in the three cells around the tile's first sample along the last
+// axis (two binary searches in the sorted keys), a measure of the local density.
+__global__ void tile_density_kernel(int num_tiles, const int64_t* __restrict__ sample_keys,
+                                    const int32_t* __restrict__ order, const int64_t* __restrict__ pt_keys, int num_pts,
+                                    uint32_t* __restrict__ est) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= num_tiles) return;
+    const int i = t * 32;
+    const long long key = __ldg(sample_keys + (order ? __ldg(order + i) : i));
+    const int lo = lower_bound_key(pt_keys, 0, num_pts, key - 1);
+    const int hi = upper_bound_key(pt_keys, lo, num_pts, key + 1);
+    est[t] = (uint32_t)(hi - lo);
+}
+
+// Once the counts are known: the pairs of the tile.
+__global__ void tile_pairs_kernel(int num_tiles, int num_samples, const int32_t* __restrict__ order,
+                                  const int32_t* __restrict__ counts, uint32_t* __restrict__ est) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= num_tiles) return;
+    uint32_t sum = 0;
+    for (int i = t * 32; i < min(num_samples, t * 32 + 32); ++i) sum += (uint32_t)__ldg(counts + (order ? __ldg(order + i) : i));
+    est[t] = sum;
+}
+
 __global__ void iota32_kernel(int n, int32_t* out) {
     const int stride = gridDim.x * blockDim.x;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = i;
 }
 
 struct NeighborLayout {
-    size_t counts_off, total_off, order_off, iota_off, keys_off, cub_off, cub_bytes, mask_off_off, pool_off, total;
+    size_t counts_off, total_off, order_off, iota_off, keys_off, cub_off, cub_bytes, mask_off_off, tiles_off, pool_off, total;
+    int num_tiles;
+    size_t tile_sort_bytes;
 };
+
+// Launches of at least this many tiles visit them heaviest first (below, the few extra launches cost more than an
+// uneven end of the search).
+constexpr int kMinTilesForOrdering = 4096;
 
 // Hit-mask pool requested by default: 256 bytes (2048 tested candidates) per sample.
 constexpr size_t kMaskBytesPerSample = 256;
@@ -364,8 +400,14 @@ static NeighborLayout neighbor_layout(int64_t m) {
     L.iota_off = L.order_off + align_up((size_t)m * 4);
     L.keys_off = L.iota_off + align_up((size_t)m * 4);
     L.cub_off = L.keys_off + align_up((size_t)m * 8);
+    L.num_tiles = (mm + 31) / 32;
+    L.tile_sort_bytes = 0;
+    cub::DeviceRadixSort::SortPairsDescending(nullptr, L.tile_sort_bytes, (const uint32_t*)nullptr, (uint32_t*)nullptr,
+                                              (const int32_t*)nullptr, (int32_t*)nullptr, L.num_tiles, 0, 32);
+    if (L.tile_sort_bytes > L.cub_bytes) L.cub_bytes = L.tile_sort_bytes;
     L.mask_off_off = L.cub_off + align_up(L.cub_bytes) + 256;
-    L.pool_off = L.mask_off_off + align_up((size_t)m * 4);
+    L.tiles_off = L.mask_off_off + align_up((size_t)m * 4);
+    L.pool_off = L.tiles_off + 4 * align_up((size_t)L.num_tiles * 4);  // estimates, sorted estimates, tile ids, order
     size_t pool = (size_t)m * kMaskBytesPerSample;
     if (pool < (1u << 20)) pool = 1u << 20;
     if (pool > ((size_t)8 << 30)) pool = (size_t)8 << 30;
@@ -402,6 +444,32 @@ static MaskCache mask_cache(char* ws, const NeighborLayout& L, size_t workspace_
 
 static unsigned neighbor_grid(int64_t num_samples) {
     return (unsigned)((num_samples + kWarpsPerBlock * 32 - 1) / (kWarpsPerBlock * 32));
+}
+
+// Heaviest-first order of the tiles from the estimates in the first tile array; null when the launch is too small
+// for it to pay.  `counts` null = before the count pass (density estimate).
+static int tile_order(char* ws, const NeighborLayout& L, int m, const int64_t* sample_keys, const int32_t* order,
+                      const int64_t* pt_keys, int num_pts, const int32_t* counts, cudaStream_t s, const int32_t** out) {
+    *out = nullptr;
+    if (L.num_tiles < kMinTilesForOrdering || num_pts == 0) return PCCNN_OK;
+    const size_t stride = align_up((size_t)L.num_tiles * 4);
+    uint32_t* est = (uint32_t*)(ws + L.tiles_off);
+    uint32_t* est_sorted = (uint32_t*)(ws + L.tiles_off + stride);
+    int32_t* ids = (int32_t*)(ws + L.tiles_off + 2 * stride);
+    int32_t* sorted_ids = (int32_t*)(ws + L.tiles_off + 3 * stride);
+    const unsigned grid = (unsigned)((L.num_tiles + 255) / 256);
+    if (counts)
+        tile_pairs_kernel<<<grid, 256, 0, s>>>(L.num_tiles, m, order, counts, est);
+    else
+        tile_density_kernel<<<grid, 256, 0, s>>>(L.num_tiles, sample_keys, order, pt_keys, num_pts, est);
+    PCCNN_LAUNCH_CHECK();
+    iota32_kernel<<<grid, 256, 0, s>>>(L.num_tiles, ids);
+    PCCNN_LAUNCH_CHECK();
+    size_t bytes = L.cub_bytes;
+    PCCNN_CUDA(cub::DeviceRadixSort::SortPairsDescending(ws + L.cub_off, bytes, (const uint32_t*)est, est_sorted,
+                                                         (const int32_t*)ids, sorted_ids, L.num_tiles, 0, 32, s));
+    *out = sorted_ids;
+    return PCCNN_OK;
 }
 
 }  // namespace pccnn
@@ -459,9 +527,12 @@ int pccnn_find_neighbors_count(int D, int64_t num_pts, const float* pts, const i
                                                    sample_key_bits > 0 ? sample_key_bits : 64, s));
         order = (const int32_t*)(ws + L.order_off);
     }
+    const int32_t* tiles = nullptr;
+    if (int rc = tile_order(ws, L, m, sample_keys, order, pt_keys, (int)num_pts, nullptr, s, &tiles)) return rc;
     PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kCount><<<neighbor_grid(m), kWarpsPerBlock * 32, 0, s>>>(
                               (int)num_pts, pts, pt_keys, m, samples, sample_keys, order, (const int2*)grid_ds,
-                              grid_size, radii, max_neighbors, counts, nullptr, nullptr, nullptr, cache)));
+                              grid_size, radii, max_neighbors, counts, nullptr, nullptr, nullptr, cache, tiles,
+                              L.num_tiles)));
     PCCNN_LAUNCH_CHECK();
     clamp_counts_kernel<<<grid_for(m, 256, 8), 256, 0, s>>>(m, counts, max_neighbors, out_start_ids, total_dev);
     PCCNN_LAUNCH_CHECK();
@@ -501,16 +572,18 @@ int pccnn_find_neighbors_store(int D, int64_t num_pts, const float* pts, const i
         samples_are_sorted_points(pts, pt_keys, samples, sample_keys) ? nullptr : (const int32_t*)(ws + L.order_off);
     const int m = (int)num_samples;
     const MaskCache cache = mask_cache(ws, L, workspace_bytes);
+    const int32_t* tiles = nullptr;
+    if (int rc = tile_order(ws, L, m, sample_keys, order, pt_keys, (int)num_pts, counts, s, &tiles)) return rc;
     if (max_neighbors > 0) {
         PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kStoreLimited><<<neighbor_grid(m), kWarpsPerBlock * 32, 0, s>>>(
                                   (int)num_pts, pts, pt_keys, m, samples, sample_keys, order, (const int2*)grid_ds,
                                   grid_size, radii, max_neighbors, counts, start_ids, pt_index_map,
-                                  (int2*)out_neighbors, cache)));
+                                  (int2*)out_neighbors, cache, tiles, L.num_tiles)));
     } else {
         PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kStore><<<neighbor_grid(m), kWarpsPerBlock * 32, 0, s>>>(
                                   (int)num_pts, pts, pt_keys, m, samples, sample_keys, order, (const int2*)grid_ds,
                                   grid_size, radii, max_neighbors, counts, start_ids, pt_index_map,
-                                  (int2*)out_neighbors, cache)));
+                                  (int2*)out_neighbors, cache, tiles, L.num_tiles)));
     }
     PCCNN_LAUNCH_CHECK();
     return PCCNN_OK;

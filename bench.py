@@ -648,7 +648,10 @@ def run_neighbors_kde(args, R):
                 "host_results_equal_resident_run": e2e_verified,
                 "pipelining": "uploads of the next and downloads of the previous sub-batch overlap the kernels of the "
                               "current one (two copy streams); all copies inside the timed region"},
-        "gpu_launches": 12 * n_sub * args.steps,
+        # kernels of this library per sub-batch and step (cub's sort and scan kernels not counted): box init and
+        # accumulate, cells per axis, keys, iota, gather, cell table; tile estimate + iota, count, clamp; tile estimate
+        # + iota, store; point padding, density
+        "gpu_launches": 16 * n_sub * args.steps,
         "roofline": roofline,
         "cpu_baseline": cpu,
         "parity_checked": parity,

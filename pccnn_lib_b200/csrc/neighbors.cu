@@ -355,7 +355,7 @@ __global__ void tile_density_kernel(int num_tiles, const int64_t* __restrict__ s
     const long long key = __ldg(sample_keys + (order ? __ldg(order + i) : i));
     const int lo = lower_bound_key(pt_keys, 0, num_pts, key - 1);
     const int hi = upper_bound_key(pt_keys, lo, num_pts, key + 1);
-    est[t] = (uint32_t)(hi - lo);
+    est[t] = (uint32_t)min(hi - lo, 0xffff);  // 16 bits order the tiles well enough and halve the sort
 }
 
 // Once the counts are known: the pairs of the tile.
@@ -365,7 +365,7 @@ __global__ void tile_pairs_kernel(int num_tiles, int num_samples, const int32_t*
     if (t >= num_tiles) return;
     uint32_t sum = 0;
     for (int i = t * 32; i < min(num_samples, t * 32 + 32); ++i) sum += (uint32_t)__ldg(counts + (order ? __ldg(order + i) : i));
-    est[t] = sum;
+    est[t] = min(sum >> 3, 0xffffu);  // 16 bits, as above
 }
 
 __global__ void iota32_kernel(int n, int32_t* out) {
@@ -381,7 +381,7 @@ struct NeighborLayout {
 
 // Launches of at least this many tiles visit them heaviest first (below, the few extra launches cost more than an
 // uneven end of the search).
-constexpr int kMinTilesForOrdering = 4096;
+constexpr int kMinTilesForOrdering = 8192;
 
 // Hit-mask pool requested by default: 256 bytes (2048 tested candidates) per sample.
 constexpr size_t kMaskBytesPerSample = 256;
@@ -403,7 +403,7 @@ static NeighborLayout neighbor_layout(int64_t m) {
     L.num_tiles = (mm + 31) / 32;
     L.tile_sort_bytes = 0;
     cub::DeviceRadixSort::SortPairsDescending(nullptr, L.tile_sort_bytes, (const uint32_t*)nullptr, (uint32_t*)nullptr,
-                                              (const int32_t*)nullptr, (int32_t*)nullptr, L.num_tiles, 0, 32);
+                                              (const int32_t*)nullptr, (int32_t*)nullptr, L.num_tiles, 0, 16);
     if (L.tile_sort_bytes > L.cub_bytes) L.cub_bytes = L.tile_sort_bytes;
     L.mask_off_off = L.cub_off + align_up(L.cub_bytes) + 256;
     L.tiles_off = L.mask_off_off + align_up((size_t)m * 4);
@@ -467,7 +467,7 @@ static int tile_order(char* ws, const NeighborLayout& L, int m, const int64_t* s
     PCCNN_LAUNCH_CHECK();
     size_t bytes = L.cub_bytes;
     PCCNN_CUDA(cub::DeviceRadixSort::SortPairsDescending(ws + L.cub_off, bytes, (const uint32_t*)est, est_sorted,
-                                                         (const int32_t*)ids, sorted_ids, L.num_tiles, 0, 32, s));
+                                                         (const int32_t*)ids, sorted_ids, L.num_tiles, 0, 16, s));
     *out = sorted_ids;
     return PCCNN_OK;
 }

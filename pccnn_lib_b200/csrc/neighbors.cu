@@ -355,7 +355,7 @@ __global__ void tile_density_kernel(int num_tiles, const int64_t* __restrict__ s
     const long long key = __ldg(sample_keys + (order ? __ldg(order + i) : i));
     const int lo = lower_bound_key(pt_keys, 0, num_pts, key - 1);
     const int hi = upper_bound_key(pt_keys, lo, num_pts, key + 1);
-    est[t] = (uint32_t)min(hi - lo, 0xffff);  // 16 bits order the tiles well enough and halve the sort
+    est[t] = (uint32_t)(32 - __clz(hi - lo));  // its power of two: see tile_order
 }
 
 // Once the counts are known: the pairs of the tile.
@@ -365,7 +365,7 @@ __global__ void tile_pairs_kernel(int num_tiles, int num_samples, const int32_t*
     if (t >= num_tiles) return;
     uint32_t sum = 0;
     for (int i = t * 32; i < min(num_samples, t * 32 + 32); ++i) sum += (uint32_t)__ldg(counts + (order ? __ldg(order + i) : i));
-    est[t] = min(sum >> 3, 0xffffu);  // 16 bits, as above
+    est[t] = (uint32_t)(32 - __clz((int)min(sum, 0x7fffffffu)));
 }
 
 __global__ void iota32_kernel(int n, int32_t* out) {
@@ -403,7 +403,7 @@ static NeighborLayout neighbor_layout(int64_t m) {
     L.num_tiles = (mm + 31) / 32;
     L.tile_sort_bytes = 0;
     cub::DeviceRadixSort::SortPairsDescending(nullptr, L.tile_sort_bytes, (const uint32_t*)nullptr, (uint32_t*)nullptr,
-                                              (const int32_t*)nullptr, (int32_t*)nullptr, L.num_tiles, 0, 16);
+                                              (const int32_t*)nullptr, (int32_t*)nullptr, L.num_tiles, 0, 6);
     if (L.tile_sort_bytes > L.cub_bytes) L.cub_bytes = L.tile_sort_bytes;
     L.mask_off_off = L.cub_off + align_up(L.cub_bytes) + 256;
     L.tiles_off = L.mask_off_off + align_up((size_t)m * 4);
@@ -446,8 +446,10 @@ static unsigned neighbor_grid(int64_t num_samples) {
     return (unsigned)((num_samples + kWarpsPerBlock * 32 - 1) / (kWarpsPerBlock * 32));
 }
 
-// Heaviest-first order of the tiles from the estimates in the first tile array; null when the launch is too small
-// for it to pay.  `counts` null = before the count pass (density estimate).
+// Heaviest-first order of the tiles; null when the launch is too small for it to pay.  `counts` null = before the
+// count pass (density estimate).  The tiles are ordered by the power of two of their estimate only, with a stable
+// sort: the classes go from heavy to light, and inside a class the tiles keep their cell order, so that tiles
+// running at the same time still share candidates in the caches.
 static int tile_order(char* ws, const NeighborLayout& L, int m, const int64_t* sample_keys, const int32_t* order,
                       const int64_t* pt_keys, int num_pts, const int32_t* counts, cudaStream_t s, const int32_t** out) {
     *out = nullptr;
@@ -467,7 +469,7 @@ static int tile_order(char* ws, const NeighborLayout& L, int m, const int64_t* s
     PCCNN_LAUNCH_CHECK();
     size_t bytes = L.cub_bytes;
     PCCNN_CUDA(cub::DeviceRadixSort::SortPairsDescending(ws + L.cub_off, bytes, (const uint32_t*)est, est_sorted,
-                                                         (const int32_t*)ids, sorted_ids, L.num_tiles, 0, 16, s));
+                                                         (const int32_t*)ids, sorted_ids, L.num_tiles, 0, 6, s));
     *out = sorted_ids;
     return PCCNN_OK;
 }

@@ -5,9 +5,10 @@
 
 Headline (the JSON line's `value`): neighbor search + KDE on 16 clouds x 100 000 surface points per GPU, radius
 0.05, KDE bandwidth 0.01.  One step = bounding boxes -> grid size -> keys -> stable sort (+ gathers) -> cell table
--> radius search (count, scan, store) -> KDE for one batch.  With N GPUs the batch is 16 N distinct clouds,
-dealt to the ranks by an estimate of their neighbor pairs (clouds are independent: no collective on the data
-path); the value is all pairs divided by the slowest rank's time.
+-> radius search (count, scan, store) -> KDE for one batch.  With N GPUs the batch is 16 N distinct clouds
+(every 16 consecutive ids hold the same mix of primitives, drawn anew), dealt to the ranks by an estimate of their
+neighbor pairs (clouds are independent: no collective on the data path); the value is all pairs divided by the
+slowest rank's time.
 
 The same line carries, under `secondary`, the convolution configurations (conv-layer points/s): the single-layer
 KPConv forward on 4096 points, MCConv forward+backward on 32 x 32k points with Poisson-disk pooled outputs, the
@@ -34,6 +35,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 CLOUDS_PER_RANK = 16
+CLOUDS_PER_RANK_DEFAULT = 16  # the surface sampler repeats its recipes with this period (not changed by --clouds)
 POINTS_PER_CLOUD = 100000
 RADIUS = 0.05
 BANDWIDTH = 0.01
@@ -51,12 +53,16 @@ def _rotation(rs):
 
 def surface_cloud(cloud_id, num_pts):
     """Points on the surfaces of 1-8 random primitives (sphere / box / plane patch, scale 0.1-0.5,
-    centres in the unit cube) plus N(0, 0.002) jitter; seeded by the cloud id."""
-    rs = np.random.RandomState(1000 + cloud_id)
+    centres in the unit cube) plus N(0, 0.002) jitter; seeded by the cloud id.  Clouds 16 and up repeat the
+    primitives of cloud (id mod 16) with points, orientations and jitter drawn anew, so that every 16 consecutive
+    clouds -- what one GPU gets under weak scaling -- hold the same mix of sparse and dense clouds."""
+    rs = np.random.RandomState(1000 + cloud_id % CLOUDS_PER_RANK_DEFAULT)
     k = rs.randint(1, 9)
     kinds = rs.randint(0, 3, size=k)
     scales = rs.uniform(0.1, 0.5, size=k)
     centres = rs.uniform(0.0, 1.0, size=(k, 3))
+    if cloud_id >= CLOUDS_PER_RANK_DEFAULT:
+        rs = np.random.RandomState(1000 + cloud_id)
     areas = np.where(kinds == 0, 4 * np.pi * scales ** 2, np.where(kinds == 1, 24 * scales ** 2, 4 * scales ** 2))
     counts = np.floor(areas / areas.sum() * num_pts).astype(np.int64)
     counts[np.argmax(counts)] += num_pts - counts.sum()
@@ -634,9 +640,10 @@ def run_neighbors_kde(args, R):
                    "pairs_per_step_rank0": t_rank, "neighbors_per_point_rank0": t_rank / n_pts,
                    "pointcloud_compute_pdf_ms": round(class_pdf_ms, 3), "sub_batches_for_int32_offsets": n_sub,
                    "l2": "inputs larger than L2 (neighbor list)", "library_kernels": "cub radix sort and scan",
-                   "sharding": "one batch of 16 N distinct clouds dealt to the ranks by estimated neighbor pairs, heaviest "
-                               "first (parallel.assign_clouds); every rank runs the whole pipeline on its clouds; no "
-                               "collective on the data path",
+                   "sharding": "one batch of 16 N distinct clouds (every 16 consecutive ids repeat the same primitives with "
+                               "new points) dealt to the ranks by estimated neighbor pairs, heaviest first "
+                               "(parallel.assign_clouds); every rank runs the whole pipeline on its clouds; no collective "
+                               "on the data path",
                    "clouds_rank0": cloud_ids,
                    "rank_ms_per_step": [round(v, 4) for v in rank_ms], "rank_pairs_per_step": rank_pairs,
                    "imbalance_max_over_mean": round(max(rank_ms) / mean_ms, 4) if mean_ms > 0 else None,

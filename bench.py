@@ -855,7 +855,19 @@ def _conv_host_data(w, R):
     if w["gen"] == "cube":
         return np.random.RandomState(1000).rand(w["pts"], 3).astype(np.float32), np.zeros(w["pts"], np.int32), 1
     if w["gen"] == "scene":
-        return scene_cloud(R.rank, w["pts"]), np.zeros(w["pts"], np.int32), 1
+        # Weak scaling with equal work: every rank gets the same room, turned by a multiple of 90 degrees about its
+        # centre (mirrored from the fifth rank on) and shifted by a fraction of a cell, i.e. different coordinates,
+        # another alignment to the grid, the same neighborhoods.
+        pts = scene_cloud(0, w["pts"])
+        if R.rank > 0:
+            x, y = pts[:, 0] - 10.0, pts[:, 1] - 10.0
+            if R.rank >= 4:
+                x = -x
+            for _ in range(R.rank % 4):
+                x, y = -y, x
+            shift = np.float32(0.013 * R.rank)
+            pts = np.stack([x + 10.0 + shift, y + 10.0 + shift, pts[:, 2]], 1).astype(np.float32)
+        return np.ascontiguousarray(pts), np.zeros(w["pts"], np.int32), 1
     from pccnn_lib_b200 import parallel
     lo, hi = parallel.shard_clouds([w["pts"]] * w["clouds"], R.world, R.rank)
     pts, ids = make_batch(lo, hi - lo, w["pts"])
@@ -1041,7 +1053,7 @@ def conv_entry(name, args, R, steps=None, with_gemm_alone=True):
                    "forward_ms": fwd_ms, "backward_ms": ms - fwd_ms if w["backward"] else 0.0,
                    "setup_s_untimed": setup_s,
                    "sharding": {"none": "single cloud", "clouds": "clouds split over the ranks (parallel.shard_clouds)",
-                                "scenes": "one scene per rank"}[w["shard"]]},
+                                "scenes": "one scene per rank (the same room, turned and shifted)"}[w["shard"]]},
         "clocks": clocks,
         "e2e": {"value": total_m / (e2e_ms * 1e-3), "unit": "points/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -56,6 +56,15 @@ inline unsigned grid_for(int64_t work_items, int block, int blocks_per_sm) {
 // ---- device helpers -----------------------------------------------------------------------
 #ifdef __CUDACC__
 
+// Grid of a grid-stride kernel whose blocks all get the same share of the work: exactly the blocks that are resident
+// at once (registers decide how many), so that no partial second wave runs alone at a fraction of the occupancy.
+template <class Kernel>
+inline unsigned resident_grid(Kernel kernel, int64_t work_items, int block) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+    return grid_for(work_items, block, per_sm);
+}
+
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
 
 // Packed fp32x2 arithmetic (sm_100): both halves are rounded to nearest, as by the scalar

@@ -308,8 +308,8 @@ int pccnn_compute_pdf_grads(int D, int manifold_dims, const float* bandwidth, in
     PCCNN_CHECK_ARG(bandwidth && pts && start_ids && in_grads && out_pt_grads, "compute_pdf_grads: null pointer");
     cudaStream_t s = (cudaStream_t)stream;
     PCCNN_CUDA(cudaMemsetAsync(out_pt_grads, 0, (size_t)n * D * sizeof(float), s));
-    const unsigned grid = grid_for(n * 32, kPdfWarps * 32, 8);
-    PCCNN_DISPATCH_DIM(D, (pdf_grads_kernel<DIM><<<grid, kPdfWarps * 32, 0, s>>>(
+    PCCNN_DISPATCH_DIM(D, (pdf_grads_kernel<DIM><<<resident_grid(pdf_grads_kernel<DIM>, n * 32, kPdfWarps * 32),
+                                                   kPdfWarps * 32, 0, s>>>(
                               manifold_dims, bandwidth, (int)n, pts, (const int2*)neighbors, start_ids, in_grads,
                               out_pt_grads)));
     PCCNN_LAUNCH_CHECK();
@@ -323,17 +323,19 @@ int pccnn_compute_pdf_grads_symmetric(int D, int manifold_dims, const float* ban
     if (n == 0) return PCCNN_OK;
     PCCNN_CHECK_ARG(bandwidth && pts && start_ids && in_grads && out_pt_grads, "compute_pdf_grads_symmetric: null pointer");
     cudaStream_t s = (cudaStream_t)stream;
-    const unsigned grid = grid_for(n * 32, kPdfWarps * 32, 8);
     if (D == 3 && workspace && workspace_bytes >= (size_t)n * 16 && reinterpret_cast<uintptr_t>(workspace) % 16 == 0) {
         float4* padded = (float4*)workspace;
         pad_points_grads_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>((int)n, pts, in_grads, padded);
         PCCNN_LAUNCH_CHECK();
-        pdf_grads_symmetric_padded<<<grid, kPdfWarps * 32, 0, s>>>(manifold_dims, bandwidth, (int)n, padded,
-                                                                  (const int2*)neighbors, start_ids, out_pt_grads);
+        pdf_grads_symmetric_padded<<<resident_grid(pdf_grads_symmetric_padded, n * 32, kPdfWarps * 32), kPdfWarps * 32, 0,
+                                     s>>>(manifold_dims, bandwidth, (int)n, padded, (const int2*)neighbors, start_ids,
+                                          out_pt_grads);
         PCCNN_LAUNCH_CHECK();
         return PCCNN_OK;
     }
-    PCCNN_DISPATCH_DIM(D, (pdf_grads_symmetric_kernel<DIM><<<grid, kPdfWarps * 32, 0, s>>>(
+    PCCNN_DISPATCH_DIM(D, (pdf_grads_symmetric_kernel<DIM><<<resident_grid(pdf_grads_symmetric_kernel<DIM>, n * 32,
+                                                                          kPdfWarps * 32),
+                                                             kPdfWarps * 32, 0, s>>>(
                               manifold_dims, bandwidth, (int)n, pts, (const int2*)neighbors, start_ids, in_grads,
                               out_pt_grads)));
     PCCNN_LAUNCH_CHECK();

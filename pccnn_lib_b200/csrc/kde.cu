@@ -102,7 +102,18 @@ pdf_kernel_padded(int manifold_dims, const float* __restrict__ bandwidth, int n,
             const float vx = (q.x - p.x) * ibw[0], vy = (q.y - p.y) * ibw[1], vz = (q.z - p.z) * ibw[2];
             return expf(fmaf(vz, vz, fmaf(vy, vy, fmaf(vx, vx, 0.f))) * -0.5f);
         };
+        // eight row loads per lane in flight where the row is long enough (4 % over four), then four, then one
         int t = lo + lane;
+        for (; t + 224 < hi; t += 256) {
+            int j[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) j[u] = __ldcs(&neighbors[t + 32 * u]).x;
+            float e[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) e[u] = term(j[u]);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc += e[u];
+        }
         for (; t + 96 < hi; t += 128) {
             const int j0 = __ldcs(&neighbors[t]).x;
             const int j1 = __ldcs(&neighbors[t + 32]).x;
@@ -288,8 +299,8 @@ int pccnn_compute_pdf(int D, int manifold_dims, const float* bandwidth, int64_t 
         float4* padded = (float4*)workspace;
         pad_points_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>((int)n, pts, padded);
         PCCNN_LAUNCH_CHECK();
-        pdf_kernel_padded<<<grid, kPdfWarps * 32, 0, s>>>(manifold_dims, bandwidth, (int)n, padded, (const int2*)neighbors,
-                                                         start_ids, out_pdf);
+        pdf_kernel_padded<<<resident_grid(pdf_kernel_padded, n * 32, kPdfWarps * 32), kPdfWarps * 32, 0, s>>>(
+            manifold_dims, bandwidth, (int)n, padded, (const int2*)neighbors, start_ids, out_pdf);
         PCCNN_LAUNCH_CHECK();
         return PCCNN_OK;
     }

@@ -75,8 +75,10 @@ __device__ __forceinline__ void emit_row(int2* __restrict__ out, int base, int r
     }
 }
 
-template <int D, int MODE>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+// MIN_BLOCKS: resident blocks per SM the register allocation has to leave room for (the 3-D count pass gains 4 %
+// from 8 blocks of 64 registers against 7 of 72; the other passes are left to the compiler).
+template <int D, int MODE, int MIN_BLOCKS = 1>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS)
 neighbors_kernel(int num_pts, const float* __restrict__ pts, const int64_t* __restrict__ pt_keys,
                  int num_samples, const float* __restrict__ samples, const int64_t* __restrict__ sample_keys,
                  const int32_t* __restrict__ sample_order,  // samples in cell order, or null = identity
@@ -355,7 +357,9 @@ __global__ void tile_density_kernel(int num_tiles, const int64_t* __restrict__ s
     const long long key = __ldg(sample_keys + (order ? __ldg(order + i) : i));
     const int lo = lower_bound_key(pt_keys, 0, num_pts, key - 1);
     const int hi = upper_bound_key(pt_keys, lo, num_pts, key + 1);
-    est[t] = (uint32_t)(32 - __clz(hi - lo));  // its power of two: see tile_order
+    // its class: the power of two and the bit below it (half octaves; see tile_order)
+    const int v = hi - lo, c = 32 - __clz(v);
+    est[t] = (uint32_t)(2 * c + (c >= 2 ? ((v >> (c - 2)) & 1) : 0));
 }
 
 // Once the counts are known: the pairs of the tile.
@@ -365,7 +369,7 @@ __global__ void tile_pairs_kernel(int num_tiles, int num_samples, const int32_t*
     if (t >= num_tiles) return;
     uint32_t sum = 0;
     for (int i = t * 32; i < min(num_samples, t * 32 + 32); ++i) sum += (uint32_t)__ldg(counts + (order ? __ldg(order + i) : i));
-    est[t] = (uint32_t)(32 - __clz((int)min(sum, 0x7fffffffu)));
+    est[t] = (uint32_t)(2 * (32 - __clz((int)min(sum, 0x7fffffffu))));  // whole octaves, on the scale of the density classes
 }
 
 __global__ void iota32_kernel(int n, int32_t* out) {
@@ -403,7 +407,7 @@ static NeighborLayout neighbor_layout(int64_t m) {
     L.num_tiles = (mm + 31) / 32;
     L.tile_sort_bytes = 0;
     cub::DeviceRadixSort::SortPairsDescending(nullptr, L.tile_sort_bytes, (const uint32_t*)nullptr, (uint32_t*)nullptr,
-                                              (const int32_t*)nullptr, (int32_t*)nullptr, L.num_tiles, 0, 6);
+                                              (const int32_t*)nullptr, (int32_t*)nullptr, L.num_tiles, 0, 7);
     if (L.tile_sort_bytes > L.cub_bytes) L.cub_bytes = L.tile_sort_bytes;
     L.mask_off_off = L.cub_off + align_up(L.cub_bytes) + 256;
     L.tiles_off = L.mask_off_off + align_up((size_t)m * 4);
@@ -447,9 +451,10 @@ static unsigned neighbor_grid(int64_t num_samples) {
 }
 
 // Heaviest-first order of the tiles; null when the launch is too small for it to pay.  `counts` null = before the
-// count pass (density estimate).  The tiles are ordered by the power of two of their estimate only, with a stable
-// sort: the classes go from heavy to light, and inside a class the tiles keep their cell order, so that tiles
-// running at the same time still share candidates in the caches.
+// count pass (density estimate).  The tiles are ordered by a coarse class of their estimate only (half octaves of
+// the density, whole octaves of the pair count: what measured best for each pass), with a stable sort: the classes
+// go from heavy to light, and inside a class the tiles keep their cell order, so that tiles running at the same
+// time still share candidates in the caches.
 static int tile_order(char* ws, const NeighborLayout& L, int m, const int64_t* sample_keys, const int32_t* order,
                       const int64_t* pt_keys, int num_pts, const int32_t* counts, cudaStream_t s, const int32_t** out) {
     *out = nullptr;
@@ -469,7 +474,7 @@ static int tile_order(char* ws, const NeighborLayout& L, int m, const int64_t* s
     PCCNN_LAUNCH_CHECK();
     size_t bytes = L.cub_bytes;
     PCCNN_CUDA(cub::DeviceRadixSort::SortPairsDescending(ws + L.cub_off, bytes, (const uint32_t*)est, est_sorted,
-                                                         (const int32_t*)ids, sorted_ids, L.num_tiles, 0, 6, s));
+                                                         (const int32_t*)ids, sorted_ids, L.num_tiles, 0, 7, s));
     *out = sorted_ids;
     return PCCNN_OK;
 }
@@ -531,7 +536,7 @@ int pccnn_find_neighbors_count(int D, int64_t num_pts, const float* pts, const i
     }
     const int32_t* tiles = nullptr;
     if (int rc = tile_order(ws, L, m, sample_keys, order, pt_keys, (int)num_pts, nullptr, s, &tiles)) return rc;
-    PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kCount><<<neighbor_grid(m), kWarpsPerBlock * 32, 0, s>>>(
+    PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kCount, (DIM == 3 ? 8 : 1)><<<neighbor_grid(m), kWarpsPerBlock * 32, 0, s>>>(
                               (int)num_pts, pts, pt_keys, m, samples, sample_keys, order, (const int2*)grid_ds,
                               grid_size, radii, max_neighbors, counts, nullptr, nullptr, nullptr, cache, tiles,
                               L.num_tiles)));

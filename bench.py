@@ -629,6 +629,10 @@ def run_neighbors_kde(args, R):
     h2d = sum(s["h_pts"].numel() * 4 + s["h_ids"].numel() * 4 for s in subs)
     d2h = sum(s["out_pdf"].numel() * 4 + s["out_ends"].numel() * 4 + s["out_perm"].numel() * 8 for s in subs)
     mean_ms = float(np.mean(rank_ms))
+    # neighbors per point of this rank's clouds, from the CSR ends the end-to-end run left in host memory
+    per_point = np.concatenate([np.diff(s["out_ends"].numpy().astype(np.int64), prepend=0) for s in subs])
+    quantiles = {name: int(v) for name, v in zip(["min", "p10", "p50", "p90", "p99", "max"],
+                                                  np.percentile(per_point, [0, 10, 50, 90, 99, 100]))}
     line = {
         "metric": "neighbor pairs/s (radius search + KDE)", "value": pairs / (ms * 1e-3), "unit": "pairs/s",
         "n_gpus": R.world, "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps,
@@ -638,6 +642,7 @@ def run_neighbors_kde(args, R):
                                "int32 CSR, fp32 KDE bandwidth 0.01" % CLOUDS_PER_RANK,
                    "clouds_total": total_clouds, "points_per_cloud": POINTS_PER_CLOUD,
                    "pairs_per_step_rank0": t_rank, "neighbors_per_point_rank0": t_rank / n_pts,
+                   "neighbors_per_point_quantiles_rank0": quantiles,
                    "pointcloud_compute_pdf_ms": round(class_pdf_ms, 3), "sub_batches_for_int32_offsets": n_sub,
                    "l2": "inputs larger than L2 (neighbor list)", "library_kernels": "cub radix sort and scan",
                    "sharding": "one batch of 16 N distinct clouds (every 16 consecutive ids repeat the same primitives with "

@@ -76,7 +76,7 @@ __device__ __forceinline__ void emit_row(int2* __restrict__ out, int base, int r
 }
 
 // MIN_BLOCKS: resident blocks per SM the register allocation has to leave room for (the 3-D count pass gains 4 %
-// from 8 blocks of 64 registers against 7 of 72).  0 leaves the choice to the compiler, which is not the same as 1:
+// from 8 blocks of 64 registers against 7 of 72 and 3 % more from 9 blocks of 56, which spills four words).  0 leaves the choice to the compiler, which is not the same as 1:
 // told that one block is enough, it gives the 3-D store pass 96 registers instead of 56 and the pass loses 7 %.
 template <int D, int MODE, int MIN_BLOCKS = 0>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, MIN_BLOCKS)
@@ -537,7 +537,7 @@ int pccnn_find_neighbors_count(int D, int64_t num_pts, const float* pts, const i
     }
     const int32_t* tiles = nullptr;
     if (int rc = tile_order(ws, L, m, sample_keys, order, pt_keys, (int)num_pts, nullptr, s, &tiles)) return rc;
-    PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kCount, (DIM == 3 ? 8 : 0)><<<neighbor_grid(m), kWarpsPerBlock * 32, 0, s>>>(
+    PCCNN_DISPATCH_DIM(D, (neighbors_kernel<DIM, kCount, (DIM == 3 ? 9 : 0)><<<neighbor_grid(m), kWarpsPerBlock * 32, 0, s>>>(
                               (int)num_pts, pts, pt_keys, m, samples, sample_keys, order, (const int2*)grid_ds,
                               grid_size, radii, max_neighbors, counts, nullptr, nullptr, nullptr, cache, tiles,
                               L.num_tiles)));

@@ -723,8 +723,15 @@ static int launch_project(int K, const ARGS& args, const float* pts, const FT* f
     return PCCNN_OK;
 }
 
-// Samples are processed in chunks so that the P scratch stays bounded.
-constexpr int64_t kConvChunk = 1 << 17;
+// Samples are processed in chunks so that the P scratch stays bounded: 131 072 samples, and 524 288 for calls with
+// more samples than that whose P row has at most 2048 entries (a 2 M-point scene is then 4 chunks instead of 16; the
+// ends of the chunks' launches, where the SMs run dry one by one, cost 2 % of such a layer; the scratch grows to
+// ~9 GB for 128 channels x 16 basis values, and an index into a chunk's P stays below 2^30).
+static int64_t conv_chunk(int64_t num_samples, int ld_p) {
+    const int64_t small = 1 << 17, large = 1 << 19;
+    if (num_samples <= 0) return 1;
+    return num_samples < small ? num_samples : ((num_samples > large && ld_p <= 2048) ? large : small);
+}
 
 struct ConvLayout {
     int ld_p;      // padded Cin * K
@@ -741,7 +748,7 @@ static size_t feature_plane_bytes(int64_t num_pts, int cin) {
 static ConvLayout conv_layout(int64_t num_pts, int64_t num_samples, int cin, int K, int cout) {
     ConvLayout L;
     L.ld_p = (cin * K + 63) / 64 * 64;
-    L.chunk = num_samples < kConvChunk ? (num_samples > 0 ? num_samples : 1) : kConvChunk;
+    L.chunk = conv_chunk(num_samples, L.ld_p);
     const size_t p_bytes = align_up((size_t)L.chunk * L.ld_p * 2);
     const size_t w_bytes = align_up((size_t)cout * L.ld_p * 2);
     L.p_hi_off = 0;
@@ -947,7 +954,7 @@ static ConvBackwardLayout conv_backward_layout(int64_t num_pts, int64_t num_samp
     const int inner = cin * K;
     L.ld_p = (inner + 63) / 64 * 64;
     L.ld_g = (cout + 63) / 64 * 64;
-    L.chunk = num_samples < kConvChunk ? (num_samples > 0 ? num_samples : 1) : kConvChunk;
+    L.chunk = conv_chunk(num_samples, L.ld_p);
     const size_t p_bytes = align_up((size_t)L.chunk * L.ld_p * 2);
     const size_t g_bytes = align_up((size_t)L.chunk * L.ld_g * 2);
     const size_t d_bytes = align_up((size_t)L.chunk * inner * 4);

@@ -172,6 +172,45 @@ def test_mcconv_over_several_sample_chunks(many_samples):
         assert _grads_close(x.cpu().numpy(), y.numpy().reshape(x.shape)), name
 
 
+@pytest.mark.parametrize("cin", [8, 32])
+def test_calls_with_more_than_half_a_million_samples_equal_their_halves(cin):
+    """Above 524 288 samples the library switches to chunks of that size (131 072 otherwise).  The rows of a sample do
+    not depend on the other samples of the call, so one call over 540 000 samples (one large chunk and a ragged one)
+    must give what two calls over its halves give (three small chunks each), which the tests above tie to the oracle:
+    bit for bit in the forward pass, within the gradient tolerance where the halves' sums are added.  cin = 8 runs on
+    the CUDA cores, cin = 32 through the tensor-core pair kernels."""
+    from pccnn_lib_b200 import ops
+    from pccnn_lib_b200.pc.layers import prepare_kernel_points
+    n, half, cout, k = 540000, 270000, 16, 16
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    pts = torch.rand((n, 3), device="cuda", generator=gen)
+    cell = torch.full((3,), 0.0164, device="cuda")
+    g = ops.grid_front_end(pts, torch.zeros((n,), dtype=torch.int32, device="cuda"), 1, cell)
+    sp, sk = g["sorted_pts"], g["sorted_keys"]
+    nb, ends = ops.find_neighbors(sp, sk, sp, sk, g["grid_ds"], g["num_cells"], cell, 0)
+    assert 5 * n < nb.shape[0] < 20 * n
+    feats = torch.randn((n, cin), device="cuda", generator=gen)
+    kpts, sigma = prepare_kernel_points(3, k)
+    kpts = dev((kpts * np.random.RandomState(1).uniform(0.85, 0.99, size=(k, 1))).astype(np.float32))
+    weights = torch.randn((k * cin, cout), device="cuda", generator=gen) * float(np.sqrt(2.0 / (cin * k)))
+    grads = torch.randn((n, cout), device="cuda", generator=gen)
+    t_half = int(ends[half - 1].item())
+    parts = [(sp[:half], nb[:t_half], ends[:half], grads[:half]),
+             (sp[half:], nb[t_half:] - torch.tensor([0, half], dtype=torch.int32, device="cuda"), ends[half:] - t_half,
+              grads[half:])]
+    whole = ops.kp_conv(sp, feats, sp, nb, ends, cell, kpts, sigma, weights)
+    halves = [ops.kp_conv(sp, feats, s, b.contiguous(), e.contiguous(), cell, kpts, sigma, weights) for s, b, e, _ in parts]
+    assert torch.equal(whole, torch.cat(halves, 0))
+    assert float(whole[524288:].abs().max()) > 0
+    gw = ops.kp_conv_grads(sp, feats, sp, nb, ends, cell, kpts, sigma, weights, grads)
+    gh = [ops.kp_conv_grads(sp, feats, s, b.contiguous(), e.contiguous(), cell, kpts, sigma, weights, go.contiguous())
+          for s, b, e, go in parts]
+    ops.check_status()
+    for i, name in enumerate(["weights", "features", "kernel_pts", "pts"]):
+        assert _grads_close(gw[i].cpu().numpy(), (gh[0][i] + gh[1][i]).cpu().numpy()), name
+    assert _grads_close(gw[4].cpu().numpy(), torch.cat([gh[0][4], gh[1][4]], 0).cpu().numpy()), "samples"
+
+
 def test_scene_sampler_neighbors_and_capped_density():
     # a small instance of the room-like scene (planes + clutter, density varying over the floor) at its radius
     from pccnn_lib_b200 import ops

@@ -161,12 +161,15 @@ __device__ __forceinline__ void store_p_row(const float (&acc)[NB], int c, int c
     }
 }
 
-template <int NB>
+// SPLIT_F: the features come as two bf16 planes (fp32 inputs); with bf16 inputs there is no lo plane and the CTA is
+// 32 KB smaller, so that five instead of three fit an SM.
+template <int NB, bool SPLIT_F>
 struct TcForwardSmem {
     static constexpr int kF = 2 * kTcRows * 128;  // one plane of the F tile: 32 KB
     static constexpr int kBT = 2 * NB * 128;      // one plane of the BT tile: two 64-neighbor blocks of [NB x 128 B]
-    static constexpr int kFHi = 0, kFLo = kF, kBTHi = 2 * kF, kBTLo = 2 * kF + kBT;
-    static constexpr int kTiles = 2 * kF + 2 * kBT;
+    static constexpr int kFPlanes = SPLIT_F ? 2 : 1;
+    static constexpr int kFHi = 0, kFLo = SPLIT_F ? kF : 0, kBTHi = kFPlanes * kF, kBTLo = kBTHi + kBT;
+    static constexpr int kTiles = kFPlanes * kF + 2 * kBT;
     static constexpr int kMisc = 2048;  // barrier, tensor-memory slot, neighbor ids, basis parameters
     static constexpr int kBytes = kTiles + kMisc;
     static constexpr int kGridBytes = kTiles + 2688;  // list-free variant: + candidate ranges and the hit queue
@@ -187,7 +190,7 @@ project_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes
                   const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
                   __nv_bfloat16* __restrict__ p_hi, __nv_bfloat16* __restrict__ p_lo, int ld_p, uint32_t poll_limit,
                   int* __restrict__ status) {
-    using SM = TcForwardSmem<NB>;
+    using SM = TcForwardSmem<NB, SPLIT_F>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];  // the swizzled tiles need 1024-byte alignment
     uint8_t* smem = smem_raw;
     uint8_t* misc = smem + SM::kTiles;
@@ -843,14 +846,14 @@ static int launch_project_tc_nb(int K, const ARGS& args, const float* pts, const
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcForwardSmem<NB>::kBytes);
+        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcForwardSmem<NB, SPLIT_F>::kBytes);
     });
     PCCNN_CUDA(attr_err);
-    const int per_sm = (227 * 1024) / (TcForwardSmem<NB>::kBytes + 1024);
+    const int per_sm = (227 * 1024) / (TcForwardSmem<NB, SPLIT_F>::kBytes + 1024);
     const int64_t cap = (int64_t)sm_count() * (per_sm < 1 ? 1 : per_sm);
     const int count = m_end - m_begin;
     const unsigned grid = (unsigned)(count < cap ? count : cap);
-    kernel<<<grid, 128, TcForwardSmem<NB>::kBytes, s>>>(args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids,
+    kernel<<<grid, 128, TcForwardSmem<NB, SPLIT_F>::kBytes, s>>>(args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids,
                                                         radii, m_begin, m_end, (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo,
                                                         ld_p, tensor_core_poll_limit(), status);
     PCCNN_LAUNCH_CHECK();
@@ -934,7 +937,7 @@ project_tc_grid_kernel(ARGS args, int K, int num_pts, const float* __restrict__ 
                        const int2* __restrict__ grid_ds, const int32_t* __restrict__ grid_size,
                        const float* __restrict__ radii, int m_begin, int m_end, __nv_bfloat16* __restrict__ p_hi,
                        __nv_bfloat16* __restrict__ p_lo, int ld_p, uint32_t poll_limit, int* __restrict__ status) {
-    using SM = TcForwardSmem<NB>;
+    using SM = TcForwardSmem<NB, SPLIT_F>;
     using S = Stencil<3>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
@@ -1159,14 +1162,14 @@ static int launch_project_tc_grid_nb(int K, const ARGS& args, int num_pts, const
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcForwardSmem<NB>::kGridBytes);
+        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcForwardSmem<NB, SPLIT_F>::kGridBytes);
     });
     PCCNN_CUDA(attr_err);
-    const int per_sm = (227 * 1024) / (TcForwardSmem<NB>::kGridBytes + 1024);
+    const int per_sm = (227 * 1024) / (TcForwardSmem<NB, SPLIT_F>::kGridBytes + 1024);
     const int64_t cap = (int64_t)sm_count() * (per_sm < 1 ? 1 : per_sm);
     const int count = m_end - m_begin;
     const unsigned grid = (unsigned)(count < cap ? count : cap);
-    kernel<<<grid, 128, TcForwardSmem<NB>::kGridBytes, s>>>(args, K, num_pts, sorted_pts, sorted_keys, feats, cin, num_samples, samples,
+    kernel<<<grid, 128, TcForwardSmem<NB, SPLIT_F>::kGridBytes, s>>>(args, K, num_pts, sorted_pts, sorted_keys, feats, cin, num_samples, samples,
                                                         sample_keys, (const int2*)grid_ds, grid_size, radii, m_begin, m_end,
                                                         (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo, ld_p,
                                                         tensor_core_poll_limit(), status);

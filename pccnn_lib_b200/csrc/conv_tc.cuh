@@ -70,11 +70,12 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // the hi plane and lanes 16-31 those of the lo plane (one warp instruction per row); with one plane the two half
 // warps take two rows (NW = warps of the CTA).  Chunks past the row's end and rows without a neighbor are zero-filled.  Asynchronous: the
 // caller waits (cp_async_wait_all) before the tile is used.
-template <bool SPLIT_F, int NW = 4>
+template <bool SPLIT_F, int NW = 4, bool HALF = false>
 __device__ __forceinline__ void gather_features_async(uint32_t f_hi, uint32_t f_lo, const int* s_n0, int rows,
                                                       const FeaturePlanes& f, int cb) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int chunk = lane & 15;       // 8 channels
+    if (HALF && chunk >= 8) return;    // a plane of one 64-channel block: nothing to copy (or to clear) behind it
     const int c = cb + 8 * chunk;
     const uint32_t in_tile = (uint32_t)(chunk >> 3) * (kTcRows * 128);
     if (SPLIT_F) {
@@ -163,15 +164,21 @@ __device__ __forceinline__ void store_p_row(const float (&acc)[NB], int c, int c
 
 // SPLIT_F: the features come as two bf16 planes (fp32 inputs); with bf16 inputs there is no lo plane and the CTA is
 // 32 KB smaller, so that five instead of three fit an SM.
-template <int NB, bool SPLIT_F>
+// HALF: at most 64 input channels, so a plane of the F tile holds one 64-channel block instead of two.  The products
+// still run with M = 128: the descriptor of A finds its second block 16 KB behind the first, which is then whatever
+// follows the plane (the lo plane, the BT tiles, the slots behind them), and the accumulator rows 64-127 that come out
+// of it are never read.  kBytes keeps those 16 KB behind the last plane inside the CTA's allocation.
+template <int NB, bool SPLIT_F, bool HALF = false>
 struct TcForwardSmem {
-    static constexpr int kF = 2 * kTcRows * 128;  // one plane of the F tile: 32 KB
+    static constexpr int kBlock = kTcRows * 128;          // one 64-channel block of a plane: 16 KB
+    static constexpr int kF = (HALF ? 1 : 2) * kBlock;    // one plane of the F tile
     static constexpr int kBT = 2 * NB * 128;      // one plane of the BT tile: two 64-neighbor blocks of [NB x 128 B]
     static constexpr int kFPlanes = SPLIT_F ? 2 : 1;
     static constexpr int kFHi = 0, kFLo = SPLIT_F ? kF : 0, kBTHi = kFPlanes * kF, kBTLo = kBTHi + kBT;
     static constexpr int kTiles = kFPlanes * kF + 2 * kBT;
     static constexpr int kMisc = 2048;  // barrier, tensor-memory slot, neighbor ids, basis parameters
-    static constexpr int kBytes = kTiles + kMisc;
+    static constexpr int kReach = HALF ? kFPlanes * kF + kBlock : 0;
+    static constexpr int kBytes = (kTiles + kMisc > kReach) ? kTiles + kMisc : kReach;
     static constexpr int kGridBytes = kTiles + 2688;  // list-free variant: + candidate ranges and the hit queue
 };
 
@@ -183,14 +190,14 @@ static __device__ long long g_tc_prof[16];
 #endif
 
 // P rows (bf16 hi [+ lo]) of the samples [m_begin, m_end).  One CTA = one sample at a time.
-template <int NB, class BASIS, class ARGS, bool SPLIT_F>
+template <int NB, class BASIS, class ARGS, bool SPLIT_F, bool HALF>
 __global__ void __launch_bounds__(128)
 project_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes feats, int cin,
                   const float* __restrict__ samples, const int2* __restrict__ neighbors,
                   const int32_t* __restrict__ start_ids, const float* __restrict__ radii, int m_begin, int m_end,
                   __nv_bfloat16* __restrict__ p_hi, __nv_bfloat16* __restrict__ p_lo, int ld_p, uint32_t poll_limit,
                   int* __restrict__ status) {
-    using SM = TcForwardSmem<NB, SPLIT_F>;
+    using SM = TcForwardSmem<NB, SPLIT_F, HALF>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];  // the swizzled tiles need 1024-byte alignment
     uint8_t* smem = smem_raw;
     uint8_t* misc = smem + SM::kTiles;
@@ -281,7 +288,7 @@ project_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes
         s_n0[tid] = n0;
         __syncthreads();
         TC_PROF(0);
-        if (cnt > 0) gather_features_async<SPLIT_F>(f_hi, f_lo, s_n0, rows, feats, cb);
+        if (cnt > 0) gather_features_async<SPLIT_F, 4, HALF>(f_hi, f_lo, s_n0, rows, feats, cb);
         TC_PROF(1);
 
         // ---- epilogue of the previous (sample, channel block): thread = channel, NB columns -> K entries of the P row
@@ -838,22 +845,26 @@ backward_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlane
 // Poll limit of the bounded waits (gemm.cu owns it, together with the test hook that shortens it).
 uint32_t tensor_core_poll_limit();
 
-template <int NB, class BASIS, class ARGS, bool SPLIT_F>
+template <int NB, class BASIS, class ARGS, bool SPLIT_F, bool HALF = false>
 static int launch_project_tc_nb(int K, const ARGS& args, const float* pts, const FeaturePlanes& feats, int cin, const float* samples,
                                 const int32_t* neighbors, const int32_t* start_ids, const float* radii, int m_begin,
                                 int m_end, void* p_hi, void* p_lo, int ld_p, int* status, cudaStream_t s) {
-    auto kernel = project_tc_kernel<NB, BASIS, ARGS, SPLIT_F>;
+    if (!HALF && cin <= 64)  // one 64-channel block per plane: a smaller CTA, more of them per SM
+        return launch_project_tc_nb<NB, BASIS, ARGS, SPLIT_F, true>(K, args, pts, feats, cin, samples, neighbors, start_ids,
+                                                                    radii, m_begin, m_end, p_hi, p_lo, ld_p, status, s);
+    using SM = TcForwardSmem<NB, SPLIT_F, HALF>;
+    auto kernel = project_tc_kernel<NB, BASIS, ARGS, SPLIT_F, HALF>;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcForwardSmem<NB, SPLIT_F>::kBytes);
+        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kBytes);
     });
     PCCNN_CUDA(attr_err);
-    const int per_sm = (227 * 1024) / (TcForwardSmem<NB, SPLIT_F>::kBytes + 1024);
+    const int per_sm = (227 * 1024) / (SM::kBytes + 1024);
     const int64_t cap = (int64_t)sm_count() * (per_sm < 1 ? 1 : per_sm);
     const int count = m_end - m_begin;
     const unsigned grid = (unsigned)(count < cap ? count : cap);
-    kernel<<<grid, 128, TcForwardSmem<NB, SPLIT_F>::kBytes, s>>>(args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids,
+    kernel<<<grid, 128, SM::kBytes, s>>>(args, K, pts, feats, cin, samples, (const int2*)neighbors, start_ids,
                                                         radii, m_begin, m_end, (__nv_bfloat16*)p_hi, (__nv_bfloat16*)p_lo,
                                                         ld_p, tensor_core_poll_limit(), status);
     PCCNN_LAUNCH_CHECK();

@@ -164,10 +164,8 @@ __device__ __forceinline__ void store_p_row(const float (&acc)[NB], int c, int c
 
 // SPLIT_F: the features come as two bf16 planes (fp32 inputs); with bf16 inputs there is no lo plane and the CTA is
 // 32 KB smaller, so that five instead of three fit an SM.
-// HALF: at most 64 input channels, so a plane of the F tile holds one 64-channel block instead of two.  The products
-// still run with M = 128: the descriptor of A finds its second block 16 KB behind the first, which is then whatever
-// follows the plane (the lo plane, the BT tiles, the slots behind them), and the accumulator rows 64-127 that come out
-// of it are never read.  kBytes keeps those 16 KB behind the last plane inside the CTA's allocation.
+// HALF: at most 64 input channels, so a plane of the F tile holds one 64-channel block instead of two and the
+// products run with M = 64 (their 64 accumulator rows lie in lanes 0-15 of each quarter of the tensor memory).
 template <int NB, bool SPLIT_F, bool HALF = false>
 struct TcForwardSmem {
     static constexpr int kBlock = kTcRows * 128;          // one 64-channel block of a plane: 16 KB
@@ -177,8 +175,7 @@ struct TcForwardSmem {
     static constexpr int kFHi = 0, kFLo = SPLIT_F ? kF : 0, kBTHi = kFPlanes * kF, kBTLo = kBTHi + kBT;
     static constexpr int kTiles = kFPlanes * kF + 2 * kBT;
     static constexpr int kMisc = 2048;  // barrier, tensor-memory slot, neighbor ids, basis parameters
-    static constexpr int kReach = HALF ? kFPlanes * kF + kBlock : 0;
-    static constexpr int kBytes = (kTiles + kMisc > kReach) ? kTiles + kMisc : kReach;
+    static constexpr int kBytes = kTiles + kMisc;
     static constexpr int kGridBytes = kTiles + 2688;  // list-free variant: + candidate ranges and the hit queue
 };
 
@@ -234,8 +231,9 @@ project_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes
     const uint32_t f_hi = smem_u32(smem + SM::kFHi), f_lo = smem_u32(smem + SM::kFLo);
     const uint32_t bt_hi = smem_u32(smem + SM::kBTHi), bt_lo = smem_u32(smem + SM::kBTLo);
     // fp32 accumulate, bf16 x bf16, A MN-major (bit 15), B K-major, N = NB, M = 128
+    // (M = 64 with one channel block per plane)
     constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)(NB >> 3) << 17) |
-                               ((uint32_t)(128 >> 4) << 24);
+                               ((uint32_t)((HALF ? 64 : 128) >> 4) << 24);
     uint32_t parity = 0;
     bool failed = false;
 
@@ -308,7 +306,11 @@ project_tc_kernel(ARGS args, int K, const float* __restrict__ pts, FeaturePlanes
                     for (int k = 0; k < 16; ++k) acc[k0 + k] = __uint_as_float(r[k]);
                 }
             }
-            store_p_row<NB>(acc, epi_cb + tid, cin, K, p_hi, p_lo, row);
+            if (HALF) {  // 64 accumulator rows: channel 16 w + l is in lane l < 16 of warp w's quarter
+                if ((tid & 31) < 16) store_p_row<NB>(acc, epi_cb + 16 * warp + (tid & 31), cin, K, p_hi, p_lo, row);
+            } else {
+                store_p_row<NB>(acc, epi_cb + tid, cin, K, p_hi, p_lo, row);
+            }
             if (epi_cb + kTcChan >= cin) {  // last channel block: the padding columns feed the contraction too
                 for (int c = inner + tid; c < ld_p; c += 128) {
                     p_hi[row + c] = __float2bfloat16_rn(0.f);
